@@ -1,0 +1,403 @@
+"""Benchmark of the data-parallel hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workloads all|main]
+
+Headline workload (one "step" = one whole image): the Julia-set escape-time map on a
+16384 x 16384 binary32 grid over [-1.6, 1.6]^2, c = -0.8 + 0.156i, max_iter = 4096, uint32
+counts, exact (uncontracted) arithmetic.  With N > 1 the rows are dealt to the ranks in cyclic
+128-row chunks and the image is all-gathered (NCCL) at the end of every step, as the workload
+states; the compute-only figure is reported beside it.  Metric: Gpixel-iters/s = (sum over
+pixels of the iteration count) / time; the count total is an exact property of the workload
+(7 055 521 946, from the CPU oracle, stored in tests/golden/golden.npz).
+
+The JSON line also carries: `roofline` (FP32 issue-rate bound for the escape-time kernel: 8
+binary32 operations per pixel-iteration against an FFMA-chain probe measured in the same run),
+`cpu_baseline` (the CPU oracle on the box's host cores), `e2e` (through the public API with the
+result landing in pinned host memory), `other_workloads` (1080p Mandelbrot frames, the fused map
+chain, row reductions / softmax, tanh-MSE forward and backward: achieved HBM GB/s against the
+measured copy bandwidth) and `clocks`.
+
+`--impl reference` times the CPU restatement of the path (the reference project ships no
+runnable implementation of it) on all host threads, on a bounded row sample of the same image.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+JULIA = dict(W=16384, H=16384, x0=-1.6, x1=1.6, y0=-1.6, y1=1.6, cr=-0.8, ci=0.156, max_iter=4096)
+WORKLOAD_NAME = "julia 16384x16384 [-1.6,1.6]^2 c=-0.8+0.156i max_iter=4096 u32 exact"
+OPS_PER_ITER = 8  # a=zr*zr b=zi*zi s=a+b t=zr*zi t+t (..)+ci a-b (..)+cr
+
+
+def golden_total() -> int:
+    g = np.load(os.path.join(ROOT, "tests", "golden", "golden.npz"))
+    return int(g["julia_16k_digest"][0])
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.proc, self.path = gpu_index, None, None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.gpu)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        for line in open(self.path):
+            f = [v.strip() for v in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
+                "samples": len(sm), "power_w_max": max(power)}
+
+
+def run_reference(args):
+    """CPU arm: the oracle on all host threads, on a bounded row sample of the Julia image."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle
+
+    J = JULIA
+    dx, dy = oracle.grid_steps(J["x0"], J["x1"], J["y0"], J["y1"], J["W"], J["H"])
+    cores = oracle.num_threads()
+
+    def sample(stride):
+        t = time.perf_counter()
+        _, total = oracle.escape_time(oracle.JULIA, J["W"], J["H"], J["x0"], J["y0"], dx, dy, J["cr"], J["ci"], J["max_iter"],
+                                      row_begin=stride // 2 if stride > 1 else 0, row_step=stride, want_image=False)
+        return total, time.perf_counter() - t
+
+    _, probe_s = sample(64)
+    stride = 1
+    while probe_s * 64 / stride > 6.0 and stride < 64:  # keep one step under ~6 s
+        stride *= 2
+    for _ in range(args.warmup):
+        sample(stride)
+    iters, secs = 0, 0.0
+    for _ in range(args.steps):
+        n, s = sample(stride)
+        iters += n
+        secs += s
+    value = iters / secs / 1e9
+    desc = f"every {stride}th row of the image ({J['H'] // stride} rows x {J['W']} px per step)" if stride > 1 else "the whole image per step"
+    line = {"impl": "reference", "metric": "Gpixel-iters/s", "value": value, "unit": "Gpixel-iters/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * secs / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD_NAME, "sample": desc},
+            "cpu_baseline": {"value": value, "unit": "Gpixel-iters/s", "cores": cores, "kind": "port", "sample": desc},
+            "e2e": {"value": value, "unit": "Gpixel-iters/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": "the reference project has no runnable implementation of this path; this is the CPU restatement (oracle/) on all host threads"}
+    print(json.dumps(line), flush=True)
+
+
+def time_launches(dev, st, fn, iters, warmup=3):
+    """Average milliseconds per call of fn(), CUDA events on the launching stream."""
+    for _ in range(warmup):
+        fn()
+    e0, e1 = dev.event(), dev.event()
+    st.synchronize()
+    e0.record(st)
+    for _ in range(iters):
+        fn()
+    e1.record(st)
+    e1.synchronize()
+    ms = e0.elapsed_ms(e1) / iters
+    e0.close(); e1.close()
+    return ms
+
+
+def other_workloads(dev, st, torch, hbm_peak, peak_kind, fp32_peak):
+    """Single-GPU lines for the remaining workloads; inputs are generated on the device (seeded)."""
+    from vernondsl_b200 import _lib as L
+    from vernondsl_b200 import ops
+
+    out = []
+    device = f"cuda:{dev.ordinal}"
+    gen = torch.Generator(device=device)
+
+    def randn(shape, seed, scale=1.0):
+        gen.manual_seed(seed)
+        return torch.randn(shape, generator=gen, device=device, dtype=torch.float32) * scale
+
+    def line(name, kernel, ms, algo_bytes, note=""):
+        gbs = algo_bytes / (ms * 1e-3) / 1e9
+        out.append({"workload": name, "kernel": kernel, "ms": ms, "algorithmic_bytes": algo_bytes, "achieved_gbs": gbs,
+                    "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak,
+                                 "peak_kind": peak_kind, "frac_of_nominal_8tbs": gbs / 8000.0}, "note": note})
+
+    # Mandelbrot 1920x1080, max_iter 256: frames back to back (the image is 8.3 MB, so this one is not DRAM-sized)
+    W, H = 1920, 1080
+    dx, dy = ops.grid_steps(-2.5, 1.0, -1.0, 1.0, W, H)
+    img = dev.empty((H, W), np.uint32, L.IMAGE)
+    p = ops.escape_params(L.MANDELBROT, W, H, -2.5, -1.0, dx, dy, max_iter=256)
+    ms = time_launches(dev, st, lambda: ops.escape_time(st, img, p), 50)
+    total = int(np.load(os.path.join(ROOT, "tests", "golden", "golden.npz"))["mandelbrot_1080p_digest"][0])
+    rate = total / (ms * 1e-3)
+    out.append({"workload": "mandelbrot 1920x1080 max_iter=256 u32 exact, 50 frames back to back", "kernel": "escape_time", "ms": ms,
+                "gpixel_iters_per_s": rate / 1e9,
+                "roofline": {"bound": "fp32", "achieved": OPS_PER_ITER * rate / 1e9, "peak": fp32_peak, "unit": "Gop/s",
+                             "frac": OPS_PER_ITER * rate / 1e9 / fp32_peak}})
+    img.close()
+
+    # fused map chain, 2^28 elements
+    n = 1 << 28
+    gen.manual_seed(1003)
+    a = torch.rand(n, generator=gen, device=device, dtype=torch.float32) * 2 - 1
+    x, y = randn(n, 1001), randn(n, 1002)
+    o = torch.empty_like(x)
+    A, X, Y, O = (dev.wrap_tensor(t) for t in (a, x, y, o))
+    ms = time_launches(dev, st, lambda: ops.fused_map(st, A, X, Y, O, n), 10)
+    line("fused map chain, 2^28 f32", "fused_map", ms, 16 * n)
+    del a, x, y, o
+
+    # row reductions and softmax, [65536, 4096], N(0,4) read as sigma = 2
+    R, Cc = 65536, 4096
+    m = randn((R, Cc), 2001, 2.0)
+    sm = torch.empty_like(m)
+    rs, rm = torch.empty(R, device=device), torch.empty(R, device=device)
+    M, SM, RS, RM = (dev.wrap_tensor(t) for t in (m, sm, rs, rm))
+    ms = time_launches(dev, st, lambda: ops.row_sum(st, M, RS, R, Cc), 10)
+    line("row sum [65536,4096] f32", "row_sum", ms, 4 * R * Cc + 4 * R)
+    ms = time_launches(dev, st, lambda: ops.row_max(st, M, RM, R, Cc), 10)
+    line("row max [65536,4096] f32", "row_max", ms, 4 * R * Cc + 4 * R)
+    ms = time_launches(dev, st, lambda: ops.row_softmax(st, M, SM, R, Cc), 10)
+    line("row softmax [65536,4096] f32", "row_softmax", ms, 8 * R * Cc)
+    ms = time_launches(dev, st, lambda: ops.row_stats_softmax(st, M, RS, RM, SM, R, Cc), 10)
+    line("row sum+max+softmax in one pass [65536,4096] f32", "row_stats_softmax", ms, 8 * R * Cc + 8 * R)
+    del m, sm
+
+    # tanh-MSE forward and backward, [32768, 4096]
+    R, Cc = 32768, 4096
+    Wt, xt, tt = randn((R, Cc), 3001), randn((R, Cc), 3002), randn((R, Cc), 3003)
+    bt = randn(Cc, 3004)
+    dWt, dxt = torch.empty_like(Wt), torch.empty_like(Wt)
+    dbt, lt = torch.empty(Cc, device=device), torch.empty(4, device=device)
+    bW, bx, bb, bt_, bdW, bdx, bdb, bl = (dev.wrap_tensor(t) for t in (Wt, xt, bt, tt, dWt, dxt, dbt, lt))
+    ms = time_launches(dev, st, lambda: ops.mse_tanh_fwd(st, bW, bx, bb, bt_, bl, R, Cc), 10)
+    line("tanh-MSE loss [32768,4096] f32", "mse_tanh_fwd", ms, 12 * R * Cc)
+    ms = time_launches(dev, st, lambda: ops.mse_tanh_bwd(st, bW, bx, bb, bt_, bdW, bdx, bdb, R, Cc), 10)
+    line("tanh-MSE backward dW,dx,db [32768,4096] f32 (forward recomputed)", "mse_tanh_bwd", ms, 20 * R * Cc + 8 * Cc,
+         "includes the column-sum finalize kernel")
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workloads", default="all", choices=["all", "main"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import vernondsl_b200 as vd
+    from vernondsl_b200 import _lib as L
+    from vernondsl_b200 import ops, partition
+
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
+
+    dev = vd.Device(local)
+    tstream = torch.cuda.Stream(device=local)
+    st = dev.wrap_stream(tstream.cuda_stream)
+    hbm_peak, peak_kind = measured_peaks()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # FP32 issue-rate probe (FFMA chains): the denominator of the escape-time roofline
+    probe_out = dev.empty(4, np.float32)
+    per_thread = 64 * 4000
+    threads = dev.sm_count * 2048
+    probe_ms = min(time_launches(dev, st, lambda: ops.fp32_probe(st, probe_out, per_thread, threads), 3, warmup=1) for _ in range(3))
+    fp32_peak = per_thread * threads / (probe_ms * 1e-3) / 1e9  # G lane-instructions / s
+    fp32_nominal = dev.sm_count * 128 * dev.sm_clock_khz * 1e3 / 1e9
+
+    J = JULIA
+    W, H = J["W"], J["H"]
+    dx, dy = ops.grid_steps(J["x0"], J["x1"], J["y0"], J["y1"], W, H)
+    plan = partition.plan_image(H, world, rank, L.PART_CYCLIC, 128)
+    image_t = torch.zeros((H, W), dtype=torch.int32, device=f"cuda:{local}")
+    image = dev.wrap_tensor(image_t, L.IMAGE)
+    params = ops.escape_params(L.JULIA, W, H, J["x0"], J["y0"], dx, dy, cr=J["cr"], ci=J["ci"], max_iter=J["max_iter"],
+                               partition=plan.part if world > 1 else None)
+    total_iters = golden_total()
+
+    def compute():
+        ops.escape_time(st, image, params)
+
+    def step():
+        compute()
+        if world > 1:
+            with torch.cuda.stream(tstream):
+                partition.all_gather_image(image_t, plan)
+
+    def timed(fn, k):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(tstream):
+            e0.record(tstream)
+            for _ in range(k):
+                fn()
+            e1.record(tstream)
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=f"cuda:{local}")
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(args.warmup):
+        step()
+    launches0 = st.launch_count()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    total_ms = timed(step, args.steps)
+    launches = st.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    ms_per_step = total_ms / args.steps
+    value = total_iters / (ms_per_step * 1e-3) / 1e9
+
+    # the image every rank now holds must be the oracle's, bit for bit (exact integer digest)
+    got_sum = int(image_t.sum(dtype=torch.int64).item())
+    idx = torch.arange(1, H * W + 1, device=f"cuda:{local}", dtype=torch.int64)
+    got_wsum = int((image_t.view(-1).to(torch.int64) * idx).sum().item()) & 0xFFFFFFFFFFFFFFFF
+    del idx
+    g = np.load(os.path.join(ROOT, "tests", "golden", "golden.npz"))
+    verified = [got_sum, got_wsum] == [int(v) for v in g["julia_16k_digest"]]
+
+    compute_ms = timed(compute, args.steps) / args.steps if world > 1 else ms_per_step
+    compute_value = total_iters / (compute_ms * 1e-3) / 1e9
+
+    # end to end through the public API: the result lands in pinned host memory every step
+    chunks = plan.chunks() if world > 1 else [(0, H)]
+    host = vd.PinnedArray((sum(n for _, n in chunks), W), np.uint32)
+
+    def e2e_step():
+        compute()
+        row = 0
+        for r0, n in chunks:
+            image.download(host.array[row:row + n], offset=r0 * W * 4, stream=st)
+            row += n
+        st.synchronize()
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(e2e_steps):
+        e2e_step()
+    barrier()
+    e2e_s = torch.tensor([time.perf_counter() - t0], device=f"cuda:{local}", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
+    e2e_value = total_iters * e2e_steps / float(e2e_s.item()) / 1e9
+    d2h = sum(n for _, n in chunks) * W * 4
+    host.close()
+
+    if rank == 0:
+        achieved = OPS_PER_ITER * total_iters / (compute_ms * 1e-3) / 1e9 / world  # per GPU
+        line = {
+            "metric": "Gpixel-iters/s", "value": value, "unit": "Gpixel-iters/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD_NAME, "partition": f"cyclic 128-row chunks over {world} rank(s)",
+                       "collective": "in-place NCCL all-gather of the image each step" if world > 1 else "none",
+                       "l2": "no inputs; the 1 GiB output image written each step exceeds L2 (126 MB)"},
+            "verified_bit_exact": verified,
+            "compute_only": {"value": compute_value, "ms_per_step": compute_ms},
+            "roofline": {"bound": "fp32", "achieved": achieved, "peak": fp32_peak, "unit": "Gop/s", "frac": achieved / fp32_peak,
+                         "traffic": None, "peak_kind": "FFMA-chain probe in this run (lane-instructions/s)",
+                         "peak_nominal": fp32_nominal, "frac_of_nominal": achieved / fp32_nominal,
+                         "algorithmic": f"{OPS_PER_ITER} f32 ops per pixel-iteration x {total_iters} iterations per image, per GPU"},
+            "e2e": {"value": e2e_value, "unit": "Gpixel-iters/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": d2h,
+                    "note": "kernel + download of this rank's rows into pinned host memory; uniforms travel as kernel parameters"},
+            "gpu_launches": int(launches), "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            import oracle
+
+            t0 = time.perf_counter()
+            _, tot = oracle.escape_time(oracle.JULIA, W, H, J["x0"], J["y0"], dx, dy, J["cr"], J["ci"], J["max_iter"], want_image=False)
+            secs = time.perf_counter() - t0
+            line["cpu_baseline"] = {"value": tot / secs / 1e9, "unit": "Gpixel-iters/s", "cores": oracle.num_threads(), "kind": "port",
+                                    "sample": "the whole 16384x16384 image, once"}
+        if world == 1 and args.workloads == "all":
+            image.close()
+            del image_t
+            torch.cuda.empty_cache()
+            line["other_workloads"] = other_workloads(dev, st, torch, hbm_peak, peak_kind, fp32_peak)
+        print(json.dumps(line), flush=True)
+    barrier()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,328 @@
+/*
+ * vrhi.h -- C ABI of libvrhi.so, the B200 (sm_100a) execution backend for VernonDSL-style
+ * data-parallel kernels: the per-element escape-time map of fractal.py, fused elementwise map
+ * chains, the row reductions and softmax they feed, and the backward of those operators.
+ *
+ * WHAT THIS BOUNDARY REPLACES.  The reference project has no runtime, device layer, operator
+ * registry or FFI of its own; nothing in its tree calls a kernel library.  Its only executable
+ * statement of the path is fractal.py, which reaches a GPU through the third-party Taichi
+ * runtime (fractal.py:5 ti.init, :8 ti.field, :16 @ti.kernel, :31 paint(t)).  The entry points
+ * below are therefore what a Vernon runtime would bind in place of those Taichi calls; each
+ * group names the reference line it stands in for.  The one Vernon-specific artefact that
+ * constrains this ABI is the `vernon.semantic` argument vocabulary
+ * (source/lib/Dialect/Vernon/Transforms/VernonToSpirv.cpp:38-56,
+ * source/tests/integration/color.mlir:4-9,43-45), kept here as `vrhi_arg_class`.
+ *
+ * RULES.  C linkage, plain pointers and sizes, opaque handles; no C++ or torch types.  Every
+ * function returns an int status (0 = VRHI_OK, negative = VRHI_ERR_*); `vrhi_last_error()`
+ * returns a thread-local message for the last failure on the calling thread.  Nothing aborts,
+ * exits or traps.  There is NO CPU fallback: a shape or mode a kernel does not support returns
+ * VRHI_ERR_UNSUPPORTED.  Handles are not locked internally: drive one stream from one thread
+ * at a time; different streams and devices may be driven from different threads.
+ */
+#ifndef VRHI_H_
+#define VRHI_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define VRHI_API __attribute__((visibility("default")))
+#else
+#define VRHI_API
+#endif
+
+#define VRHI_VERSION 100 /* major*100 + minor */
+
+/* ---------------------------------------------------------------- status codes ---------- */
+enum vrhi_status {
+  VRHI_OK = 0,
+  VRHI_ERR_INVALID = -1,     /* NULL handle, bad enum, bad argument count ...                 */
+  VRHI_ERR_CUDA = -2,        /* a CUDA runtime call failed; message holds cudaGetErrorString  */
+  VRHI_ERR_OOM = -3,         /* device or pinned-host allocation failed                       */
+  VRHI_ERR_UNSUPPORTED = -4, /* shape / mode not implemented by any kernel (no CPU fallback)  */
+  VRHI_ERR_TIMEOUT = -5,     /* a bounded device-side wait gave up                            */
+  VRHI_ERR_NOT_FOUND = -6,   /* unknown operator or semantic name                             */
+  VRHI_ERR_SIZE = -7,        /* buffer too small / size mismatch / misaligned offset          */
+  VRHI_ERR_GRAPH = -8        /* execution-graph construction or compilation error            */
+};
+
+/* Thread-local text of the last error on this thread ("" if none).  Never NULL. */
+VRHI_API const char *vrhi_last_error(void);
+VRHI_API int vrhi_version(void);
+
+/* ------------------------------------------------------------- argument classes --------- */
+/* The `vernon.semantic` vocabulary: VernonToSpirv.cpp:44-55 (input, output, uniform,
+ * uniform_constant, storage_buffer, image) plus `varying`, which color.mlir:9,44 uses and the
+ * reference pass leaves unhandled.  A buffer is created with one class; operators check that
+ * what they write is not INPUT / UNIFORM / UNIFORM_CONSTANT. */
+enum vrhi_arg_class {
+  VRHI_INPUT = 0,
+  VRHI_OUTPUT = 1,
+  VRHI_UNIFORM = 2,
+  VRHI_UNIFORM_CONSTANT = 3,
+  VRHI_STORAGE_BUFFER = 4,
+  VRHI_IMAGE = 5,
+  VRHI_VARYING = 6
+};
+/* "input" -> VRHI_INPUT ...; VRHI_ERR_NOT_FOUND for any other string. */
+VRHI_API int vrhi_arg_class_from_semantic(const char *semantic, int *out_class);
+VRHI_API const char *vrhi_arg_class_name(int arg_class); /* NULL if out of range */
+
+/* ------------------------------------------------------------------- handles ------------ */
+typedef struct vrhi_device_t *vrhi_device;
+typedef struct vrhi_buffer_t *vrhi_buffer;
+typedef struct vrhi_stream_t *vrhi_stream;
+typedef struct vrhi_event_t *vrhi_event;
+typedef struct vrhi_graph_t *vrhi_graph;
+
+/* ------------------------------------------------------------------- device ------------- */
+/* Stands in for fractal.py:5 (ti.init(arch=...)): choose and open the compute device. */
+typedef struct vrhi_device_props {
+  uint32_t size;           /* set to sizeof(vrhi_device_props) by the caller */
+  int32_t ordinal;
+  int32_t sm_count;
+  int32_t cc_major, cc_minor;
+  int32_t sm_clock_khz;    /* maximum SM clock */
+  int32_t mem_clock_khz;
+  int32_t l2_bytes;
+  int32_t smem_per_block_optin;
+  uint64_t total_mem_bytes;
+  char name[128];
+} vrhi_device_props;
+
+VRHI_API int vrhi_device_count(int *out_count);
+VRHI_API int vrhi_device_create(int ordinal, vrhi_device *out_dev);
+VRHI_API int vrhi_device_destroy(vrhi_device dev); /* NULL is accepted */
+VRHI_API int vrhi_device_props_get(vrhi_device dev, vrhi_device_props *out_props);
+VRHI_API int vrhi_device_synchronize(vrhi_device dev);
+/* Test hook for the out-of-memory path: refuse allocations once more than `bytes` are held by
+ * this device handle (0 = no limit).  Host-side accounting only. */
+VRHI_API int vrhi_device_set_alloc_limit(vrhi_device dev, uint64_t bytes);
+VRHI_API int vrhi_device_allocated(vrhi_device dev, uint64_t *out_bytes);
+
+/* ------------------------------------------------------------------- buffers ------------ */
+/* Stands in for fractal.py:8 (ti.field(dtype, shape)): dense device storage.  The library owns
+ * device memory it creates; the caller owns host memory and any pointer it wraps. */
+VRHI_API int vrhi_buffer_create(vrhi_device dev, uint64_t bytes, int arg_class, vrhi_buffer *out_buf);
+/* Adopt device memory owned by someone else (for example a torch tensor's data_ptr). */
+VRHI_API int vrhi_buffer_wrap(vrhi_device dev, void *device_ptr, uint64_t bytes, int arg_class,
+                              vrhi_buffer *out_buf);
+VRHI_API int vrhi_buffer_destroy(vrhi_buffer buf); /* NULL is accepted */
+VRHI_API int vrhi_buffer_size(vrhi_buffer buf, uint64_t *out_bytes);
+VRHI_API int vrhi_buffer_class(vrhi_buffer buf, int *out_class);
+VRHI_API int vrhi_buffer_device_ptr(vrhi_buffer buf, void **out_ptr);
+/* Asynchronous on `stream` (NULL = the device's default stream, then synchronous).  Host memory
+ * should be pinned (vrhi_host_alloc) for the copy to overlap. */
+VRHI_API int vrhi_buffer_upload(vrhi_buffer buf, uint64_t offset, const void *host, uint64_t bytes,
+                                vrhi_stream stream);
+VRHI_API int vrhi_buffer_download(vrhi_buffer buf, uint64_t offset, void *host, uint64_t bytes,
+                                  vrhi_stream stream);
+VRHI_API int vrhi_buffer_fill_u8(vrhi_buffer buf, uint64_t offset, int value, uint64_t bytes,
+                                 vrhi_stream stream);
+VRHI_API int vrhi_host_alloc(uint64_t bytes, void **out_host); /* pinned */
+VRHI_API int vrhi_host_free(void *host);
+
+/* ---------------------------------------------------------------- streams / events ------ */
+VRHI_API int vrhi_stream_create(vrhi_device dev, vrhi_stream *out_stream);
+/* Adopt an existing CUDA stream handle (a cudaStream_t / CUstream, e.g. torch's). */
+VRHI_API int vrhi_stream_wrap(vrhi_device dev, void *cuda_stream, vrhi_stream *out_stream);
+VRHI_API int vrhi_stream_destroy(vrhi_stream stream); /* NULL is accepted */
+VRHI_API int vrhi_stream_synchronize(vrhi_stream stream);
+/* Device-side status word of the stream: kernels with bounded waits or index checks record a
+ * VRHI_ERR_* there instead of trapping.  Synchronises the stream, returns and clears it. */
+VRHI_API int vrhi_stream_check(vrhi_stream stream);
+/* Number of kernels this library has launched on the stream since it was created. */
+VRHI_API int vrhi_stream_launch_count(vrhi_stream stream, uint64_t *out_count);
+VRHI_API int vrhi_event_create(vrhi_device dev, vrhi_event *out_event);
+VRHI_API int vrhi_event_destroy(vrhi_event event); /* NULL is accepted */
+VRHI_API int vrhi_event_record(vrhi_event event, vrhi_stream stream);
+VRHI_API int vrhi_event_synchronize(vrhi_event event);
+VRHI_API int vrhi_event_elapsed_ms(vrhi_event start, vrhi_event stop, float *out_ms);
+VRHI_API int vrhi_stream_wait_event(vrhi_stream stream, vrhi_event event);
+
+/* ------------------------------------------------------------------ operators ----------- */
+/* Stands in for fractal.py:16,31 (@ti.kernel definition and its launch): a registry of named
+ * kernels, each launched with buffer arguments and a small POD parameter block ("uniforms").
+ * The registry is immutable after library load. */
+typedef struct vrhi_arg {
+  vrhi_buffer buffer;
+  uint64_t offset;   /* byte offset into the buffer; must be a multiple of 16 */
+  uint64_t bytes;    /* bytes of the view; 0 = from offset to the end of the buffer */
+  int32_t arg_class; /* how this operator uses the view (checked against the op's signature) */
+  int32_t reserved;
+} vrhi_arg;
+
+VRHI_API int vrhi_op_count(int *out_count);
+VRHI_API int vrhi_op_name(int op, const char **out_name);
+VRHI_API int vrhi_op_lookup(const char *name, int *out_op);
+/* One line describing the op's arguments and parameter struct, for diagnostics. */
+VRHI_API int vrhi_op_signature(int op, const char **out_text);
+VRHI_API int vrhi_op_launch(vrhi_stream stream, int op, const vrhi_arg *args, int n_args,
+                            const void *params, size_t params_size);
+
+/* Every parameter struct starts with its own size so that it can grow compatibly. */
+
+/* op "escape_time" -- args: [0] OUTPUT/IMAGE image, row-major [height][width].
+ * Per pixel (i, j): x = x0 + (float)i*dx, y = y0 + (float)j*dy (pixel corner, fractal.py:20);
+ * MANDELBROT: z = 0, c = (x, y);  JULIA: z = (x, y), c = (cr, ci).
+ * Loop (fractal.py:21-24): a = zr*zr; b = zi*zi; stop if test(a+b) or count == max_iter;
+ * t = zr*zi; zi = (t+t)+ci; zr = (a-b)+cr; ++count.
+ * EXACT mode performs exactly these binary32 roundings (no contraction across them), so the
+ * counts are reproducible bit for bit; FAST mode lets multiply-adds fuse and may differ on a
+ * small fraction of pixels.
+ * Rows processed: chunks k = chunk_first, chunk_first+chunk_step, ... (chunk_count of them),
+ * chunk k covering rows [k*chunk_rows, min(height, (k+1)*chunk_rows)).  Results are written at
+ * their true position in the full image.  chunk_rows = 0 means "the whole image". */
+enum { VRHI_ESCAPE_MANDELBROT = 0, VRHI_ESCAPE_JULIA = 1 };
+enum { VRHI_ESCAPE_EXACT = 0, VRHI_ESCAPE_FAST = 1 };
+enum { VRHI_TEST_NORM2_GT = 0, /* stop when a+b > bound                         */
+       VRHI_TEST_NORM_GE = 1   /* stop unless sqrtf(a+b) < bound (fractal.py:22) */ };
+enum { VRHI_OUT_COUNT_U32 = 0, VRHI_OUT_COUNT_U16 = 1,
+       VRHI_OUT_COLOR_F32 = 2 /* 1 - count*color_scale, fractal.py:25 */ };
+typedef struct vrhi_escape_params {
+  uint32_t size;
+  uint32_t kind, mode, test, output;
+  uint32_t width, height;
+  uint32_t max_iter;
+  float x0, y0, dx, dy;
+  float cr, ci;
+  float bound;
+  float color_scale;
+  uint32_t chunk_rows, chunk_first, chunk_step, chunk_count;
+} vrhi_escape_params;
+
+/* op "fused_map" -- the map chain  out = tanh(a*x + y) * exp(-0.5*x*x) + sqrt(|y| + 1e-3)
+ * as one kernel.  args: [0] a, [1] x, [2] y (INPUT, n floats), [3] out (OUTPUT, n floats). */
+typedef struct vrhi_map_params {
+  uint32_t size;
+  uint32_t reserved;
+  uint64_t n;
+} vrhi_map_params;
+
+/* op "map_tape" -- a fused chain of elementwise operations given as a register tape, run as
+ * one kernel.  args: n_inputs INPUT views then n_outputs OUTPUT views.  Input k is a full
+ * [rows][cols] array unless bit k is set in one of the masks: row_vector_mask = a [cols] row
+ * vector broadcast down the rows; col_vector_mask = a [rows] vector, one value per row,
+ * broadcast along it; scalar_mask = a single float broadcast everywhere.
+ * Instruction t computes value (n_inputs + t) from earlier values. */
+enum vrhi_tape_op {
+  VRHI_T_CONST = 0, /* imm */
+  VRHI_T_ADD, VRHI_T_SUB, VRHI_T_MUL, VRHI_T_DIV, VRHI_T_MAX, VRHI_T_MIN,  /* a, b */
+  VRHI_T_FMA,                                                           /* a*b + c */
+  VRHI_T_NEG, VRHI_T_ABS, VRHI_T_SQUARE, VRHI_T_SQRT, VRHI_T_RSQRT, VRHI_T_RECIP,
+  VRHI_T_EXP, VRHI_T_LOG, VRHI_T_TANH, VRHI_T_SIGMOID, VRHI_T_RELU, VRHI_T_COS, VRHI_T_SIN,
+  VRHI_T_SIGN, VRHI_T_STEP, /* step: 1 if a > 0 else 0 */
+  VRHI_T_EQ,                /* 1 if a == b else 0 */
+  VRHI_T_OPCOUNT
+};
+#define VRHI_TAPE_MAX_INSTR 64
+#define VRHI_TAPE_MAX_INPUTS 8
+#define VRHI_TAPE_MAX_OUTPUTS 4
+typedef struct vrhi_tape_instr {
+  uint16_t op;
+  uint16_t a, b, c; /* value indices */
+  float imm;
+} vrhi_tape_instr;
+typedef struct vrhi_tape_params {
+  uint32_t size;
+  uint32_t n_inputs, n_outputs, n_instr;
+  uint64_t rows, cols;              /* element count = rows*cols */
+  uint32_t row_vector_mask, col_vector_mask, scalar_mask;
+  uint32_t out_value[VRHI_TAPE_MAX_OUTPUTS]; /* value index stored to output k */
+  vrhi_tape_instr instr[VRHI_TAPE_MAX_INSTR];
+} vrhi_tape_params;
+
+/* ops "row_sum", "row_max": args [0] INPUT [rows][cols] floats, [1] OUTPUT [rows] floats.
+ * op "row_softmax": args [0] INPUT [rows][cols], [1] OUTPUT [rows][cols]; max is subtracted.
+ * op "row_stats_softmax": one pass producing all three: args [0] INPUT, [1] OUTPUT sum[rows],
+ *   [2] OUTPUT max[rows], [3] OUTPUT softmax[rows][cols].
+ * op "col_sum": args [0] INPUT [rows][cols], [1] OUTPUT [cols]. Deterministic (no float atomics). */
+typedef struct vrhi_rows_params {
+  uint32_t size;
+  uint32_t reserved;
+  uint64_t rows, cols;
+} vrhi_rows_params;
+
+/* op "mse_tanh_fwd": loss contribution of `rows` rows:  sum((tanh(W*x + b[col]) - t)^2) / denom.
+ *   args [0] W, [1] x, [2] b ([cols]), [3] t (INPUT), [4] OUTPUT loss (one float).
+ * op "mse_tanh_bwd": g = 2*(y - t)*(1 - y*y)/denom with y recomputed; dW = g*x, dx = g*W,
+ *   db[col] = sum over rows of g (fixed summation order, bit-reproducible).
+ *   args [0] W, [1] x, [2] b, [3] t (INPUT), [4] dW, [5] dx, [6] db (OUTPUT),
+ *   optional [7] OUTPUT loss (one float).
+ * denom = 0 means rows*cols; a row shard of a larger matrix passes the whole element count. */
+typedef struct vrhi_mse_params {
+  uint32_t size;
+  uint32_t reserved;
+  uint64_t rows, cols;
+  double denom;
+} vrhi_mse_params;
+
+/* op "fp32_probe": dependent-free FFMA chains, for measuring the FP32 issue peak the
+ * escape-time kernel is bounded by.  args [0] OUTPUT (>= 4 bytes).  Executes
+ * `ffma_per_thread` FFMAs in each of `threads` threads. */
+typedef struct vrhi_probe_params {
+  uint32_t size;
+  uint32_t reserved;
+  uint64_t ffma_per_thread;
+  uint64_t threads; /* 0 = fill the device */
+} vrhi_probe_params;
+
+/* --------------------------------------------------------------- partitioning ----------- */
+/* Host-side planning for N devices in one box, one process per device.  No CUDA calls. */
+enum { VRHI_PART_CONTIGUOUS = 0, VRHI_PART_CYCLIC = 1 };
+typedef struct vrhi_row_partition {
+  uint32_t chunk_rows, chunk_first, chunk_step, chunk_count; /* feed vrhi_escape_params */
+  uint64_t rows_owned;
+} vrhi_row_partition;
+/* Split `total_rows` image rows over `world` ranks.  CONTIGUOUS: one band per rank (sizes
+ * differ by at most one chunk).  CYCLIC: chunks of `chunk_rows` rows dealt round-robin, which
+ * balances escape-time work whose cost varies smoothly over the image. */
+VRHI_API int vrhi_partition_rows(uint64_t total_rows, uint32_t chunk_rows, uint32_t world,
+                                 uint32_t rank, int scheme, vrhi_row_partition *out);
+/* Split `n` leading-axis units evenly (first n%world ranks get one more). */
+VRHI_API int vrhi_partition_leading(uint64_t n, uint32_t world, uint32_t rank, uint64_t *out_begin,
+                                    uint64_t *out_count);
+
+/* ------------------------------------------------------------- execution graph ---------- */
+/* A small tensor graph over [rows][cols] float arrays, [cols] row vectors (broadcast down the
+ * rows), [rows] column vectors produced by row reductions, and scalars.  `grad` appends the
+ * reverse-mode derivative sub-graph; `compile` fuses every maximal group of elementwise nodes
+ * into one map kernel (several results of one group leave the same kernel), selects a
+ * hand-written specialised kernel where the whole group matches one, and plans the reductions
+ * between them; `launch` enqueues the planned kernels on a stream. */
+enum vrhi_graph_reduce {
+  VRHI_R_ROW_SUM = 0, VRHI_R_ROW_MAX = 1, VRHI_R_COL_SUM = 2, VRHI_R_SUM_ALL = 3, VRHI_R_MEAN_ALL = 4
+};
+VRHI_API int vrhi_graph_create(vrhi_device dev, uint64_t rows, uint64_t cols, vrhi_graph *out_graph);
+VRHI_API int vrhi_graph_destroy(vrhi_graph g); /* NULL is accepted */
+/* flags: bit 0 = never select a specialised kernel (every fused group runs the generic tape
+ * kernel).  The environment variable VRHI_GRAPH_NO_SPECIALIZE=1 sets bit 0 at creation. */
+VRHI_API int vrhi_graph_set_flags(vrhi_graph g, uint32_t flags);
+/* shape: 0 = full [rows][cols]; 1 = row vector [cols]; 2 = column vector [rows]; 3 = scalar. */
+enum { VRHI_SHAPE_FULL = 0, VRHI_SHAPE_ROWVEC = 1, VRHI_SHAPE_COLVEC = 2, VRHI_SHAPE_SCALAR = 3 };
+VRHI_API int vrhi_graph_input(vrhi_graph g, vrhi_buffer buf, int shape, int *out_node);
+VRHI_API int vrhi_graph_const(vrhi_graph g, float value, int *out_node);
+VRHI_API int vrhi_graph_unary(vrhi_graph g, int tape_op, int a, int *out_node);
+VRHI_API int vrhi_graph_binary(vrhi_graph g, int tape_op, int a, int b, int *out_node);
+VRHI_API int vrhi_graph_reduce(vrhi_graph g, int reduce_op, int a, int *out_node);
+VRHI_API int vrhi_graph_softmax(vrhi_graph g, int a, int *out_node);
+/* Append d(loss)/d(wrt[k]) for each k; loss must be a scalar node.  out_nodes[k] has the shape
+ * of wrt[k] (a row-vector input receives a column reduction of its broadcast gradient). */
+VRHI_API int vrhi_graph_grad(vrhi_graph g, int loss_node, const int *wrt, int n_wrt, int *out_nodes);
+/* Mark `node` as a result to be written to `buf` (must hold the node's shape in floats). */
+VRHI_API int vrhi_graph_output(vrhi_graph g, int node, vrhi_buffer buf);
+VRHI_API int vrhi_graph_compile(vrhi_graph g);
+VRHI_API int vrhi_graph_launch(vrhi_graph g, vrhi_stream stream);
+/* Text plan of the compiled graph (one line per kernel); returns the needed length. */
+VRHI_API int vrhi_graph_describe(vrhi_graph g, char *out_text, size_t capacity, size_t *out_needed);
+VRHI_API int vrhi_graph_kernel_count(vrhi_graph g, int *out_count);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VRHI_H_ */

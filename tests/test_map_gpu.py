@@ -1,0 +1,153 @@
+"""GPU: fused map chain and the generic tape kernel against the binary64 CPU oracle."""
+import numpy as np
+import pytest
+
+import oracle
+from vernondsl_b200 import _lib as L
+from vernondsl_b200 import ops
+
+pytestmark = pytest.mark.gpu
+
+# Tolerance of the fused chain: within 2 ulp of the binary64-evaluated, once-rounded oracle, where
+# the ulp is taken at the largest intermediate magnitude of the chain (the result is a sum of two
+# terms that can cancel, so an ulp of the result itself is not a meaningful unit there).
+CHAIN_ULPS = 2.0
+
+
+def chain_inputs(n, seed=1001):
+    rng = np.random.default_rng(seed)
+    return (rng.uniform(-1, 1, n).astype(np.float32), rng.standard_normal(n).astype(np.float32),
+            rng.standard_normal(n).astype(np.float32))
+
+
+def check_chain(got, a, x, y):
+    want, scale = oracle.fused_map(a, x, y, want_scale=True)
+    unit = np.spacing(np.maximum(scale, np.abs(want)).astype(np.float32)).astype(np.float64)
+    err = np.abs(got.astype(np.float64) - want.astype(np.float64)) / unit
+    assert err.max() <= CHAIN_ULPS, f"max error {err.max():.2f} scaled ulp"
+    # and in plain ulps of the result, nearly everything is within 2 as well
+    plain = oracle.ulp_diff(got, want)
+    assert (plain <= 2).mean() > 0.99
+    return err.max(), plain.max()
+
+
+@pytest.mark.parametrize("n", [1, 3, 4, 5, 1023, 4099, 1 << 20, (1 << 22) + 3])
+def test_fused_map_matches_oracle(dev, stream, n):
+    a, x, y = chain_inputs(n)
+    A, X, Y = (dev.from_numpy(v) for v in (a, x, y))
+    out = dev.empty(n, np.float32)
+    ops.fused_map(stream, A, X, Y, out, n)
+    stream.check()
+    check_chain(out.download(), a, x, y)
+    for b in (A, X, Y, out):
+        b.close()
+
+
+def test_fused_map_golden(dev, stream, golden):
+    a, x, y = golden["map_a"], golden["map_x"], golden["map_y"]
+    A, X, Y = (dev.from_numpy(v) for v in (a, x, y))
+    out = dev.empty(a.size, np.float32)
+    ops.fused_map(stream, A, X, Y, out, a.size)
+    stream.check()
+    got = out.download()
+    unit = np.spacing(np.maximum(np.abs(golden["map_out"]), 1.0).astype(np.float32))
+    assert (np.abs(got - golden["map_out"]) <= 4 * unit).all()
+
+
+def test_fused_map_extreme_inputs(dev, stream):
+    x = np.array([0.0, -0.0, 1e-30, 30.0, -30.0, 8.0, 1e-4, -1e-4] * 4, dtype=np.float32)
+    a = np.linspace(-1, 1, x.size).astype(np.float32)
+    y = np.array([0.0, 1e-20, -5.0, 5.0, 1e3, -1e3, 0.5, -0.5] * 4, dtype=np.float32)
+    A, X, Y = (dev.from_numpy(v) for v in (a, x, y))
+    out = dev.empty(x.size, np.float32)
+    ops.fused_map(stream, A, X, Y, out, x.size)
+    stream.check()
+    got = out.download()
+    assert np.isfinite(got).all()
+    check_chain(got, a, x, y)
+
+
+def chain_tape():
+    t = ops.Tape(3)
+    a, x, y = t.input(0), t.input(1), t.input(2)
+    u = t.op("fma", a, x, y)
+    th = t.op("tanh", u)
+    e = t.op("exp", t.op("mul", t.op("mul", t.const(-0.5), x), x))
+    q = t.op("sqrt", t.op("add", t.op("abs", y), t.const(1e-3)))
+    t.output(t.op("fma", th, e, q))
+    return t
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 4096), (64, 1024), (7, 36), (5, 13), (1, 1)])
+def test_tape_runs_the_same_chain(dev, stream, rows, cols):
+    n = rows * cols
+    a, x, y = chain_inputs(n, seed=7)
+    A, X, Y = (dev.from_numpy(v) for v in (a, x, y))
+    out = dev.empty(n, np.float32)
+    ops.map_tape(stream, chain_tape(), [A, X, Y], [out], rows, cols)
+    stream.check()
+    check_chain(out.download(), a, x, y)
+
+
+UNARY_RANGES = {"tanh": (-12, 12), "exp": (-80, 80), "sqrt": (0, 1e6), "abs": (-5, 5), "neg": (-5, 5), "square": (-1e3, 1e3),
+                "recip": (0.01, 100), "log": (1e-6, 1e6), "sigmoid": (-30, 30), "relu": (-5, 5), "cos": (-20, 20),
+                "sin": (-20, 20), "rsqrt": (1e-4, 1e4)}
+
+
+@pytest.mark.parametrize("op", sorted(UNARY_RANGES))
+def test_tape_primitives_within_2_ulp(dev, stream, op):
+    lo, hi = UNARY_RANGES[op]
+    rng = np.random.default_rng(11)
+    x = rng.uniform(lo, hi, 1 << 16).astype(np.float32)
+    if op in ("tanh", "sigmoid", "exp"):
+        x[:4096] = rng.uniform(-1e-3, 1e-3, 4096).astype(np.float32)  # near zero, where relative accuracy is hardest
+    X = dev.from_numpy(x)
+    out = dev.empty(x.size, np.float32)
+    t = ops.Tape(1)
+    t.output(t.op(op, t.input(0)))
+    ops.map_tape(stream, t, [X], [out], 1, x.size)
+    stream.check()
+    got, want = out.download(), oracle.unary(op, x)
+    ok = np.isfinite(want) & (np.abs(want) > 1e-37)
+    # cos/sin: error measured against the function's scale near its zeros, as libm accuracy tables do
+    err = oracle.ulp_diff(got[ok], want[ok]) if op not in ("cos", "sin") else \
+        np.abs(got[ok].astype(np.float64) - want[ok]) / np.spacing(np.maximum(np.abs(want[ok]), np.float32(0.25)))
+    assert err.max() <= 2.0, f"{op}: {err.max():.2f} ulp"
+
+
+def test_tape_broadcasts_and_multiple_outputs(dev, stream):
+    rows, cols = 37, 256
+    rng = np.random.default_rng(3)
+    m = rng.standard_normal((rows, cols)).astype(np.float32)
+    rv = rng.standard_normal(cols).astype(np.float32)
+    cv = rng.standard_normal(rows).astype(np.float32)
+    sc = np.array([1.75], dtype=np.float32)
+    for cols_used in (cols, 255):  # vector path and scalar path
+        mm = np.ascontiguousarray(m[:, :cols_used])
+        rr = np.ascontiguousarray(rv[:cols_used])
+        M, RV, CV, SC = dev.from_numpy(mm), dev.from_numpy(rr), dev.from_numpy(cv), dev.from_numpy(sc)
+        o1, o2 = dev.empty(mm.shape, np.float32), dev.empty(mm.shape, np.float32)
+        t = ops.Tape(4, row_vectors=[1], col_vectors=[2], scalars=[3])
+        s = t.op("add", t.op("mul", t.input(0), t.input(1)), t.input(2))
+        t.output(s)
+        t.output(t.op("mul", t.op("max", s, t.const(0.0)), t.input(3)))
+        ops.map_tape(stream, t, [M, RV, CV, SC], [o1, o2], rows, cols_used)
+        stream.check()
+        want1 = (mm * rr[None, :]).astype(np.float32) + cv[:, None]
+        assert np.array_equal(o1.download(), want1)
+        assert np.array_equal(o2.download(), np.maximum(want1, 0) * sc[0])
+
+
+def test_tape_errors(dev, stream):
+    X = dev.from_numpy(np.zeros(64, np.float32))
+    out = dev.empty(64, np.float32)
+    t = ops.Tape(1)
+    t.output(t.op("add", t.input(0), 5))  # value 5 is not defined yet
+    with pytest.raises(L.VrhiError) as e:
+        ops.map_tape(stream, t, [X], [out], 1, 64)
+    assert e.value.status == L.ERR_INVALID
+    t = ops.Tape(1)
+    t.output(t.op("neg", t.input(0)))
+    with pytest.raises(L.VrhiError) as e:
+        ops.map_tape(stream, t, [X], [out], 2, 64)  # 128 elements do not fit
+    assert e.value.status == L.ERR_SIZE

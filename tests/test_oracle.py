@@ -1,0 +1,120 @@
+"""CPU: the oracle against its golden fixtures, against the independent numpy restatement, and
+against closed-form cases.  The reference pins nothing for this path (no tests, no vectors), so
+these are the pins the GPU parity tests stand on."""
+import numpy as np
+import pytest
+
+import oracle
+from oracle import numpy_restatement as nr
+from tests.golden.make_golden import WORKLOADS, workload_image
+
+
+@pytest.mark.parametrize("name", ["mandelbrot_1080p", "julia_512", "mandelbrot_ragged"])
+def test_escape_matches_golden_digest(golden, name):
+    img, total = workload_image(name)
+    s, w = oracle.digest_u32(img)
+    assert [s, w] == [int(v) for v in golden[f"{name}_digest"]]
+    assert s == total
+    if f"{name}_counts" in golden:
+        assert np.array_equal(img, golden[f"{name}_counts"].astype(np.uint32))
+    else:
+        rows = golden[f"{name}_rows"]
+        assert np.array_equal(img[rows], golden[f"{name}_row_counts"].astype(np.uint32))
+
+
+def test_escape_julia_16k_rows_match_golden(golden):
+    kind, W, H, x0, x1, y0, y1, cr, ci, mi = WORKLOADS["julia_16k"]
+    dx, dy = oracle.grid_steps(x0, x1, y0, y1, W, H)
+    rows = golden["julia_16k_rows"]
+    for k, r in enumerate(rows):
+        img, _ = oracle.escape_time(kind, W, H, x0, y0, dx, dy, cr, ci, mi, row_begin=int(r), row_step=1, row_count=1)
+        assert np.array_equal(img[0], golden["julia_16k_row_counts"][k].astype(np.uint32))
+
+
+@pytest.mark.parametrize("name,stride", [("mandelbrot_1080p", 37), ("julia_512", 5), ("mandelbrot_ragged", 1)])
+def test_escape_c_equals_numpy_restatement(name, stride):
+    kind, W, H, x0, x1, y0, y1, cr, ci, mi = WORKLOADS[name]
+    dx, dy = oracle.grid_steps(x0, x1, y0, y1, W, H)
+    rows = np.arange(0, H, stride)
+    c_img, _ = oracle.escape_time(kind, W, H, x0, y0, dx, dy, cr, ci, mi, row_begin=0, row_step=stride)
+    n_img = nr.escape_time(kind, W, H, x0, y0, dx, dy, cr, ci, mi, rows=rows)
+    assert np.array_equal(c_img, n_img)
+
+
+def test_escape_closed_form_points():
+    # c = 0 never escapes; |c| > 2 escapes after exactly one update (test-before-update rule:
+    # z0 = 0 passes the first test, z1 = c fails the second), fractal.py:21-24.
+    one = lambda x, y, mi=50: int(oracle.escape_time(oracle.MANDELBROT, 1, 1, x, y, 0.0, 0.0, max_iter=mi)[0][0, 0])
+    assert one(0.0, 0.0) == 50
+    assert one(3.0, 0.0) == 1
+    assert one(0.0, -2.5) == 1
+    assert one(-1.0, 0.0) == 50          # period-2 point of the set
+    assert one(0.25, 0.0, 1000) == 1000  # cusp, in the set
+    assert one(0.0, 0.0, 0) == 0         # max_iter = 0: no update is ever made
+    # Julia: a start outside radius 2 fails the very first test
+    j = oracle.escape_time(oracle.JULIA, 1, 1, 2.5, 0.0, 0.0, 0.0, cr=-0.8, ci=0.156, max_iter=100)[0]
+    assert int(j[0, 0]) == 0
+
+
+def test_escape_norm_test_and_colour_follow_fractal_py():
+    # fractal.py:22 `while z.norm() < 20 and iterations < 50`, :25 colour = 1 - iterations*0.02
+    n = 16
+    dx = np.float32(2.0 / n)
+    img, _ = oracle.escape_time(oracle.JULIA, 2 * n, n, -2.0, -1.0, dx, dx, cr=-0.8, ci=0.2, max_iter=50,
+                                test=oracle.TEST_NORM_GE, bound=20.0)
+    ref = nr.escape_time(1, 2 * n, n, -2.0, -1.0, dx, dx, cr=-0.8, ci=0.2, max_iter=50, test=1, bound=20.0)
+    assert np.array_equal(img, ref)
+    col = oracle.escape_color(img, 0.02)
+    assert np.array_equal(col, (np.float32(1.0) - img.astype(np.float32) * np.float32(0.02)).astype(np.float32))
+    assert col.min() >= -1e-6 and col.max() <= 1.0
+
+
+def test_float_ops_match_golden_and_numpy(golden):
+    out = oracle.fused_map(golden["map_a"], golden["map_x"], golden["map_y"])
+    assert np.array_equal(out, golden["map_out"])
+    assert oracle.ulp_diff(nr.fused_map(golden["map_a"], golden["map_x"], golden["map_y"]), out).max() <= 1
+    m = golden["rows_in"]
+    assert np.array_equal(oracle.row_sum(m), golden["rows_sum"])
+    assert np.array_equal(oracle.row_max(m), golden["rows_max"])
+    assert np.array_equal(oracle.row_softmax(m), golden["rows_softmax"])
+    assert oracle.ulp_diff(nr.row_softmax(m), golden["rows_softmax"]).max() <= 1
+    assert np.allclose(oracle.row_softmax(m).astype(np.float64).sum(axis=1), 1.0, atol=1e-6)
+    assert np.allclose(oracle.col_sum(m), m.astype(np.float64).sum(axis=0), rtol=1e-6)
+
+
+def test_mse_matches_golden_numpy_and_finite_differences(golden):
+    W, x, b, t = golden["mse_W"], golden["mse_x"], golden["mse_b"], golden["mse_t"]
+    loss = oracle.mse_tanh_fwd(W, x, b, t)
+    dW, dx, db = oracle.mse_tanh_bwd(W, x, b, t)
+    assert loss == pytest.approx(float(golden["mse_loss"][0]), rel=1e-14)
+    assert np.array_equal(dW, golden["mse_dW"]) and np.array_equal(dx, golden["mse_dx"])
+    assert np.allclose(db, golden["mse_db"], rtol=1e-13, atol=0)
+    nl, ndW, ndx, ndb = nr.mse_tanh(W, x, b, t)
+    assert loss == pytest.approx(nl, rel=1e-12)
+    assert np.allclose(dW, ndW, rtol=1e-6, atol=1e-12) and np.allclose(dx, ndx, rtol=1e-6, atol=1e-12)
+    assert np.allclose(db, ndb, rtol=1e-10)
+    # central finite differences in binary64 on a few coordinates
+    f = lambda W_, b_: nr.mse_tanh(W_, x, b_, t)[0]
+    eps = 1e-3
+    for (r, c) in [(0, 0), (5, 17), (12, 35)]:
+        Wp, Wm = W.astype(np.float64).copy(), W.astype(np.float64).copy()
+        Wp[r, c] += eps
+        Wm[r, c] -= eps
+        # numpy restatement promotes float32 inputs; feed float64 perturbed copies through its formula directly
+        y = lambda Wv: (np.tanh(Wv * x.astype(np.float64) + b.astype(np.float64)[None, :]) - t.astype(np.float64))
+        fd = ((y(Wp) ** 2).sum() - (y(Wm) ** 2).sum()) / W.size / (2 * eps)
+        assert fd == pytest.approx(float(ndW[r, c]), rel=1e-4, abs=1e-9)
+    bp, bm = b.astype(np.float64).copy(), b.astype(np.float64).copy()
+    bp[3] += eps
+    bm[3] -= eps
+    yb = lambda bv: (np.tanh(W.astype(np.float64) * x.astype(np.float64) + bv[None, :]) - t.astype(np.float64))
+    fd = ((yb(bp) ** 2).sum() - (yb(bm) ** 2).sum()) / W.size / (2 * eps)
+    assert fd == pytest.approx(float(ndb[3]), rel=1e-4)
+    del f
+
+
+def test_row_sharded_loss_adds_up(golden):
+    W, x, b, t = golden["mse_W"], golden["mse_x"], golden["mse_b"], golden["mse_t"]
+    denom = W.size
+    parts = [oracle.mse_tanh_fwd(W[:6], x[:6], b, t[:6], denom), oracle.mse_tanh_fwd(W[6:], x[6:], b, t[6:], denom)]
+    assert sum(parts) == pytest.approx(oracle.mse_tanh_fwd(W, x, b, t), rel=1e-13)

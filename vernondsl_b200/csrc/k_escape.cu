@@ -1,0 +1,224 @@
+// Escape-time map kernels (Mandelbrot / Julia), sm_100a.
+//
+// Loop rules follow fractal.py:18-25: every pixel is independent, the escape test comes before
+// the update, the result counts the updates performed; the square is (z0*z0 - z1*z1, (z1*z0)*2)
+// (fractal.py:11-13); coordinates come from the integer index at the pixel corner
+// (fractal.py:20).
+//
+// EXACT mode reproduces these binary32 roundings and no others:
+//     a = zr*zr; b = zi*zi; s = a+b; t = zr*zi; zi' = (t+t)+ci; zr' = (a-b)+cr
+// (t+t)+ci is issued as fma(2, t, ci): 2*t is exact in binary32, so the fused form rounds the
+// same real number once and gives the same bits with one instruction fewer.  Everything else uses
+// __fmul_rn / __fadd_rn, which the compiler never contracts.
+//
+// This file holds the fully checked kernel: one pixel per lane, a test on every step.  It accepts
+// every parameter combination and is the path of record for parameters the regrouping kernel
+// cannot take.
+#include <cstring>
+
+#include "vrhi_internal.h"
+
+namespace vrhi {
+
+struct EscapeDev {
+  uint32_t width, height, max_iter;
+  float x0, y0, dx, dy, cr, ci, bound, color_scale;
+  uint32_t chunk_rows, chunk_first, chunk_step;
+  uint32_t rows_owned;       // rows this launch computes
+  uint32_t tiles_per_row;    // ceil(width / 32)
+  uint32_t batch_tiles;      // tiles per stolen batch (a batch never straddles a row)
+  uint32_t batches_per_row;
+  uint32_t n_batches;
+};
+
+template <int MODE>
+__device__ __forceinline__ void escape_step(float &zr, float &zi, float a, float b, float cr, float ci) {
+  if (MODE == VRHI_ESCAPE_EXACT) {
+    float t = __fmul_rn(zr, zi);
+    zi = __fmaf_rn(2.0f, t, ci);
+    zr = __fadd_rn(__fsub_rn(a, b), cr);
+  } else {
+    // contracted: fewer roundings, not bit-identical to the exact order
+    float t = zr + zr;
+    zi = fmaf(t, zi, ci);
+    zr = (a - b) + cr;
+  }
+}
+
+template <int TEST>
+__device__ __forceinline__ bool escaped(float s, float bound) {
+  if (TEST == VRHI_TEST_NORM2_GT) return !(s <= bound);  // NaN counts as escaped; s > bound otherwise
+  return !(__fsqrt_rn(s) < bound);
+}
+
+template <int OUT>
+__device__ __forceinline__ void store_count(void *image, size_t pix, uint32_t count, float color_scale) {
+  if (OUT == VRHI_OUT_COUNT_U32)
+    static_cast<uint32_t *>(image)[pix] = count;
+  else if (OUT == VRHI_OUT_COUNT_U16)
+    static_cast<uint16_t *>(image)[pix] = (uint16_t)count;
+  else
+    static_cast<float *>(image)[pix] = __fsub_rn(1.0f, __fmul_rn((float)count, color_scale));
+}
+
+// Row of the image that owned row r maps to (rows are owned in chunks dealt round-robin).
+__device__ __forceinline__ uint32_t owned_row_to_image_row(const EscapeDev &p, uint32_t r) {
+  uint32_t k = r / p.chunk_rows;
+  return (p.chunk_first + k * p.chunk_step) * p.chunk_rows + (r - k * p.chunk_rows);
+}
+
+template <int KIND, int MODE, int TEST, int OUT>
+__global__ void __launch_bounds__(256) escape_checked_kernel(EscapeDev p, void *image, uint32_t *work_counter) {
+  const uint32_t lane = threadIdx.x & 31u;
+  for (;;) {
+    uint32_t batch = 0;
+    if (lane == 0) batch = atomicAdd(work_counter, 1u);
+    batch = __shfl_sync(0xffffffffu, batch, 0);
+    if (batch >= p.n_batches) break;
+    const uint32_t r = batch / p.batches_per_row;
+    const uint32_t tile0 = (batch - r * p.batches_per_row) * p.batch_tiles;
+    const uint32_t tile1 = min(tile0 + p.batch_tiles, p.tiles_per_row);
+    const uint32_t j = owned_row_to_image_row(p, r);
+    const float y = __fadd_rn(p.y0, __fmul_rn((float)j, p.dy));
+    const size_t row_base = (size_t)j * p.width;
+    for (uint32_t tile = tile0; tile < tile1; ++tile) {
+      const uint32_t i = tile * 32u + lane;
+      if (i >= p.width) continue;
+      const float x = __fadd_rn(p.x0, __fmul_rn((float)i, p.dx));
+      float zr, zi, cr, ci;
+      if (KIND == VRHI_ESCAPE_MANDELBROT) {
+        zr = 0.f; zi = 0.f; cr = x; ci = y;
+      } else {
+        zr = x; zi = y; cr = p.cr; ci = p.ci;
+      }
+      uint32_t count = 0;
+      for (;;) {
+        float a, b, s;
+        if (MODE == VRHI_ESCAPE_EXACT) {
+          a = __fmul_rn(zr, zr);
+          b = __fmul_rn(zi, zi);
+          s = __fadd_rn(a, b);
+        } else {
+          a = zr * zr;
+          b = zi * zi;
+          s = fmaf(zi, zi, a);
+        }
+        if (escaped<TEST>(s, p.bound) || count >= p.max_iter) break;
+        escape_step<MODE>(zr, zi, a, b, cr, ci);
+        ++count;
+      }
+      store_count<OUT>(image, row_base + i, count, p.color_scale);
+    }
+  }
+}
+
+template <int KIND, int MODE, int TEST>
+static void launch_checked_out(int out, int grid, cudaStream_t s, const EscapeDev &p, void *image, uint32_t *ctr) {
+  switch (out) {
+    case VRHI_OUT_COUNT_U32: escape_checked_kernel<KIND, MODE, TEST, VRHI_OUT_COUNT_U32><<<grid, 256, 0, s>>>(p, image, ctr); break;
+    case VRHI_OUT_COUNT_U16: escape_checked_kernel<KIND, MODE, TEST, VRHI_OUT_COUNT_U16><<<grid, 256, 0, s>>>(p, image, ctr); break;
+    default: escape_checked_kernel<KIND, MODE, TEST, VRHI_OUT_COLOR_F32><<<grid, 256, 0, s>>>(p, image, ctr); break;
+  }
+}
+
+template <int KIND, int MODE>
+static void launch_checked_test(int test, int out, int grid, cudaStream_t s, const EscapeDev &p, void *image, uint32_t *ctr) {
+  if (test == VRHI_TEST_NORM2_GT)
+    launch_checked_out<KIND, MODE, VRHI_TEST_NORM2_GT>(out, grid, s, p, image, ctr);
+  else
+    launch_checked_out<KIND, MODE, VRHI_TEST_NORM_GE>(out, grid, s, p, image, ctr);
+}
+
+int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const void *params, size_t params_size) {
+  vrhi_escape_params q;
+  VRHI_TRY(read_params(params, params_size, &q));
+  if (n_args != 1) return fail(VRHI_ERR_INVALID, "escape_time takes 1 argument (the image), got %d", n_args);
+  if (!writable(args[0])) return fail(VRHI_ERR_INVALID, "escape_time: the image buffer is read-only (class %s)", vrhi_arg_class_name(args[0].buf_cls));
+  if (q.kind > VRHI_ESCAPE_JULIA || q.mode > VRHI_ESCAPE_FAST || q.test > VRHI_TEST_NORM_GE || q.output > VRHI_OUT_COLOR_F32)
+    return fail(VRHI_ERR_INVALID, "escape_time: kind/mode/test/output out of range");
+  if (q.width == 0 || q.height == 0) return fail(VRHI_ERR_SIZE, "escape_time: empty image");
+  if (q.output == VRHI_OUT_COUNT_U16 && q.max_iter > 65535u) return fail(VRHI_ERR_UNSUPPORTED, "escape_time: uint16 counts need max_iter <= 65535");
+  if (q.max_iter > (1u << 24) && q.output == VRHI_OUT_COLOR_F32) return fail(VRHI_ERR_UNSUPPORTED, "escape_time: colour output needs max_iter <= 2^24");
+  const size_t elem = q.output == VRHI_OUT_COUNT_U16 ? 2 : 4;
+  const uint64_t need = (uint64_t)q.width * q.height * elem;
+  if (args[0].bytes < need) return fail(VRHI_ERR_SIZE, "escape_time: image view holds %llu bytes, %llu needed", (unsigned long long)args[0].bytes, (unsigned long long)need);
+
+  EscapeDev p{};
+  p.width = q.width; p.height = q.height; p.max_iter = q.max_iter;
+  p.x0 = q.x0; p.y0 = q.y0; p.dx = q.dx; p.dy = q.dy; p.cr = q.cr; p.ci = q.ci;
+  p.bound = q.bound; p.color_scale = q.color_scale;
+  if (q.chunk_rows == 0) {
+    p.chunk_rows = q.height; p.chunk_first = 0; p.chunk_step = 1; p.rows_owned = q.height;
+  } else {
+    if (q.chunk_step == 0) return fail(VRHI_ERR_INVALID, "escape_time: chunk_step must be >= 1");
+    p.chunk_rows = q.chunk_rows; p.chunk_first = q.chunk_first; p.chunk_step = q.chunk_step;
+    uint64_t rows = 0;
+    for (uint32_t k = 0; k < q.chunk_count; ++k) {
+      uint64_t c = (uint64_t)q.chunk_first + (uint64_t)k * q.chunk_step;
+      uint64_t r0 = c * q.chunk_rows;
+      if (r0 >= q.height) return fail(VRHI_ERR_SIZE, "escape_time: chunk %llu starts beyond the image", (unsigned long long)c);
+      uint64_t r1 = r0 + q.chunk_rows;
+      if (r1 > q.height) {
+        if (k + 1 != q.chunk_count) return fail(VRHI_ERR_SIZE, "escape_time: only the last chunk may be short");
+        r1 = q.height;
+      }
+      rows += r1 - r0;
+    }
+    p.rows_owned = (uint32_t)rows;
+  }
+  if (p.rows_owned == 0) return VRHI_OK;  // an empty band is not an error
+  p.tiles_per_row = (q.width + 31u) / 32u;
+  p.batch_tiles = 16;
+  p.batches_per_row = (p.tiles_per_row + p.batch_tiles - 1) / p.batch_tiles;
+  uint64_t nb = (uint64_t)p.batches_per_row * p.rows_owned;
+  if (nb > 0xfffffff0ull) return fail(VRHI_ERR_UNSUPPORTED, "escape_time: image too large for 32-bit batch indices");
+  p.n_batches = (uint32_t)nb;
+
+  uint32_t *ctrl = nullptr;
+  VRHI_TRY(stream_arena(st, 0, &ctrl, nullptr));
+  uint32_t *counter = ctrl + CTRL_WORK0;
+  VRHI_CUDA(cudaMemsetAsync(counter, 0, sizeof(uint32_t), st->s));
+  const int sms = st->dev->prop.multiProcessorCount;
+  uint64_t warps_needed = nb;
+  int grid = (int)((warps_needed + 7) / 8 < (uint64_t)sms * 8 ? (warps_needed + 7) / 8 : (uint64_t)sms * 8);
+  if (q.kind == VRHI_ESCAPE_MANDELBROT) {
+    if (q.mode == VRHI_ESCAPE_EXACT) launch_checked_test<VRHI_ESCAPE_MANDELBROT, VRHI_ESCAPE_EXACT>(q.test, q.output, grid, st->s, p, args[0].ptr, counter);
+    else launch_checked_test<VRHI_ESCAPE_MANDELBROT, VRHI_ESCAPE_FAST>(q.test, q.output, grid, st->s, p, args[0].ptr, counter);
+  } else {
+    if (q.mode == VRHI_ESCAPE_EXACT) launch_checked_test<VRHI_ESCAPE_JULIA, VRHI_ESCAPE_EXACT>(q.test, q.output, grid, st->s, p, args[0].ptr, counter);
+    else launch_checked_test<VRHI_ESCAPE_JULIA, VRHI_ESCAPE_FAST>(q.test, q.output, grid, st->s, p, args[0].ptr, counter);
+  }
+  return post_launch(st, "escape_time");
+}
+
+// ---------------------------------------------------------------------------------------------
+// FP32 issue-rate probe: independent FFMA chains, 8 per thread, nothing else in the loop body.
+__global__ void __launch_bounds__(256) fp32_probe_kernel(float *out, uint64_t iters, float seed) {
+  float v0 = seed + threadIdx.x, v1 = v0 + 1.f, v2 = v0 + 2.f, v3 = v0 + 3.f;
+  float v4 = v0 + 4.f, v5 = v0 + 5.f, v6 = v0 + 6.f, v7 = v0 + 7.f;
+  const float m = 0.999f, c = 0.001f;
+  for (uint64_t k = 0; k < iters; ++k) {
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      v0 = fmaf(v0, m, c); v1 = fmaf(v1, m, c); v2 = fmaf(v2, m, c); v3 = fmaf(v3, m, c);
+      v4 = fmaf(v4, m, c); v5 = fmaf(v5, m, c); v6 = fmaf(v6, m, c); v7 = fmaf(v7, m, c);
+    }
+  }
+  float r = ((v0 + v1) + (v2 + v3)) + ((v4 + v5) + (v6 + v7));
+  if (r == 12345.678f) out[0] = r;  // keeps the chains alive without memory traffic
+}
+
+int launch_fp32_probe(vrhi_stream_t *st, const ArgView *args, int n_args, const void *params, size_t params_size) {
+  vrhi_probe_params q;
+  VRHI_TRY(read_params(params, params_size, &q));
+  if (n_args != 1 || args[0].bytes < 4 || !writable(args[0])) return fail(VRHI_ERR_INVALID, "fp32_probe takes one writable argument of at least 4 bytes");
+  const int sms = st->dev->prop.multiProcessorCount;
+  uint64_t threads = q.threads ? q.threads : (uint64_t)sms * 2048;
+  uint64_t blocks = (threads + 255) / 256;
+  if (blocks == 0 || blocks > 0x7fffffffull) return fail(VRHI_ERR_SIZE, "fp32_probe: thread count out of range");
+  uint64_t iters = q.ffma_per_thread / 64;  // 64 FFMAs per loop trip
+  fp32_probe_kernel<<<(unsigned)blocks, 256, 0, st->s>>>(reinterpret_cast<float *>(args[0].ptr), iters, 1.0f);
+  return post_launch(st, "fp32_probe");
+}
+
+}  // namespace vrhi

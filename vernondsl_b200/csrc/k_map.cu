@@ -1,0 +1,339 @@
+// Per-element map kernels, sm_100a: the specialised fused chain of the map workload, and a
+// generic fused-tape kernel that runs any chain of elementwise operations in one pass.
+//
+// Both are HBM-bound by design: 128-bit streaming loads and stores, grid sized to a multiple of
+// the SM count, several independent loads in flight per thread.  The reference project has no
+// counterpart; the chain's formula is the workload definition
+//     out = tanh(a*x + y) * exp(-0.5*x*x) + sqrt(|y| + 1e-3).
+#include <cstring>
+
+#include "vrhi_internal.h"
+
+namespace vrhi {
+
+__device__ __forceinline__ float4 ld_stream(const float4 *p) { return __ldcs(p); }
+__device__ __forceinline__ void st_stream(float4 *p, float4 v) { __stcs(p, v); }
+
+__device__ __forceinline__ float chain_one(float a, float x, float y) {
+  float u = fmaf(a, x, y);
+  float th = tanhf(u);
+  float e = expf(-0.5f * x * x);
+  float q = sqrtf(fabsf(y) + 1e-3f);
+  return fmaf(th, e, q);
+}
+
+__device__ __forceinline__ float4 chain_four(float4 a, float4 x, float4 y) {
+  return make_float4(chain_one(a.x, x.x, y.x), chain_one(a.y, x.y, y.y), chain_one(a.z, x.z, y.z),
+                     chain_one(a.w, x.w, y.w));
+}
+
+// Each thread owns UNROLL float4 groups per trip, strided by the grid so that every warp's
+// accesses stay contiguous.
+template <int UNROLL>
+__global__ void __launch_bounds__(256) fused_map_kernel(const float4 *__restrict__ a, const float4 *__restrict__ x,
+                                                        const float4 *__restrict__ y, float4 *__restrict__ out,
+                                                        uint64_t n4, uint64_t n, const float *a1, const float *x1,
+                                                        const float *y1, float *o1) {
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  uint64_t k = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; k + (UNROLL - 1) * stride < n4; k += UNROLL * stride) {
+    float4 va[UNROLL], vx[UNROLL], vy[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      va[u] = ld_stream(a + k + u * stride);
+      vx[u] = ld_stream(x + k + u * stride);
+      vy[u] = ld_stream(y + k + u * stride);
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) st_stream(out + k + u * stride, chain_four(va[u], vx[u], vy[u]));
+  }
+  for (; k < n4; k += stride) st_stream(out + k, chain_four(ld_stream(a + k), ld_stream(x + k), ld_stream(y + k)));
+  // ragged tail (n not a multiple of 4): at most 3 elements, first block only
+  if (blockIdx.x == 0 && threadIdx.x < (n & 3u)) {
+    uint64_t e = n4 * 4 + threadIdx.x;
+    o1[e] = chain_one(a1[e], x1[e], y1[e]);
+  }
+}
+
+int launch_fused_map(vrhi_stream_t *st, const ArgView *args, int n_args, const void *params, size_t params_size) {
+  vrhi_map_params q;
+  VRHI_TRY(read_params(params, params_size, &q));
+  if (n_args != 4) return fail(VRHI_ERR_INVALID, "fused_map takes 4 arguments (a, x, y, out), got %d", n_args);
+  if (q.n == 0) return VRHI_OK;
+  for (int k = 0; k < 4; ++k)
+    if (args[k].bytes < q.n * 4) return fail(VRHI_ERR_SIZE, "fused_map: argument %d holds %llu bytes, %llu needed", k, (unsigned long long)args[k].bytes, (unsigned long long)q.n * 4);
+  if (!writable(args[3])) return fail(VRHI_ERR_INVALID, "fused_map: output buffer is read-only (class %s)", vrhi_arg_class_name(args[3].buf_cls));
+  const uint64_t n4 = q.n / 4;
+  const int sms = st->dev->prop.multiProcessorCount;
+  uint64_t want = (n4 + 255) / 256;
+  uint64_t cap = (uint64_t)sms * 8;
+  unsigned grid = (unsigned)(want < cap ? (want ? want : 1) : cap);
+  fused_map_kernel<2><<<grid, 256, 0, st->s>>>(
+      (const float4 *)args[0].ptr, (const float4 *)args[1].ptr, (const float4 *)args[2].ptr, (float4 *)args[3].ptr, n4, q.n,
+      (const float *)args[0].ptr, (const float *)args[1].ptr, (const float *)args[2].ptr, (float *)args[3].ptr);
+  return post_launch(st, "fused_map");
+}
+
+// ---------------------------------------------------------------------------------------------
+// Generic fused tape.  The caller's tape is in SSA form (instruction t defines value
+// n_inputs + t).  The host assigns each value a physical slot by a linear scan over live ranges;
+// the kernel keeps one float4 per slot per thread in shared memory ([slot][thread], conflict
+// free) and walks the tape once per group of four elements.  Every branch on the opcode is
+// uniform across the CTA, so there is no divergence; the decode cost is hidden while the kernel
+// waits on HBM for short chains and shows as instruction pressure for long ones.
+
+constexpr int kTapeThreads = 128;
+constexpr int kTapeMaxSlots = 24;  // 24 slots * 128 threads * 16 B = 48 KiB, the default dynamic limit
+
+struct TapeInstrDev {
+  uint8_t op, dst, a, b, c, pad[3];
+  float imm;
+};
+
+struct TapeDev {
+  uint32_t n_inputs, n_outputs, n_instr, n_slots;
+  uint32_t row_vector_mask, col_vector_mask, scalar_mask;
+  uint8_t in_slot[VRHI_TAPE_MAX_INPUTS];
+  uint8_t out_slot[VRHI_TAPE_MAX_OUTPUTS];
+  TapeInstrDev instr[VRHI_TAPE_MAX_INSTR];
+  const float *in[VRHI_TAPE_MAX_INPUTS];
+  float *out[VRHI_TAPE_MAX_OUTPUTS];
+  uint64_t rows, cols;
+};
+
+#define TAPE_U(EXPR)                                                        \
+  do {                                                                      \
+    { const float a = va.x; res.x = (EXPR); } { const float a = va.y; res.y = (EXPR); } \
+    { const float a = va.z; res.z = (EXPR); } { const float a = va.w; res.w = (EXPR); } \
+  } while (0)
+#define TAPE_B(EXPR)                                                        \
+  do {                                                                      \
+    { const float a = va.x, b = vb.x; res.x = (EXPR); } { const float a = va.y, b = vb.y; res.y = (EXPR); } \
+    { const float a = va.z, b = vb.z; res.z = (EXPR); } { const float a = va.w, b = vb.w; res.w = (EXPR); } \
+  } while (0)
+
+// Executes the tape on the float4 group held in the slots of this thread.
+__device__ __forceinline__ void tape_run(const TapeDev &T, float4 *slots /* [slot][kTapeThreads] */) {
+  const int tid = threadIdx.x;
+  for (uint32_t t = 0; t < T.n_instr; ++t) {
+    const TapeInstrDev I = T.instr[t];
+    float4 va = slots[I.a * kTapeThreads + tid];
+    float4 vb = slots[I.b * kTapeThreads + tid];
+    float4 vc;
+    float4 res;
+    const float imm = I.imm;
+    switch (I.op) {
+      case VRHI_T_CONST: res = make_float4(imm, imm, imm, imm); break;
+      case VRHI_T_ADD: TAPE_B(a + b); break;
+      case VRHI_T_SUB: TAPE_B(a - b); break;
+      case VRHI_T_MUL: TAPE_B(a * b); break;
+      case VRHI_T_DIV: TAPE_B(a / b); break;
+      case VRHI_T_MAX: TAPE_B(fmaxf(a, b)); break;
+      case VRHI_T_MIN: TAPE_B(fminf(a, b)); break;
+      case VRHI_T_FMA: vc = slots[I.c * kTapeThreads + tid]; { res.x = fmaf(va.x, vb.x, vc.x); res.y = fmaf(va.y, vb.y, vc.y); res.z = fmaf(va.z, vb.z, vc.z); res.w = fmaf(va.w, vb.w, vc.w); }; break;
+      case VRHI_T_NEG: TAPE_U(-a); break;
+      case VRHI_T_ABS: TAPE_U(fabsf(a)); break;
+      case VRHI_T_SQUARE: TAPE_U(a * a); break;
+      case VRHI_T_SQRT: TAPE_U(sqrtf(a)); break;
+      case VRHI_T_RSQRT: TAPE_U(1.0f / sqrtf(a)); break;
+      case VRHI_T_RECIP: TAPE_U(1.0f / a); break;
+      case VRHI_T_EXP: TAPE_U(expf(a)); break;
+      case VRHI_T_LOG: TAPE_U(logf(a)); break;
+      case VRHI_T_TANH: TAPE_U(tanhf(a)); break;
+      case VRHI_T_SIGMOID: TAPE_U(1.0f / (1.0f + expf(-a))); break;
+      case VRHI_T_RELU: TAPE_U(fmaxf(a, 0.0f)); break;
+      case VRHI_T_COS: TAPE_U(cosf(a)); break;
+      case VRHI_T_SIN: TAPE_U(sinf(a)); break;
+      case VRHI_T_SIGN: TAPE_U((a > 0.f) ? 1.f : ((a < 0.f) ? -1.f : 0.f)); break;
+      case VRHI_T_STEP: TAPE_U(a > 0.f ? 1.f : 0.f); break;
+      case VRHI_T_EQ: TAPE_B(a == b ? 1.f : 0.f); break;
+      default: res = make_float4(0.f, 0.f, 0.f, 0.f); break;
+    }
+    slots[I.dst * kTapeThreads + tid] = res;
+  }
+}
+
+// Vector path: cols % 4 == 0.  blockIdx.x walks column groups of kTapeThreads float4s,
+// blockIdx.y strides over rows, so a broadcast row vector is loaded once per thread.
+__global__ void __launch_bounds__(kTapeThreads) map_tape_vec_kernel(const __grid_constant__ TapeDev T) {
+  extern __shared__ float4 slots[];
+  const int tid = threadIdx.x;
+  const uint64_t cols4 = T.cols / 4;
+  const uint64_t cg = (uint64_t)blockIdx.x * kTapeThreads + tid;
+  const bool in_range = cg < cols4;
+  float4 rowvec[VRHI_TAPE_MAX_INPUTS];
+#pragma unroll
+  for (int k = 0; k < VRHI_TAPE_MAX_INPUTS; ++k) {
+    rowvec[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (k < (int)T.n_inputs && ((T.row_vector_mask >> k) & 1u) && in_range)
+      rowvec[k] = reinterpret_cast<const float4 *>(T.in[k])[cg];
+    if (k < (int)T.n_inputs && ((T.scalar_mask >> k) & 1u)) {
+      const float s = T.in[k][0];
+      rowvec[k] = make_float4(s, s, s, s);
+    }
+  }
+  for (uint64_t r = blockIdx.y; r < T.rows; r += gridDim.y) {
+    const uint64_t e4 = r * cols4 + cg;
+#pragma unroll
+    for (int k = 0; k < VRHI_TAPE_MAX_INPUTS; ++k) {
+      if (k < (int)T.n_inputs) {
+        float4 v = rowvec[k];
+        if ((T.col_vector_mask >> k) & 1u) {
+          const float s = T.in[k][r];
+          v = make_float4(s, s, s, s);
+        } else if (!((T.row_vector_mask >> k) & 1u) && in_range) {
+          v = ld_stream(reinterpret_cast<const float4 *>(T.in[k]) + e4);
+        }
+        slots[T.in_slot[k] * kTapeThreads + tid] = v;
+      }
+    }
+    tape_run(T, slots);
+    if (in_range) {
+#pragma unroll
+      for (int k = 0; k < VRHI_TAPE_MAX_OUTPUTS; ++k)
+        if (k < (int)T.n_outputs) st_stream(reinterpret_cast<float4 *>(T.out[k]) + e4, slots[T.out_slot[k] * kTapeThreads + tid]);
+    }
+  }
+}
+
+// Scalar path for any shape: one element per thread per trip (lane .x of the float4 slot).
+__global__ void __launch_bounds__(kTapeThreads) map_tape_scalar_kernel(const __grid_constant__ TapeDev T) {
+  extern __shared__ float4 slots[];
+  const int tid = threadIdx.x;
+  const uint64_t n = T.rows * T.cols;
+  const uint64_t stride = (uint64_t)gridDim.x * kTapeThreads;
+  for (uint64_t base = (uint64_t)blockIdx.x * kTapeThreads; base < n; base += stride) {
+    const uint64_t e = base + tid;
+    const bool in_range = e < n;
+    const uint64_t col = in_range ? e % T.cols : 0;
+    for (uint32_t k = 0; k < T.n_inputs; ++k) {
+      float v = 0.f;
+      if (in_range) {
+        if ((T.row_vector_mask >> k) & 1u) v = T.in[k][col];
+        else if ((T.col_vector_mask >> k) & 1u) v = T.in[k][e / T.cols];
+        else if ((T.scalar_mask >> k) & 1u) v = T.in[k][0];
+        else v = T.in[k][e];
+      }
+      slots[T.in_slot[k] * kTapeThreads + tid] = make_float4(v, v, v, v);
+    }
+    tape_run(T, slots);
+    if (in_range)
+      for (uint32_t k = 0; k < T.n_outputs; ++k) T.out[k][e] = slots[T.out_slot[k] * kTapeThreads + tid].x;
+  }
+}
+
+static int tape_arity(int op) {
+  switch (op) {
+    case VRHI_T_CONST: return 0;
+    case VRHI_T_ADD: case VRHI_T_SUB: case VRHI_T_MUL: case VRHI_T_DIV: case VRHI_T_MAX: case VRHI_T_MIN: case VRHI_T_EQ: return 2;
+    case VRHI_T_FMA: return 3;
+    default: return 1;
+  }
+}
+
+// Linear-scan slot assignment: a value's slot is freed after its last use.
+static int assign_slots(const vrhi_tape_params &q, TapeDev *T) {
+  const uint32_t nv = q.n_inputs + q.n_instr;
+  int last_use[VRHI_TAPE_MAX_INPUTS + VRHI_TAPE_MAX_INSTR];
+  int slot_of[VRHI_TAPE_MAX_INPUTS + VRHI_TAPE_MAX_INSTR];
+  for (uint32_t v = 0; v < nv; ++v) { last_use[v] = -1; slot_of[v] = -1; }
+  for (uint32_t t = 0; t < q.n_instr; ++t) {
+    const vrhi_tape_instr &I = q.instr[t];
+    if (I.op >= VRHI_T_OPCOUNT) return fail(VRHI_ERR_INVALID, "map_tape: instruction %u has unknown opcode %u", t, I.op);
+    const int ar = tape_arity(I.op);
+    const uint16_t src[3] = {I.a, I.b, I.c};
+    for (int s = 0; s < ar; ++s) {
+      if (src[s] >= q.n_inputs + t) return fail(VRHI_ERR_INVALID, "map_tape: instruction %u reads value %u before it is defined", t, src[s]);
+      last_use[src[s]] = (int)t;
+    }
+  }
+  for (uint32_t k = 0; k < q.n_outputs; ++k) {
+    if (q.out_value[k] >= nv) return fail(VRHI_ERR_INVALID, "map_tape: output %u names value %u, which does not exist", k, q.out_value[k]);
+    last_use[q.out_value[k]] = (int)q.n_instr;  // live to the end
+  }
+  bool busy[kTapeMaxSlots] = {};
+  int n_slots = 0;
+  auto take = [&]() -> int {
+    for (int s = 0; s < kTapeMaxSlots; ++s)
+      if (!busy[s]) { busy[s] = true; if (s + 1 > n_slots) n_slots = s + 1; return s; }
+    return -1;
+  };
+  for (uint32_t k = 0; k < q.n_inputs; ++k) {
+    int s = take();
+    if (s < 0) return fail(VRHI_ERR_UNSUPPORTED, "map_tape: more than %d values live at once", kTapeMaxSlots);
+    slot_of[k] = s;
+    T->in_slot[k] = (uint8_t)s;
+  }
+  for (uint32_t t = 0; t < q.n_instr; ++t) {
+    const vrhi_tape_instr &I = q.instr[t];
+    const int ar = tape_arity(I.op);
+    const uint16_t src[3] = {I.a, I.b, I.c};
+    TapeInstrDev D{};
+    D.op = (uint8_t)I.op;
+    D.imm = I.imm;
+    uint8_t ss[3] = {0, 0, 0};
+    for (int s = 0; s < ar; ++s) ss[s] = (uint8_t)slot_of[src[s]];
+    D.a = ss[0]; D.b = ar >= 2 ? ss[1] : ss[0]; D.c = ar >= 3 ? ss[2] : ss[0];
+    // sources whose last use is this instruction release their slot before the result is placed
+    for (int s = 0; s < ar; ++s)
+      if (last_use[src[s]] == (int)t) busy[slot_of[src[s]]] = false;
+    int d = take();
+    if (d < 0) return fail(VRHI_ERR_UNSUPPORTED, "map_tape: more than %d values live at once", kTapeMaxSlots);
+    slot_of[q.n_inputs + t] = d;
+    D.dst = (uint8_t)d;
+    if (last_use[q.n_inputs + t] < 0) busy[d] = false;  // dead value
+    T->instr[t] = D;
+  }
+  for (uint32_t k = 0; k < q.n_outputs; ++k) T->out_slot[k] = (uint8_t)slot_of[q.out_value[k]];
+  T->n_slots = (uint32_t)n_slots;
+  return VRHI_OK;
+}
+
+int launch_map_tape(vrhi_stream_t *st, const ArgView *args, int n_args, const void *params, size_t params_size) {
+  vrhi_tape_params q;
+  VRHI_TRY(read_params(params, params_size, &q));
+  if (q.n_inputs > VRHI_TAPE_MAX_INPUTS || q.n_outputs == 0 || q.n_outputs > VRHI_TAPE_MAX_OUTPUTS || q.n_instr > VRHI_TAPE_MAX_INSTR)
+    return fail(VRHI_ERR_INVALID, "map_tape: %u inputs / %u outputs / %u instructions outside the limits (%d / 1..%d / %d)", q.n_inputs, q.n_outputs, q.n_instr, VRHI_TAPE_MAX_INPUTS, VRHI_TAPE_MAX_OUTPUTS, VRHI_TAPE_MAX_INSTR);
+  if (n_args != (int)(q.n_inputs + q.n_outputs)) return fail(VRHI_ERR_INVALID, "map_tape: %d arguments passed, tape declares %u inputs + %u outputs", n_args, q.n_inputs, q.n_outputs);
+  const uint64_t n = q.rows * q.cols;
+  if (n == 0) return VRHI_OK;
+  TapeDev T{};
+  T.n_inputs = q.n_inputs; T.n_outputs = q.n_outputs; T.n_instr = q.n_instr;
+  T.row_vector_mask = q.row_vector_mask; T.col_vector_mask = q.col_vector_mask; T.scalar_mask = q.scalar_mask;
+  T.rows = q.rows; T.cols = q.cols;
+  if ((q.row_vector_mask & q.col_vector_mask) | (q.row_vector_mask & q.scalar_mask) | (q.col_vector_mask & q.scalar_mask))
+    return fail(VRHI_ERR_INVALID, "map_tape: an input is marked with more than one broadcast shape");
+  VRHI_TRY(assign_slots(q, &T));
+  for (uint32_t k = 0; k < q.n_inputs; ++k) {
+    uint64_t need = ((q.row_vector_mask >> k) & 1u) ? q.cols * 4 : ((q.col_vector_mask >> k) & 1u) ? q.rows * 4 : ((q.scalar_mask >> k) & 1u) ? 4 : n * 4;
+    if (args[k].bytes < need) return fail(VRHI_ERR_SIZE, "map_tape: input %u holds %llu bytes, %llu needed", k, (unsigned long long)args[k].bytes, (unsigned long long)need);
+    T.in[k] = (const float *)args[k].ptr;
+  }
+  for (uint32_t k = 0; k < q.n_outputs; ++k) {
+    const ArgView &o = args[q.n_inputs + k];
+    if (o.bytes < n * 4) return fail(VRHI_ERR_SIZE, "map_tape: output %u holds %llu bytes, %llu needed", k, (unsigned long long)o.bytes, (unsigned long long)n * 4);
+    if (!writable(o)) return fail(VRHI_ERR_INVALID, "map_tape: output %u is read-only (class %s)", k, vrhi_arg_class_name(o.buf_cls));
+    T.out[k] = (float *)o.ptr;
+  }
+  const size_t smem = (size_t)(T.n_slots ? T.n_slots : 1) * kTapeThreads * sizeof(float4);
+  const int sms = st->dev->prop.multiProcessorCount;
+  if (q.cols % 4 == 0) {
+    uint64_t cols4 = q.cols / 4;
+    uint64_t gx = (cols4 + kTapeThreads - 1) / kTapeThreads;
+    if (gx > 0x7fffffffull) return fail(VRHI_ERR_UNSUPPORTED, "map_tape: too many columns");
+    uint64_t target = (uint64_t)sms * 8;
+    uint64_t gy = (target + gx - 1) / gx;
+    if (gy > q.rows) gy = q.rows;
+    if (gy > 65535) gy = 65535;
+    if (gy == 0) gy = 1;
+    dim3 grid((unsigned)gx, (unsigned)gy);
+    map_tape_vec_kernel<<<grid, kTapeThreads, smem, st->s>>>(T);
+  } else {
+    uint64_t want = (n + kTapeThreads - 1) / kTapeThreads;
+    uint64_t cap = (uint64_t)sms * 8;
+    map_tape_scalar_kernel<<<(unsigned)(want < cap ? want : cap), kTapeThreads, smem, st->s>>>(T);
+  }
+  return post_launch(st, "map_tape");
+}
+
+}  // namespace vrhi

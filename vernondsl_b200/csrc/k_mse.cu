@@ -1,0 +1,271 @@
+// loss = mean((tanh(W*x + b) - t)^2) over a row-major [rows][cols] problem with b a [cols] row
+// vector, and its hand-fused reverse-mode gradient, sm_100a.  HBM-bound.
+//
+// Backward recomputes the forward instead of reading a saved activation, which is the algorithmic
+// minimum of traffic: read W, x, t once, write dW, dx once (20 bytes per element).  A thread owns
+// four adjacent columns and walks down a fixed set of rows, so b is loaded once per thread and the
+// column sums for db accumulate in registers in a fixed order; one partial row per row group is
+// then added up by a second tiny kernel.  No float atomics anywhere: reruns are bit-identical.
+// The reference project has no counterpart for these operators.
+//
+// Numerics: with E = exp(-2|u|), tanh(u) = sign(u)*(1-E)/(1+E) and 1 - tanh(u)^2 = 4E/(1+E)^2.
+// The second form has no cancellation, so the gradient keeps its relative accuracy where tanh
+// saturates (1 - y*y evaluated from a rounded y loses it).
+#include <cstring>
+
+#include "vrhi_internal.h"
+
+namespace vrhi {
+
+int col_finalize(vrhi_stream_t *st, const float *partial, float *out, uint32_t groups, uint64_t cols, float scale);
+
+struct TanhPair {
+  float y;      // tanh(u)
+  float sech2;  // 1 - tanh(u)^2
+};
+
+__device__ __forceinline__ TanhPair tanh_pair(float u) {
+  const float e = expf(-2.0f * fabsf(u));
+  const float r = 1.0f / (1.0f + e);
+  TanhPair p;
+  p.y = copysignf((1.0f - e) * r, u);
+  p.sech2 = 4.0f * e * r * r;
+  return p;
+}
+
+__device__ __forceinline__ float block_sum_256(float v, float *smem) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) smem[w] = v;
+  __syncthreads();
+  float r = (l < 8) ? smem[l] : 0.f;
+#pragma unroll
+  for (int o = 4; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+  return r;  // valid in warp 0
+}
+
+// One element of the backward.  inv = 2/denom.
+__device__ __forceinline__ void bwd_one(float w, float x, float b, float t, float inv, float &dw, float &dx, float &gsum,
+                                        float &lsum) {
+  const TanhPair p = tanh_pair(fmaf(w, x, b));
+  const float d = p.y - t;
+  const float g = d * p.sech2 * inv;
+  dw = g * x;
+  dx = g * w;
+  gsum += g;
+  lsum = fmaf(d, d, lsum);
+}
+
+template <bool VEC>
+__global__ void __launch_bounds__(256) mse_bwd_kernel(const float *__restrict__ W, const float *__restrict__ X,
+                                                      const float *__restrict__ B, const float *__restrict__ Tt,
+                                                      float *__restrict__ dW, float *__restrict__ dX,
+                                                      float *__restrict__ db_partial, float *__restrict__ loss_partial,
+                                                      uint64_t rows, uint64_t cols, float inv) {
+  __shared__ float smem[8];
+  const uint64_t c0 = ((uint64_t)blockIdx.x * 256 + threadIdx.x) * 4;
+  float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+  float lsum = 0.f;
+  if (c0 < cols) {
+    if (VEC) {
+      const uint64_t cols4 = cols / 4, cg = c0 / 4;
+      const float4 b = *reinterpret_cast<const float4 *>(B + c0);
+      const float4 *w4 = reinterpret_cast<const float4 *>(W) + cg;
+      const float4 *x4 = reinterpret_cast<const float4 *>(X) + cg;
+      const float4 *t4 = reinterpret_cast<const float4 *>(Tt) + cg;
+      float4 *dw4 = reinterpret_cast<float4 *>(dW) + cg;
+      float4 *dx4 = reinterpret_cast<float4 *>(dX) + cg;
+      uint64_t r = blockIdx.y;
+      const uint64_t step = gridDim.y;
+      // two rows per trip: six independent 16-byte loads in flight per thread
+      for (; r + step < rows; r += 2 * step) {
+        const uint64_t o0 = r * cols4, o1 = (r + step) * cols4;
+        const float4 wa = __ldcs(w4 + o0), xa = __ldcs(x4 + o0), ta = __ldcs(t4 + o0);
+        const float4 wb = __ldcs(w4 + o1), xb = __ldcs(x4 + o1), tb = __ldcs(t4 + o1);
+        float4 ow, ox;
+        bwd_one(wa.x, xa.x, b.x, ta.x, inv, ow.x, ox.x, g.x, lsum);
+        bwd_one(wa.y, xa.y, b.y, ta.y, inv, ow.y, ox.y, g.y, lsum);
+        bwd_one(wa.z, xa.z, b.z, ta.z, inv, ow.z, ox.z, g.z, lsum);
+        bwd_one(wa.w, xa.w, b.w, ta.w, inv, ow.w, ox.w, g.w, lsum);
+        __stcs(dw4 + o0, ow);
+        __stcs(dx4 + o0, ox);
+        bwd_one(wb.x, xb.x, b.x, tb.x, inv, ow.x, ox.x, g.x, lsum);
+        bwd_one(wb.y, xb.y, b.y, tb.y, inv, ow.y, ox.y, g.y, lsum);
+        bwd_one(wb.z, xb.z, b.z, tb.z, inv, ow.z, ox.z, g.z, lsum);
+        bwd_one(wb.w, xb.w, b.w, tb.w, inv, ow.w, ox.w, g.w, lsum);
+        __stcs(dw4 + o1, ow);
+        __stcs(dx4 + o1, ox);
+      }
+      for (; r < rows; r += step) {
+        const uint64_t o0 = r * cols4;
+        const float4 wa = __ldcs(w4 + o0), xa = __ldcs(x4 + o0), ta = __ldcs(t4 + o0);
+        float4 ow, ox;
+        bwd_one(wa.x, xa.x, b.x, ta.x, inv, ow.x, ox.x, g.x, lsum);
+        bwd_one(wa.y, xa.y, b.y, ta.y, inv, ow.y, ox.y, g.y, lsum);
+        bwd_one(wa.z, xa.z, b.z, ta.z, inv, ow.z, ox.z, g.z, lsum);
+        bwd_one(wa.w, xa.w, b.w, ta.w, inv, ow.w, ox.w, g.w, lsum);
+        __stcs(dw4 + o0, ow);
+        __stcs(dx4 + o0, ox);
+      }
+      *reinterpret_cast<float4 *>(db_partial + (uint64_t)blockIdx.y * cols + c0) = g;
+    } else {
+      float bb[4], gg[4] = {0.f, 0.f, 0.f, 0.f};
+      const int nc = (int)((cols - c0) < 4 ? (cols - c0) : 4);
+      for (int k = 0; k < nc; ++k) bb[k] = B[c0 + k];
+      for (uint64_t r = blockIdx.y; r < rows; r += gridDim.y) {
+        const uint64_t o = r * cols + c0;
+        for (int k = 0; k < nc; ++k) {
+          float ow, ox;
+          bwd_one(W[o + k], X[o + k], bb[k], Tt[o + k], inv, ow, ox, gg[k], lsum);
+          dW[o + k] = ow;
+          dX[o + k] = ox;
+        }
+      }
+      for (int k = 0; k < nc; ++k) db_partial[(uint64_t)blockIdx.y * cols + c0 + k] = gg[k];
+    }
+  }
+  const float bl = block_sum_256(lsum, smem);
+  if (threadIdx.x == 0) loss_partial[(uint64_t)blockIdx.y * gridDim.x + blockIdx.x] = bl;
+}
+
+template <bool VEC>
+__global__ void __launch_bounds__(256) mse_fwd_kernel(const float *__restrict__ W, const float *__restrict__ X,
+                                                      const float *__restrict__ B, const float *__restrict__ Tt,
+                                                      float *__restrict__ loss_partial, uint64_t rows, uint64_t cols) {
+  __shared__ float smem[8];
+  const uint64_t c0 = ((uint64_t)blockIdx.x * 256 + threadIdx.x) * 4;
+  float lsum = 0.f;
+  if (c0 < cols) {
+    if (VEC) {
+      const uint64_t cols4 = cols / 4, cg = c0 / 4;
+      const float4 b = *reinterpret_cast<const float4 *>(B + c0);
+      const float4 *w4 = reinterpret_cast<const float4 *>(W) + cg;
+      const float4 *x4 = reinterpret_cast<const float4 *>(X) + cg;
+      const float4 *t4 = reinterpret_cast<const float4 *>(Tt) + cg;
+      uint64_t r = blockIdx.y;
+      const uint64_t step = gridDim.y;
+#define FWD_ONE(w, x, bb, t)                         \
+  {                                                  \
+    const float d = tanhf(fmaf(w, x, bb)) - (t);     \
+    lsum = fmaf(d, d, lsum);                         \
+  }
+      for (; r + step < rows; r += 2 * step) {
+        const uint64_t o0 = r * cols4, o1 = (r + step) * cols4;
+        const float4 wa = __ldcs(w4 + o0), xa = __ldcs(x4 + o0), ta = __ldcs(t4 + o0);
+        const float4 wb = __ldcs(w4 + o1), xb = __ldcs(x4 + o1), tb = __ldcs(t4 + o1);
+        FWD_ONE(wa.x, xa.x, b.x, ta.x) FWD_ONE(wa.y, xa.y, b.y, ta.y) FWD_ONE(wa.z, xa.z, b.z, ta.z) FWD_ONE(wa.w, xa.w, b.w, ta.w)
+        FWD_ONE(wb.x, xb.x, b.x, tb.x) FWD_ONE(wb.y, xb.y, b.y, tb.y) FWD_ONE(wb.z, xb.z, b.z, tb.z) FWD_ONE(wb.w, xb.w, b.w, tb.w)
+      }
+      for (; r < rows; r += step) {
+        const uint64_t o0 = r * cols4;
+        const float4 wa = __ldcs(w4 + o0), xa = __ldcs(x4 + o0), ta = __ldcs(t4 + o0);
+        FWD_ONE(wa.x, xa.x, b.x, ta.x) FWD_ONE(wa.y, xa.y, b.y, ta.y) FWD_ONE(wa.z, xa.z, b.z, ta.z) FWD_ONE(wa.w, xa.w, b.w, ta.w)
+      }
+    } else {
+      const int nc = (int)((cols - c0) < 4 ? (cols - c0) : 4);
+      for (uint64_t r = blockIdx.y; r < rows; r += gridDim.y) {
+        const uint64_t o = r * cols + c0;
+        for (int k = 0; k < nc; ++k) FWD_ONE(W[o + k], X[o + k], B[c0 + k], Tt[o + k])
+      }
+#undef FWD_ONE
+    }
+  }
+  const float bl = block_sum_256(lsum, smem);
+  if (threadIdx.x == 0) loss_partial[(uint64_t)blockIdx.y * gridDim.x + blockIdx.x] = bl;
+}
+
+// Adds the per-block partial sums in index order, in binary64, and scales.
+__global__ void __launch_bounds__(256) loss_finalize_kernel(const float *__restrict__ partial, uint32_t n, double scale,
+                                                            float *__restrict__ out) {
+  __shared__ double sm[256];
+  double s = 0.0;
+  for (uint32_t k = threadIdx.x; k < n; k += 256) s += (double)partial[k];
+  sm[threadIdx.x] = s;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if ((int)threadIdx.x < o) sm[threadIdx.x] += sm[threadIdx.x + o];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) out[0] = (float)(sm[0] * scale);
+}
+
+struct MsePlan {
+  uint64_t rows, cols;
+  double denom;
+  unsigned gx, gy;
+  bool vec;
+};
+
+static int mse_plan(vrhi_stream_t *st, const ArgView *args, int n_in_out, const vrhi_mse_params &q, const char *name, MsePlan *pl) {
+  if (q.cols == 0 || q.rows == 0) return fail(VRHI_ERR_SIZE, "%s: empty problem", name);
+  if (q.rows > (1ull << 40) || q.cols > (1ull << 31)) return fail(VRHI_ERR_SIZE, "%s: shape out of range", name);
+  const uint64_t full = q.rows * q.cols * 4;
+  const uint64_t want[8] = {full, full, q.cols * 4, full, 0, 0, 0, 0};
+  for (int k = 0; k < 4; ++k)
+    if (args[k].bytes < want[k]) return fail(VRHI_ERR_SIZE, "%s: argument %d holds %llu bytes, %llu needed", name, k, (unsigned long long)args[k].bytes, (unsigned long long)want[k]);
+  for (int k = 4; k < n_in_out; ++k)
+    if (!writable(args[k])) return fail(VRHI_ERR_INVALID, "%s: argument %d is read-only (class %s)", name, k, vrhi_arg_class_name(args[k].buf_cls));
+  pl->rows = q.rows; pl->cols = q.cols;
+  pl->denom = q.denom > 0.0 ? q.denom : (double)q.rows * (double)q.cols;
+  const int sms = st->dev->prop.multiProcessorCount;
+  const uint64_t gx = (q.cols + 1023) / 1024;
+  uint64_t gy = ((uint64_t)sms * 8 + gx - 1) / gx;
+  if (gy > q.rows) gy = q.rows;
+  if (gy > 4096) gy = 4096;
+  if (gx > 0x7fffffffull) return fail(VRHI_ERR_UNSUPPORTED, "%s: too many columns", name);
+  pl->gx = (unsigned)gx; pl->gy = (unsigned)gy;
+  pl->vec = (q.cols % 4 == 0);
+  return VRHI_OK;
+}
+
+int launch_mse_tanh_fwd(vrhi_stream_t *st, const ArgView *args, int n_args, const void *params, size_t params_size) {
+  vrhi_mse_params q;
+  VRHI_TRY(read_params(params, params_size, &q));
+  if (n_args != 5) return fail(VRHI_ERR_INVALID, "mse_tanh_fwd takes 5 arguments (W, x, b, t, loss), got %d", n_args);
+  MsePlan pl;
+  VRHI_TRY(mse_plan(st, args, 5, q, "mse_tanh_fwd", &pl));
+  if (args[4].bytes < 4) return fail(VRHI_ERR_SIZE, "mse_tanh_fwd: loss output needs 4 bytes");
+  char *payload = nullptr;
+  const size_t n_part = (size_t)pl.gx * pl.gy;
+  VRHI_TRY(stream_arena(st, n_part * 4, nullptr, &payload));
+  dim3 grid(pl.gx, pl.gy);
+  const float *W = (const float *)args[0].ptr, *X = (const float *)args[1].ptr, *B = (const float *)args[2].ptr, *T = (const float *)args[3].ptr;
+  if (pl.vec) mse_fwd_kernel<true><<<grid, 256, 0, st->s>>>(W, X, B, T, (float *)payload, pl.rows, pl.cols);
+  else mse_fwd_kernel<false><<<grid, 256, 0, st->s>>>(W, X, B, T, (float *)payload, pl.rows, pl.cols);
+  VRHI_TRY(post_launch(st, "mse_tanh_fwd"));
+  loss_finalize_kernel<<<1, 256, 0, st->s>>>((const float *)payload, (uint32_t)n_part, 1.0 / pl.denom, (float *)args[4].ptr);
+  return post_launch(st, "loss_finalize");
+}
+
+int launch_mse_tanh_bwd(vrhi_stream_t *st, const ArgView *args, int n_args, const void *params, size_t params_size) {
+  vrhi_mse_params q;
+  VRHI_TRY(read_params(params, params_size, &q));
+  if (n_args != 7 && n_args != 8) return fail(VRHI_ERR_INVALID, "mse_tanh_bwd takes 7 or 8 arguments (W, x, b, t, dW, dx, db[, loss]), got %d", n_args);
+  MsePlan pl;
+  VRHI_TRY(mse_plan(st, args, n_args, q, "mse_tanh_bwd", &pl));
+  const uint64_t full = pl.rows * pl.cols * 4;
+  if (args[4].bytes < full || args[5].bytes < full) return fail(VRHI_ERR_SIZE, "mse_tanh_bwd: dW/dx outputs need %llu bytes each", (unsigned long long)full);
+  if (args[6].bytes < pl.cols * 4) return fail(VRHI_ERR_SIZE, "mse_tanh_bwd: db output needs %llu bytes", (unsigned long long)pl.cols * 4);
+  if (n_args == 8 && args[7].bytes < 4) return fail(VRHI_ERR_SIZE, "mse_tanh_bwd: loss output needs 4 bytes");
+  char *payload = nullptr;
+  const size_t n_part = (size_t)pl.gx * pl.gy;
+  const size_t db_bytes = (size_t)pl.gy * pl.cols * 4;
+  VRHI_TRY(stream_arena(st, db_bytes + n_part * 4, nullptr, &payload));
+  float *db_partial = (float *)payload;
+  float *loss_partial = (float *)(payload + db_bytes);
+  dim3 grid(pl.gx, pl.gy);
+  const float *W = (const float *)args[0].ptr, *X = (const float *)args[1].ptr, *B = (const float *)args[2].ptr, *T = (const float *)args[3].ptr;
+  const float inv = (float)(2.0 / pl.denom);
+  if (pl.vec) mse_bwd_kernel<true><<<grid, 256, 0, st->s>>>(W, X, B, T, (float *)args[4].ptr, (float *)args[5].ptr, db_partial, loss_partial, pl.rows, pl.cols, inv);
+  else mse_bwd_kernel<false><<<grid, 256, 0, st->s>>>(W, X, B, T, (float *)args[4].ptr, (float *)args[5].ptr, db_partial, loss_partial, pl.rows, pl.cols, inv);
+  VRHI_TRY(post_launch(st, "mse_tanh_bwd"));
+  VRHI_TRY(col_finalize(st, db_partial, (float *)args[6].ptr, pl.gy, pl.cols, 1.0f));
+  if (n_args == 8) {
+    loss_finalize_kernel<<<1, 256, 0, st->s>>>((const float *)loss_partial, (uint32_t)n_part, 1.0 / pl.denom, (float *)args[7].ptr);
+    VRHI_TRY(post_launch(st, "loss_finalize"));
+  }
+  return VRHI_OK;
+}
+
+}  // namespace vrhi

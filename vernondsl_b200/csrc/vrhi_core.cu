@@ -1,0 +1,558 @@
+// Device, buffer, stream, event, error and operator-registry half of libvrhi.so.
+// Stands in for the runtime services fractal.py gets from Taichi (fractal.py:5 ti.init,
+// :8 ti.field, :16 kernel registration, :31 launch); see include/vrhi.h.
+#include <cstring>
+#include <new>
+
+#include "vrhi_internal.h"
+
+namespace vrhi {
+
+static thread_local std::string g_last_error;
+
+int fail(int code, const char *fmt, ...) {
+  char buf[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+  return code;
+}
+
+void clear_error() { g_last_error.clear(); }
+
+static int set_device(vrhi_device_t *dev) {
+  VRHI_CUDA(cudaSetDevice(dev->ordinal));
+  return VRHI_OK;
+}
+
+int stream_arena(vrhi_stream_t *st, size_t payload, uint32_t **ctrl, char **payload_ptr) {
+  if (!st->arena || st->arena_payload < payload) {
+    VRHI_TRY(set_device(st->dev));
+    size_t want = payload < (size_t(4) << 20) ? (size_t(4) << 20) : payload;
+    if (st->arena) {
+      VRHI_CUDA(cudaStreamSynchronize(st->s));
+      VRHI_CUDA(cudaFree(st->arena));
+      st->arena = nullptr;
+      st->arena_payload = 0;
+    }
+    void *p = nullptr;
+    VRHI_CUDA(cudaMalloc(&p, kCtrlBytes + want));
+    VRHI_CUDA(cudaMemsetAsync(p, 0, kCtrlBytes, st->s));
+    st->arena = static_cast<char *>(p);
+    st->arena_payload = want;
+  }
+  if (ctrl) *ctrl = reinterpret_cast<uint32_t *>(st->arena);
+  if (payload_ptr) *payload_ptr = st->arena + kCtrlBytes;
+  return VRHI_OK;
+}
+
+static const OpDef kOps[] = {
+    {"escape_time", "args: image(OUTPUT|IMAGE u32/u16/f32 [height][width]); params: vrhi_escape_params",
+     launch_escape_time},
+    {"fused_map", "args: a,x,y(INPUT f32[n]), out(OUTPUT f32[n]); params: vrhi_map_params", launch_fused_map},
+    {"map_tape", "args: inputs..., outputs...; params: vrhi_tape_params", launch_map_tape},
+    {"row_sum", "args: in(INPUT f32[rows][cols]), out(OUTPUT f32[rows]); params: vrhi_rows_params", launch_row_sum},
+    {"row_max", "args: in(INPUT f32[rows][cols]), out(OUTPUT f32[rows]); params: vrhi_rows_params", launch_row_max},
+    {"row_softmax", "args: in(INPUT f32[rows][cols]), out(OUTPUT f32[rows][cols]); params: vrhi_rows_params",
+     launch_row_softmax},
+    {"row_stats_softmax",
+     "args: in(INPUT), sum(OUTPUT f32[rows]), max(OUTPUT f32[rows]), softmax(OUTPUT f32[rows][cols]); params: "
+     "vrhi_rows_params",
+     launch_row_stats_softmax},
+    {"col_sum", "args: in(INPUT f32[rows][cols]), out(OUTPUT f32[cols]); params: vrhi_rows_params", launch_col_sum},
+    {"mse_tanh_fwd", "args: W,x,b,t(INPUT), loss(OUTPUT f32[1]); params: vrhi_mse_params", launch_mse_tanh_fwd},
+    {"mse_tanh_bwd", "args: W,x,b,t(INPUT), dW,dx,db(OUTPUT)[, loss(OUTPUT f32[1])]; params: vrhi_mse_params",
+     launch_mse_tanh_bwd},
+    {"fp32_probe", "args: out(OUTPUT >=4 bytes); params: vrhi_probe_params", launch_fp32_probe},
+};
+static const int kNumOps = int(sizeof(kOps) / sizeof(kOps[0]));
+
+static const char *const kSemantic[] = {"input",  "output", "uniform", "uniform_constant",
+                                        "storage_buffer", "image", "varying"};
+
+}  // namespace vrhi
+
+using namespace vrhi;
+
+extern "C" {
+
+const char *vrhi_last_error(void) { return g_last_error.c_str(); }
+int vrhi_version(void) { return VRHI_VERSION; }
+
+int vrhi_arg_class_from_semantic(const char *semantic, int *out_class) {
+  if (!semantic || !out_class) return fail(VRHI_ERR_INVALID, "NULL argument");
+  for (int k = 0; k <= VRHI_VARYING; ++k)
+    if (strcmp(semantic, kSemantic[k]) == 0) {
+      *out_class = k;
+      return VRHI_OK;
+    }
+  return fail(VRHI_ERR_NOT_FOUND, "unknown vernon.semantic '%s'", semantic);
+}
+
+const char *vrhi_arg_class_name(int arg_class) {
+  return (arg_class >= 0 && arg_class <= VRHI_VARYING) ? kSemantic[arg_class] : nullptr;
+}
+
+/* ---------------------------------------------------------------- device ---------------- */
+
+int vrhi_device_count(int *out_count) {
+  if (!out_count) return fail(VRHI_ERR_INVALID, "NULL out_count");
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess) {
+    *out_count = 0;
+    return fail(VRHI_ERR_CUDA, "cudaGetDeviceCount failed: %s", cudaGetErrorString(e));
+  }
+  *out_count = n;
+  return VRHI_OK;
+}
+
+int vrhi_device_create(int ordinal, vrhi_device *out_dev) {
+  if (!out_dev) return fail(VRHI_ERR_INVALID, "NULL out_dev");
+  *out_dev = nullptr;
+  int n = 0;
+  VRHI_TRY(vrhi_device_count(&n));
+  if (ordinal < 0 || ordinal >= n) return fail(VRHI_ERR_INVALID, "device ordinal %d out of range [0,%d)", ordinal, n);
+  vrhi_device_t *d = new (std::nothrow) vrhi_device_t();
+  if (!d) return fail(VRHI_ERR_OOM, "host allocation failed");
+  d->ordinal = ordinal;
+  cudaError_t e = cudaSetDevice(ordinal);
+  if (e == cudaSuccess) e = cudaGetDeviceProperties(&d->prop, ordinal);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&d->sm_clock_khz, cudaDevAttrClockRate, ordinal);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&d->mem_clock_khz, cudaDevAttrMemoryClockRate, ordinal);
+  if (e != cudaSuccess) {
+    delete d;
+    return fail(VRHI_ERR_CUDA, "opening device %d failed: %s", ordinal, cudaGetErrorString(e));
+  }
+  if (d->prop.major < 10) {
+    int maj = d->prop.major, min = d->prop.minor;
+    delete d;
+    return fail(VRHI_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library carries sm_100a code only", ordinal, maj, min);
+  }
+  vrhi_stream_t *s = new (std::nothrow) vrhi_stream_t();
+  if (!s) {
+    delete d;
+    return fail(VRHI_ERR_OOM, "host allocation failed");
+  }
+  s->dev = d;
+  s->s = nullptr;  // legacy default stream
+  s->owned = false;
+  d->default_stream = s;
+  *out_dev = d;
+  return VRHI_OK;
+}
+
+int vrhi_device_destroy(vrhi_device dev) {
+  if (!dev) return VRHI_OK;
+  if (dev->default_stream) {
+    if (dev->default_stream->arena) {
+      cudaSetDevice(dev->ordinal);
+      cudaFree(dev->default_stream->arena);
+    }
+    delete dev->default_stream;
+  }
+  delete dev;
+  return VRHI_OK;
+}
+
+int vrhi_device_props_get(vrhi_device dev, vrhi_device_props *out) {
+  if (!dev || !out) return fail(VRHI_ERR_INVALID, "NULL argument");
+  if (out->size < sizeof(uint32_t) * 2) return fail(VRHI_ERR_SIZE, "vrhi_device_props.size not set");
+  vrhi_device_props p{};
+  p.size = sizeof p;
+  p.ordinal = dev->ordinal;
+  p.sm_count = dev->prop.multiProcessorCount;
+  p.cc_major = dev->prop.major;
+  p.cc_minor = dev->prop.minor;
+  p.sm_clock_khz = dev->sm_clock_khz;
+  p.mem_clock_khz = dev->mem_clock_khz;
+  p.l2_bytes = dev->prop.l2CacheSize;
+  p.smem_per_block_optin = (int32_t)dev->prop.sharedMemPerBlockOptin;
+  p.total_mem_bytes = dev->prop.totalGlobalMem;
+  strncpy(p.name, dev->prop.name, sizeof p.name - 1);
+  size_t n = out->size < sizeof p ? out->size : sizeof p;
+  uint32_t declared = out->size;
+  memcpy(out, &p, n);
+  out->size = declared < sizeof p ? declared : (uint32_t)sizeof p;
+  return VRHI_OK;
+}
+
+int vrhi_device_synchronize(vrhi_device dev) {
+  if (!dev) return fail(VRHI_ERR_INVALID, "NULL device");
+  VRHI_TRY(set_device(dev));
+  VRHI_CUDA(cudaDeviceSynchronize());
+  return VRHI_OK;
+}
+
+int vrhi_device_set_alloc_limit(vrhi_device dev, uint64_t bytes) {
+  if (!dev) return fail(VRHI_ERR_INVALID, "NULL device");
+  dev->limit = bytes;
+  return VRHI_OK;
+}
+
+int vrhi_device_allocated(vrhi_device dev, uint64_t *out_bytes) {
+  if (!dev || !out_bytes) return fail(VRHI_ERR_INVALID, "NULL argument");
+  *out_bytes = dev->allocated;
+  return VRHI_OK;
+}
+
+/* ---------------------------------------------------------------- buffers --------------- */
+
+static int check_class(int cls) {
+  if (cls < VRHI_INPUT || cls > VRHI_VARYING) return fail(VRHI_ERR_INVALID, "argument class %d out of range", cls);
+  return VRHI_OK;
+}
+
+int vrhi_buffer_create(vrhi_device dev, uint64_t bytes, int arg_class, vrhi_buffer *out_buf) {
+  if (!dev || !out_buf) return fail(VRHI_ERR_INVALID, "NULL argument");
+  *out_buf = nullptr;
+  VRHI_TRY(check_class(arg_class));
+  if (bytes == 0) return fail(VRHI_ERR_SIZE, "zero-sized buffer");
+  if (dev->limit && dev->allocated + bytes > dev->limit)
+    return fail(VRHI_ERR_OOM, "allocation of %llu bytes exceeds the device handle's limit (%llu held, limit %llu)",
+                (unsigned long long)bytes, (unsigned long long)dev->allocated, (unsigned long long)dev->limit);
+  VRHI_TRY(set_device(dev));
+  void *p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(e == cudaErrorMemoryAllocation ? VRHI_ERR_OOM : VRHI_ERR_CUDA, "cudaMalloc(%llu) failed: %s",
+                (unsigned long long)bytes, cudaGetErrorString(e));
+  }
+  vrhi_buffer_t *b = new (std::nothrow) vrhi_buffer_t{dev, p, bytes, arg_class, true};
+  if (!b) {
+    cudaFree(p);
+    return fail(VRHI_ERR_OOM, "host allocation failed");
+  }
+  dev->allocated += bytes;
+  *out_buf = b;
+  return VRHI_OK;
+}
+
+int vrhi_buffer_wrap(vrhi_device dev, void *device_ptr, uint64_t bytes, int arg_class, vrhi_buffer *out_buf) {
+  if (!dev || !out_buf || !device_ptr) return fail(VRHI_ERR_INVALID, "NULL argument");
+  *out_buf = nullptr;
+  VRHI_TRY(check_class(arg_class));
+  if (bytes == 0) return fail(VRHI_ERR_SIZE, "zero-sized buffer");
+  if (reinterpret_cast<uintptr_t>(device_ptr) % 16) return fail(VRHI_ERR_SIZE, "wrapped pointer is not 16-byte aligned");
+  vrhi_buffer_t *b = new (std::nothrow) vrhi_buffer_t{dev, device_ptr, bytes, arg_class, false};
+  if (!b) return fail(VRHI_ERR_OOM, "host allocation failed");
+  *out_buf = b;
+  return VRHI_OK;
+}
+
+int vrhi_buffer_destroy(vrhi_buffer buf) {
+  if (!buf) return VRHI_OK;
+  int rc = VRHI_OK;
+  if (buf->owned) {
+    cudaSetDevice(buf->dev->ordinal);
+    cudaError_t e = cudaFree(buf->ptr);
+    if (e != cudaSuccess) rc = fail(VRHI_ERR_CUDA, "cudaFree failed: %s", cudaGetErrorString(e));
+    buf->dev->allocated -= buf->bytes;
+  }
+  delete buf;
+  return rc;
+}
+
+int vrhi_buffer_size(vrhi_buffer buf, uint64_t *out_bytes) {
+  if (!buf || !out_bytes) return fail(VRHI_ERR_INVALID, "NULL argument");
+  *out_bytes = buf->bytes;
+  return VRHI_OK;
+}
+
+int vrhi_buffer_class(vrhi_buffer buf, int *out_class) {
+  if (!buf || !out_class) return fail(VRHI_ERR_INVALID, "NULL argument");
+  *out_class = buf->cls;
+  return VRHI_OK;
+}
+
+int vrhi_buffer_device_ptr(vrhi_buffer buf, void **out_ptr) {
+  if (!buf || !out_ptr) return fail(VRHI_ERR_INVALID, "NULL argument");
+  *out_ptr = buf->ptr;
+  return VRHI_OK;
+}
+
+static int range_ok(vrhi_buffer buf, uint64_t offset, uint64_t bytes) {
+  if (offset > buf->bytes || bytes > buf->bytes - offset)
+    return fail(VRHI_ERR_SIZE, "range [%llu, +%llu) exceeds the buffer (%llu bytes)", (unsigned long long)offset,
+                (unsigned long long)bytes, (unsigned long long)buf->bytes);
+  return VRHI_OK;
+}
+
+static int copy(vrhi_buffer buf, uint64_t offset, void *host, uint64_t bytes, vrhi_stream stream, bool up) {
+  if (!buf || (!host && bytes)) return fail(VRHI_ERR_INVALID, "NULL argument");
+  VRHI_TRY(range_ok(buf, offset, bytes));
+  if (stream && stream->dev != buf->dev) return fail(VRHI_ERR_INVALID, "stream and buffer belong to different devices");
+  if (bytes == 0) return VRHI_OK;
+  VRHI_TRY(set_device(buf->dev));
+  char *d = static_cast<char *>(buf->ptr) + offset;
+  if (stream) {
+    VRHI_CUDA(cudaMemcpyAsync(up ? (void *)d : host, up ? (const void *)host : (const void *)d, bytes,
+                              up ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost, stream->s));
+  } else {
+    VRHI_CUDA(cudaMemcpy(up ? (void *)d : host, up ? (const void *)host : (const void *)d, bytes,
+                         up ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost));
+  }
+  return VRHI_OK;
+}
+
+int vrhi_buffer_upload(vrhi_buffer buf, uint64_t offset, const void *host, uint64_t bytes, vrhi_stream stream) {
+  if (buf && (buf->cls == VRHI_OUTPUT)) { /* uploading into an OUTPUT buffer is allowed (initial value) */ }
+  return copy(buf, offset, const_cast<void *>(host), bytes, stream, true);
+}
+
+int vrhi_buffer_download(vrhi_buffer buf, uint64_t offset, void *host, uint64_t bytes, vrhi_stream stream) {
+  return copy(buf, offset, host, bytes, stream, false);
+}
+
+int vrhi_buffer_fill_u8(vrhi_buffer buf, uint64_t offset, int value, uint64_t bytes, vrhi_stream stream) {
+  if (!buf) return fail(VRHI_ERR_INVALID, "NULL buffer");
+  VRHI_TRY(range_ok(buf, offset, bytes));
+  if (bytes == 0) return VRHI_OK;
+  VRHI_TRY(set_device(buf->dev));
+  char *d = static_cast<char *>(buf->ptr) + offset;
+  if (stream)
+    VRHI_CUDA(cudaMemsetAsync(d, value, bytes, stream->s));
+  else
+    VRHI_CUDA(cudaMemset(d, value, bytes));
+  return VRHI_OK;
+}
+
+int vrhi_host_alloc(uint64_t bytes, void **out_host) {
+  if (!out_host) return fail(VRHI_ERR_INVALID, "NULL out_host");
+  *out_host = nullptr;
+  if (bytes == 0) return fail(VRHI_ERR_SIZE, "zero-sized allocation");
+  cudaError_t e = cudaMallocHost(out_host, bytes);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(VRHI_ERR_OOM, "cudaMallocHost(%llu) failed: %s", (unsigned long long)bytes, cudaGetErrorString(e));
+  }
+  return VRHI_OK;
+}
+
+int vrhi_host_free(void *host) {
+  if (!host) return VRHI_OK;
+  VRHI_CUDA(cudaFreeHost(host));
+  return VRHI_OK;
+}
+
+/* ---------------------------------------------------------------- streams / events ------ */
+
+int vrhi_stream_create(vrhi_device dev, vrhi_stream *out_stream) {
+  if (!dev || !out_stream) return fail(VRHI_ERR_INVALID, "NULL argument");
+  *out_stream = nullptr;
+  VRHI_TRY(set_device(dev));
+  cudaStream_t s;
+  VRHI_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+  vrhi_stream_t *st = new (std::nothrow) vrhi_stream_t{dev, s, true, nullptr, 0, 0};
+  if (!st) {
+    cudaStreamDestroy(s);
+    return fail(VRHI_ERR_OOM, "host allocation failed");
+  }
+  *out_stream = st;
+  return VRHI_OK;
+}
+
+int vrhi_stream_wrap(vrhi_device dev, void *cuda_stream, vrhi_stream *out_stream) {
+  if (!dev || !out_stream) return fail(VRHI_ERR_INVALID, "NULL argument");
+  vrhi_stream_t *st = new (std::nothrow) vrhi_stream_t{dev, static_cast<cudaStream_t>(cuda_stream), false, nullptr, 0, 0};
+  if (!st) return fail(VRHI_ERR_OOM, "host allocation failed");
+  *out_stream = st;
+  return VRHI_OK;
+}
+
+int vrhi_stream_destroy(vrhi_stream stream) {
+  if (!stream) return VRHI_OK;
+  if (stream == stream->dev->default_stream) return fail(VRHI_ERR_INVALID, "the device's default stream is not destroyed by the caller");
+  cudaSetDevice(stream->dev->ordinal);
+  int rc = VRHI_OK;
+  if (stream->arena) {
+    cudaStreamSynchronize(stream->s);
+    cudaFree(stream->arena);
+  }
+  if (stream->owned) {
+    cudaError_t e = cudaStreamDestroy(stream->s);
+    if (e != cudaSuccess) rc = fail(VRHI_ERR_CUDA, "cudaStreamDestroy failed: %s", cudaGetErrorString(e));
+  }
+  delete stream;
+  return rc;
+}
+
+int vrhi_stream_synchronize(vrhi_stream stream) {
+  if (!stream) return fail(VRHI_ERR_INVALID, "NULL stream");
+  VRHI_TRY(set_device(stream->dev));
+  VRHI_CUDA(cudaStreamSynchronize(stream->s));
+  return VRHI_OK;
+}
+
+int vrhi_stream_check(vrhi_stream stream) {
+  if (!stream) return fail(VRHI_ERR_INVALID, "NULL stream");
+  VRHI_TRY(vrhi_stream_synchronize(stream));
+  if (!stream->arena) return VRHI_OK;
+  int32_t status = 0;
+  VRHI_CUDA(cudaMemcpy(&status, stream->arena, sizeof status, cudaMemcpyDeviceToHost));
+  if (status != 0) {
+    VRHI_CUDA(cudaMemset(stream->arena, 0, sizeof status));
+    return fail(status, "a kernel on this stream recorded device status %d", status);
+  }
+  return VRHI_OK;
+}
+
+int vrhi_stream_launch_count(vrhi_stream stream, uint64_t *out_count) {
+  if (!stream || !out_count) return fail(VRHI_ERR_INVALID, "NULL argument");
+  *out_count = stream->launches;
+  return VRHI_OK;
+}
+
+int vrhi_event_create(vrhi_device dev, vrhi_event *out_event) {
+  if (!dev || !out_event) return fail(VRHI_ERR_INVALID, "NULL argument");
+  *out_event = nullptr;
+  VRHI_TRY(set_device(dev));
+  cudaEvent_t e;
+  VRHI_CUDA(cudaEventCreate(&e));
+  vrhi_event_t *ev = new (std::nothrow) vrhi_event_t{dev, e};
+  if (!ev) {
+    cudaEventDestroy(e);
+    return fail(VRHI_ERR_OOM, "host allocation failed");
+  }
+  *out_event = ev;
+  return VRHI_OK;
+}
+
+int vrhi_event_destroy(vrhi_event event) {
+  if (!event) return VRHI_OK;
+  cudaSetDevice(event->dev->ordinal);
+  cudaEventDestroy(event->e);
+  delete event;
+  return VRHI_OK;
+}
+
+int vrhi_event_record(vrhi_event event, vrhi_stream stream) {
+  if (!event) return fail(VRHI_ERR_INVALID, "NULL event");
+  VRHI_TRY(set_device(event->dev));
+  VRHI_CUDA(cudaEventRecord(event->e, stream ? stream->s : nullptr));
+  return VRHI_OK;
+}
+
+int vrhi_event_synchronize(vrhi_event event) {
+  if (!event) return fail(VRHI_ERR_INVALID, "NULL event");
+  VRHI_CUDA(cudaEventSynchronize(event->e));
+  return VRHI_OK;
+}
+
+int vrhi_event_elapsed_ms(vrhi_event start, vrhi_event stop, float *out_ms) {
+  if (!start || !stop || !out_ms) return fail(VRHI_ERR_INVALID, "NULL argument");
+  VRHI_CUDA(cudaEventElapsedTime(out_ms, start->e, stop->e));
+  return VRHI_OK;
+}
+
+int vrhi_stream_wait_event(vrhi_stream stream, vrhi_event event) {
+  if (!stream || !event) return fail(VRHI_ERR_INVALID, "NULL argument");
+  VRHI_TRY(set_device(stream->dev));
+  VRHI_CUDA(cudaStreamWaitEvent(stream->s, event->e, 0));
+  return VRHI_OK;
+}
+
+/* ---------------------------------------------------------------- operators ------------- */
+
+int vrhi_op_count(int *out_count) {
+  if (!out_count) return fail(VRHI_ERR_INVALID, "NULL out_count");
+  *out_count = kNumOps;
+  return VRHI_OK;
+}
+
+int vrhi_op_name(int op, const char **out_name) {
+  if (!out_name) return fail(VRHI_ERR_INVALID, "NULL out_name");
+  if (op < 0 || op >= kNumOps) return fail(VRHI_ERR_NOT_FOUND, "operator id %d out of range", op);
+  *out_name = kOps[op].name;
+  return VRHI_OK;
+}
+
+int vrhi_op_signature(int op, const char **out_text) {
+  if (!out_text) return fail(VRHI_ERR_INVALID, "NULL out_text");
+  if (op < 0 || op >= kNumOps) return fail(VRHI_ERR_NOT_FOUND, "operator id %d out of range", op);
+  *out_text = kOps[op].signature;
+  return VRHI_OK;
+}
+
+int vrhi_op_lookup(const char *name, int *out_op) {
+  if (!name || !out_op) return fail(VRHI_ERR_INVALID, "NULL argument");
+  for (int k = 0; k < kNumOps; ++k)
+    if (strcmp(kOps[k].name, name) == 0) {
+      *out_op = k;
+      return VRHI_OK;
+    }
+  return fail(VRHI_ERR_NOT_FOUND, "no operator named '%s'", name);
+}
+
+int vrhi_op_launch(vrhi_stream stream, int op, const vrhi_arg *args, int n_args, const void *params,
+                   size_t params_size) {
+  if (!stream) return fail(VRHI_ERR_INVALID, "NULL stream");
+  if (op < 0 || op >= kNumOps) return fail(VRHI_ERR_NOT_FOUND, "operator id %d out of range", op);
+  if (n_args < 0 || n_args > 16 || (n_args && !args)) return fail(VRHI_ERR_INVALID, "bad argument list");
+  ArgView views[16];
+  for (int k = 0; k < n_args; ++k) {
+    const vrhi_arg &a = args[k];
+    if (!a.buffer) return fail(VRHI_ERR_INVALID, "%s: argument %d has no buffer", kOps[op].name, k);
+    if (a.buffer->dev != stream->dev) return fail(VRHI_ERR_INVALID, "%s: argument %d lives on another device", kOps[op].name, k);
+    if (a.offset % 16) return fail(VRHI_ERR_SIZE, "%s: argument %d offset %llu is not a multiple of 16", kOps[op].name, k, (unsigned long long)a.offset);
+    if (a.offset > a.buffer->bytes) return fail(VRHI_ERR_SIZE, "%s: argument %d offset beyond the buffer", kOps[op].name, k);
+    uint64_t avail = a.buffer->bytes - a.offset;
+    uint64_t bytes = a.bytes ? a.bytes : avail;
+    if (bytes > avail) return fail(VRHI_ERR_SIZE, "%s: argument %d view exceeds the buffer", kOps[op].name, k);
+    VRHI_TRY(check_class(a.arg_class));
+    views[k] = ArgView{static_cast<char *>(a.buffer->ptr) + a.offset, bytes, a.arg_class, a.buffer->cls};
+  }
+  VRHI_TRY(set_device(stream->dev));
+  return kOps[op].launch(stream, views, n_args, params, params_size);
+}
+
+/* ---------------------------------------------------------------- partitioning ---------- */
+
+int vrhi_partition_rows(uint64_t total_rows, uint32_t chunk_rows, uint32_t world, uint32_t rank, int scheme,
+                        vrhi_row_partition *out) {
+  if (!out) return fail(VRHI_ERR_INVALID, "NULL out");
+  if (world == 0 || rank >= world) return fail(VRHI_ERR_INVALID, "rank %u outside world %u", rank, world);
+  if (total_rows == 0 || total_rows > 0xffffffffull) return fail(VRHI_ERR_SIZE, "row count out of range");
+  vrhi_row_partition p{};
+  if (scheme == VRHI_PART_CONTIGUOUS) {
+    // one band per rank: band height = ceil(total/world) rounded up to chunk_rows (if given)
+    uint64_t band = (total_rows + world - 1) / world;
+    if (chunk_rows > 1) band = (band + chunk_rows - 1) / chunk_rows * chunk_rows;
+    uint64_t begin = band * rank;
+    p.chunk_rows = (uint32_t)band;
+    p.chunk_first = rank;
+    p.chunk_step = world;
+    p.chunk_count = begin < total_rows ? 1u : 0u;
+    p.rows_owned = begin < total_rows ? (total_rows - begin < band ? total_rows - begin : band) : 0;
+  } else if (scheme == VRHI_PART_CYCLIC) {
+    if (chunk_rows == 0) return fail(VRHI_ERR_INVALID, "cyclic partition needs chunk_rows > 0");
+    uint64_t n_chunks = (total_rows + chunk_rows - 1) / chunk_rows;
+    uint64_t mine = n_chunks > rank ? (n_chunks - rank + world - 1) / world : 0;
+    p.chunk_rows = chunk_rows;
+    p.chunk_first = rank;
+    p.chunk_step = world;
+    p.chunk_count = (uint32_t)mine;
+    uint64_t rows = mine * chunk_rows;
+    // the globally last chunk may be short; it belongs to rank (n_chunks-1) % world
+    if (mine && (n_chunks - 1) % world == rank) rows -= n_chunks * chunk_rows - total_rows;
+    p.rows_owned = rows;
+  } else {
+    return fail(VRHI_ERR_INVALID, "unknown partition scheme %d", scheme);
+  }
+  *out = p;
+  return VRHI_OK;
+}
+
+int vrhi_partition_leading(uint64_t n, uint32_t world, uint32_t rank, uint64_t *out_begin, uint64_t *out_count) {
+  if (!out_begin || !out_count) return fail(VRHI_ERR_INVALID, "NULL argument");
+  if (world == 0 || rank >= world) return fail(VRHI_ERR_INVALID, "rank %u outside world %u", rank, world);
+  uint64_t base = n / world, extra = n % world;
+  *out_begin = base * rank + (rank < extra ? rank : extra);
+  *out_count = base + (rank < extra ? 1 : 0);
+  return VRHI_OK;
+}
+
+}  // extern "C"

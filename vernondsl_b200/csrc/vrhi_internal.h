@@ -1,0 +1,124 @@
+// Internal definitions shared by the translation units of libvrhi.so.  Not installed.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <string>
+
+#include "vrhi.h"
+
+struct vrhi_device_t {
+  int ordinal;
+  cudaDeviceProp prop;
+  int sm_clock_khz, mem_clock_khz;
+  uint64_t allocated, limit;
+  vrhi_stream_t *default_stream;
+};
+
+struct vrhi_buffer_t {
+  vrhi_device_t *dev;
+  void *ptr;
+  uint64_t bytes;
+  int cls;
+  bool owned;
+};
+
+// Per-stream scratch arena.  Kernels launched on one stream are ordered, so they may share it.
+// Layout: [0,256) control words (status, work counters), then `scratch_bytes` of payload.
+struct vrhi_stream_t {
+  vrhi_device_t *dev;
+  cudaStream_t s;
+  bool owned;
+  char *arena;           // device memory, or nullptr until first use
+  size_t arena_payload;  // payload bytes available behind the control block
+  uint64_t launches;
+};
+
+struct vrhi_event_t {
+  vrhi_device_t *dev;
+  cudaEvent_t e;
+};
+
+namespace vrhi {
+
+constexpr size_t kCtrlBytes = 256;
+// control-word indices (uint32) inside the arena's control block
+enum { CTRL_STATUS = 0, CTRL_WORK0 = 1, CTRL_WORK1 = 2, CTRL_DONE = 3 };
+
+int fail(int code, const char *fmt, ...) __attribute__((format(printf, 2, 3)));
+void clear_error();
+
+#define VRHI_CUDA(call)                                                                   \
+  do {                                                                                    \
+    cudaError_t e__ = (call);                                                             \
+    if (e__ != cudaSuccess)                                                               \
+      return ::vrhi::fail(e__ == cudaErrorMemoryAllocation ? VRHI_ERR_OOM : VRHI_ERR_CUDA, \
+                          "%s failed: %s", #call, cudaGetErrorString(e__));               \
+  } while (0)
+
+#define VRHI_TRY(expr)            \
+  do {                            \
+    int rc__ = (expr);            \
+    if (rc__ != VRHI_OK) return rc__; \
+  } while (0)
+
+// Ensure the stream's arena holds `payload` bytes; returns control block and payload pointers.
+int stream_arena(vrhi_stream_t *st, size_t payload, uint32_t **ctrl, char **payload_ptr);
+
+struct ArgView {
+  char *ptr;
+  uint64_t bytes;
+  int cls;       // class the caller declared for this use
+  int buf_cls;   // class the buffer was created with
+};
+
+inline bool writable(const ArgView &a) {
+  return a.buf_cls != VRHI_INPUT && a.buf_cls != VRHI_UNIFORM && a.buf_cls != VRHI_UNIFORM_CONSTANT;
+}
+
+typedef int (*LaunchFn)(vrhi_stream_t *st, const ArgView *args, int n_args, const void *params,
+                        size_t params_size);
+
+struct OpDef {
+  const char *name;
+  const char *signature;
+  LaunchFn launch;
+};
+
+// Operator launchers, one per kernel family (defined in the k_*.cu files).
+int launch_escape_time(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
+int launch_fused_map(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
+int launch_map_tape(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
+int launch_row_sum(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
+int launch_row_max(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
+int launch_row_softmax(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
+int launch_row_stats_softmax(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
+int launch_col_sum(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
+int launch_mse_tanh_fwd(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
+int launch_mse_tanh_bwd(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
+int launch_fp32_probe(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
+
+// Copies a caller's parameter block into a zero-initialised struct of the current layout,
+// honouring the leading size field (older, shorter callers leave new fields zero).
+template <class P>
+int read_params(const void *params, size_t params_size, P *out) {
+  *out = P{};
+  if (!params || params_size < sizeof(uint32_t)) return fail(VRHI_ERR_INVALID, "missing parameter block");
+  uint32_t declared = *static_cast<const uint32_t *>(params);
+  if (declared > params_size) return fail(VRHI_ERR_SIZE, "parameter block declares %u bytes but %zu were passed", declared, params_size);
+  size_t n = declared < sizeof(P) ? declared : sizeof(P);
+  memcpy(out, params, n);
+  return VRHI_OK;
+}
+
+inline int post_launch(vrhi_stream_t *st, const char *what, int kernels = 1) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(VRHI_ERR_CUDA, "launch of %s failed: %s", what, cudaGetErrorString(e));
+  st->launches += (uint64_t)kernels;
+  return VRHI_OK;
+}
+
+}  // namespace vrhi

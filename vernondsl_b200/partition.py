@@ -1,0 +1,102 @@
+"""Single-box multi-GPU partitioner: one process per GPU, ``torch.distributed`` for the exchange.
+
+Work is split by the planner inside ``libvrhi.so`` (``vrhi_partition_rows`` /
+``vrhi_partition_leading``); this module adds the only exchange steps the path has:
+
+* escape-time images: every rank computes its own row chunks into a full-size image at their
+  true position, then the chunks are all-gathered in place (no staging copy, no permutation);
+* the tanh-MSE backward: ``db`` and the loss are all-reduced (sum); ``dW`` and ``dx`` stay sharded.
+
+Map and row operators need no exchange: each rank owns a slice of the leading axis.
+Collectives run on tensors that alias the library's buffers, on whatever backend the process
+group was created with (NCCL on GPUs; gloo in the CPU tests of this logic).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Tuple
+
+from . import _lib as L
+from . import ops
+
+
+@dataclass(frozen=True)
+class ImagePlan:
+    """Row ownership of one rank for an image of ``height`` rows."""
+    height: int
+    world: int
+    rank: int
+    scheme: int
+    part: L.RowPartition
+
+    def chunks(self) -> List[Tuple[int, int]]:
+        """(first_row, n_rows) of every chunk this rank owns, in launch order."""
+        p, out = self.part, []
+        for k in range(p.chunk_count):
+            c = p.chunk_first + k * p.chunk_step
+            r0 = c * p.chunk_rows
+            out.append((r0, min(self.height, r0 + p.chunk_rows) - r0))
+        return out
+
+
+def plan_image(height: int, world: int, rank: int, scheme: int = L.PART_CYCLIC, chunk_rows: int = 128) -> ImagePlan:
+    """Cyclic chunks by default: escape-time cost varies smoothly over the image, so dealing
+    128-row chunks round-robin balances ranks where equal contiguous bands do not."""
+    return ImagePlan(height, world, rank, scheme, ops.partition_rows(height, world, rank, scheme, chunk_rows))
+
+
+def owner_of_row(plan: ImagePlan, row: int) -> int:
+    """Rank that computes image row ``row`` under ``plan``'s scheme (the same for every rank)."""
+    c = row // plan.part.chunk_rows
+    return c % plan.world if plan.scheme == L.PART_CYCLIC else c
+
+
+def all_gather_image(image, plan: ImagePlan, group=None, async_op: bool = False):
+    """All-gather the row chunks of ``image`` (a [height, width] tensor holding this rank's chunks
+    at their true rows) so that every rank ends with the whole image.
+
+    Cyclic plans whose chunk count divides evenly gather IN PLACE: the image viewed as
+    [slab, rank, chunk_rows*width] already has rank r's data at [:, r, :], which is exactly the
+    output layout of an all-gather of each slab.  Anything else falls back to one broadcast per
+    chunk from its owner.  Returns the list of work handles when ``async_op``.
+    """
+    import torch.distributed as dist
+
+    world, p = plan.world, plan.part
+    if world == 1:
+        return []
+    height, width = image.shape
+    works = []
+    n_chunks = -(-height // p.chunk_rows)
+    even = plan.scheme == L.PART_CYCLIC and height % p.chunk_rows == 0 and n_chunks % world == 0
+    if even:
+        slabs = image.view(n_chunks // world, world, p.chunk_rows * width)
+        for k in range(slabs.shape[0]):
+            w = dist.all_gather_into_tensor(slabs[k].view(-1), slabs[k, plan.rank], group=group, async_op=async_op)
+            if async_op:
+                works.append(w)
+    else:
+        for c in range(n_chunks):
+            r0 = c * p.chunk_rows
+            r1 = min(height, r0 + p.chunk_rows)
+            src = c % world if plan.scheme == L.PART_CYCLIC else c  # contiguous: chunk c is rank c's band
+            src_global = dist.get_global_rank(group, src) if group is not None else src
+            w = dist.broadcast(image[r0:r1], src=src_global, group=group, async_op=async_op)
+            if async_op:
+                works.append(w)
+    return works
+
+
+def all_reduce_sum(tensors, group=None) -> None:
+    """Sum small per-rank partials (db, loss, reduction partials) across ranks, in place."""
+    import torch.distributed as dist
+
+    if dist.get_world_size(group) == 1:
+        return
+    for t in tensors:
+        dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
+
+
+def leading_slice(n: int, world: int, rank: int) -> Tuple[int, int]:
+    """(begin, count) of this rank's share of a leading axis of length n."""
+    return ops.partition_leading(n, world, rank)

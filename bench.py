@@ -230,8 +230,80 @@ def other_workloads(dev, st, torch, hbm_peak, peak_kind, fp32_peak):
     return out
 
 
+def run_only(args):
+    """One kernel family at a reduced size, a few launches: the command ncu captures are taken from."""
+    import torch
+
+    import vernondsl_b200 as vd
+    from vernondsl_b200 import _lib as L
+    from vernondsl_b200 import ops
+
+    dev = vd.Device(0)
+    st = dev.stream()
+    device = "cuda:0"
+    gen = torch.Generator(device=device)
+    gen.manual_seed(7)
+    rn = lambda *shape: torch.randn(shape, generator=gen, device=device, dtype=torch.float32)
+    name, it = args.only, args.iters
+    res = {"only": name, "scale": args.scale}
+    if name in ("escape_julia", "escape_mandelbrot"):
+        side = max(256, int(16384 * args.scale) // 128 * 128)
+        if name == "escape_julia":
+            W = H = side
+            dx, dy = ops.grid_steps(-1.6, 1.6, -1.6, 1.6, W, H)
+            p = ops.escape_params(L.JULIA, W, H, -1.6, -1.6, dx, dy, cr=-0.8, ci=0.156, max_iter=4096)
+        else:
+            W, H = 1920, 1080
+            dx, dy = ops.grid_steps(-2.5, 1.0, -1.0, 1.0, W, H)
+            p = ops.escape_params(L.MANDELBROT, W, H, -2.5, -1.0, dx, dy, max_iter=256)
+        img = dev.empty((H, W), np.uint32, L.IMAGE)
+        res["ms"] = time_launches(dev, st, lambda: ops.escape_time(st, img, p), it, warmup=1)
+        res["shape"] = [H, W]
+    elif name in ("fused_map", "map_tape"):
+        n = int((1 << 28) * args.scale) // 4096 * 4096
+        a, x, y, o = rn(n), rn(n), rn(n), torch.empty(n, device=device)
+        A, X, Y, O = (dev.wrap_tensor(t) for t in (a, x, y, o))
+        if name == "fused_map":
+            fn = lambda: ops.fused_map(st, A, X, Y, O, n)
+        else:
+            t = ops.Tape(3)
+            u = t.op("fma", t.input(0), t.input(1), t.input(2))
+            e = t.op("exp", t.op("mul", t.op("mul", t.const(-0.5), t.input(1)), t.input(1)))
+            q = t.op("sqrt", t.op("add", t.op("abs", t.input(2)), t.const(1e-3)))
+            t.output(t.op("fma", t.op("tanh", u), e, q))
+            fn = lambda: ops.map_tape(st, t, [A, X, Y], [O], n // 4096, 4096)
+        res["ms"] = time_launches(dev, st, fn, it, warmup=1)
+        res["gbs"] = 16 * n / res["ms"] / 1e6
+    elif name.startswith("row_"):
+        R, Cc = max(8, int(65536 * args.scale)), 4096
+        m, sm = rn(R, Cc) * 2, torch.empty((R, Cc), device=device)
+        rs, rm = torch.empty(R, device=device), torch.empty(R, device=device)
+        M, SM, RS, RM = (dev.wrap_tensor(t) for t in (m, sm, rs, rm))
+        fn = {"row_sum": lambda: ops.row_sum(st, M, RS, R, Cc), "row_max": lambda: ops.row_max(st, M, RM, R, Cc),
+              "row_softmax": lambda: ops.row_softmax(st, M, SM, R, Cc),
+              "row_stats_softmax": lambda: ops.row_stats_softmax(st, M, RS, RM, SM, R, Cc)}[name]
+        res["ms"] = time_launches(dev, st, fn, it, warmup=1)
+        res["gbs"] = (8 if "softmax" in name else 4) * R * Cc / res["ms"] / 1e6
+    elif name in ("mse_fwd", "mse_bwd"):
+        R, Cc = max(8, int(32768 * args.scale)), 4096
+        Wt, xt, tt, bt = rn(R, Cc), rn(R, Cc), rn(R, Cc), rn(Cc)
+        dWt, dxt, dbt, lt = torch.empty_like(Wt), torch.empty_like(Wt), torch.empty(Cc, device=device), torch.empty(4, device=device)
+        bW, bx, bb, bt_, bdW, bdx, bdb, bl = (dev.wrap_tensor(t) for t in (Wt, xt, bt, tt, dWt, dxt, dbt, lt))
+        fn = (lambda: ops.mse_tanh_fwd(st, bW, bx, bb, bt_, bl, R, Cc)) if name == "mse_fwd" else \
+            (lambda: ops.mse_tanh_bwd(st, bW, bx, bb, bt_, bdW, bdx, bdb, R, Cc))
+        res["ms"] = time_launches(dev, st, fn, it, warmup=1)
+        res["gbs"] = (12 if name == "mse_fwd" else 20) * R * Cc / res["ms"] / 1e6
+    else:
+        raise SystemExit(f"unknown --only {name}")
+    st.check()
+    print(json.dumps(res), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default=None, help="run one kernel family at reduced size (for profiling) and exit")
+    ap.add_argument("--scale", type=float, default=0.25, help="with --only: fraction of the full workload size")
+    ap.add_argument("--iters", type=int, default=3, help="with --only: timed launches")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
@@ -242,6 +314,9 @@ def main():
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
+        return
+    if args.only:
+        run_only(args)
         return
 
     import torch

@@ -194,7 +194,11 @@ typedef struct vrhi_escape_params {
   float bound;
   float color_scale;
   uint32_t chunk_rows, chunk_first, chunk_step, chunk_count;
+  uint32_t flags; /* VRHI_ESCAPE_FLAG_* */
 } vrhi_escape_params;
+/* Run the kernel that tests on every step even where the faster regrouping kernel applies
+ * (exact mode, NORM2_GT with bound >= 4, |c| <= 1.5).  Results are identical either way. */
+#define VRHI_ESCAPE_FLAG_CHECKED_ONLY 1u
 
 /* op "fused_map" -- the map chain  out = tanh(a*x + y) * exp(-0.5*x*x) + sqrt(|y| + 1e-3)
  * as one kernel.  args: [0] a, [1] x, [2] y (INPUT, n floats), [3] out (OUTPUT, n floats). */

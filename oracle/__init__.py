@@ -56,6 +56,7 @@ def lib():
                                      C.c_int, C.c_float, C.c_uint32, C.c_uint32, C.c_uint32, up]
         L.vo_escape_color.argtypes = [up, C.c_size_t, C.c_float, fp]
         L.vo_fused_map_f64.argtypes = [fp, fp, fp, C.c_size_t, fp, fp]
+        L.vo_fused_map_bound.argtypes = [fp, fp, fp, C.c_size_t, C.c_double, dp]
         L.vo_unary_f64.argtypes = [C.c_int, fp, C.c_size_t, fp]
         L.vo_unary_f64.restype = C.c_int
         for name in ("vo_row_sum", "vo_row_max", "vo_row_softmax", "vo_col_sum"):
@@ -121,6 +122,17 @@ def fused_map(a, x, y, want_scale=False):
     lib().vo_fused_map_f64(pa, px, py, a.size, out.ctypes.data_as(C.POINTER(C.c_float)),
                            scale.ctypes.data_as(C.POINTER(C.c_float)) if want_scale else None)
     return (out, scale) if want_scale else out
+
+
+def fused_map_bound(a, x, y, ulps=2.0):
+    """Absolute error bound of the fused chain when each primitive map in it is within ``ulps`` ulp
+    (first-order propagation, evaluated in binary64)."""
+    a, pa = _f32(a)
+    x, px = _f32(x)
+    y, py = _f32(y)
+    out = np.empty(a.shape, dtype=np.float64)
+    lib().vo_fused_map_bound(pa, px, py, a.size, float(ulps), out.ctypes.data_as(C.POINTER(C.c_double)))
+    return out
 
 
 def unary(op, x):

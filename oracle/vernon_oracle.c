@@ -156,6 +156,43 @@ VO_EXPORT void vo_fused_map_f64(const float *a, const float *x, const float *y, 
   }
 }
 
+static double ulp32(double v) {
+  /* spacing of binary32 numbers at magnitude |v| (normal range) */
+  int e;
+  v = fabs(v);
+  if (v < 1.17549435e-38) return 1.40129846e-45;
+  frexp(v, &e);           /* v = m * 2^e, m in [0.5, 1) */
+  return ldexp(1.0, e - 24);
+}
+
+/*
+ * Forward error bound of the same chain when every primitive map in it (the fused multiply-add
+ * a*x+y, tanh, the product x*x scaled by -0.5, exp, |y|+1e-3, sqrt, and the final fused
+ * multiply-add) returns a value within `ulps` units in the last place of the correctly rounded
+ * binary32 result for the inputs it was given.  First-order propagation:
+ *     bound = ulps * sum over intermediates t of |d out / d t| * ulp32(t)
+ * This is what "each map within N ulp" implies for the composite; an ulp of the final value
+ * alone is not a usable unit because tanh(.)*exp(.) and sqrt(.) can cancel.
+ */
+VO_EXPORT void vo_fused_map_bound(const float *a, const float *x, const float *y, size_t n,
+                                  double ulps, double *bound) {
+  const double kh = (double)-0.5f, ke = (double)1e-3f;
+#pragma omp parallel for schedule(static)
+  for (int64_t k = 0; k < (int64_t)n; ++k) {
+    double A = a[k], X = x[k], Y = y[k];
+    double u = A * X + Y, th = tanh(u), v = kh * X * X, e = exp(v);
+    double w = fabs(Y) + ke, q = sqrt(w), o = th * e + q;
+    double b = ulp32(u) * (1.0 - th * th) * e   /* u  -> tanh -> product */
+             + ulp32(th) * e                    /* tanh result           */
+             + ulp32(v) * e * fabs(th)          /* v  -> exp -> product  */
+             + ulp32(e) * fabs(th)              /* exp result            */
+             + ulp32(w) / (2.0 * q)             /* w  -> sqrt            */
+             + ulp32(q)                         /* sqrt result           */
+             + ulp32(o);                        /* final rounding        */
+    bound[k] = ulps * b;
+  }
+}
+
 /* Elementwise primitives in binary64, rounded once (for per-primitive ulp checks). */
 enum { VO_U_TANH = 0, VO_U_EXP = 1, VO_U_SQRT = 2, VO_U_ABS = 3, VO_U_NEG = 4, VO_U_SQUARE = 5,
        VO_U_RECIP = 6, VO_U_LOG = 7, VO_U_SIGMOID = 8, VO_U_RELU = 9, VO_U_COS = 10,

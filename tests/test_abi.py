@@ -126,7 +126,7 @@ def test_struct_layouts_match_the_header():
     # sizes a C compiler gives the structs of include/vrhi.h (checked against a compiled probe in CI is
     # not possible without a host compiler run; these are the natural-alignment sizes)
     assert C.sizeof(L.Arg) == 32
-    assert C.sizeof(L.EscapeParams) == 80
+    assert C.sizeof(L.EscapeParams) == 84
     assert C.sizeof(L.MapParams) == 16
     assert C.sizeof(L.RowsParams) == 24
     assert C.sizeof(L.MseParams) == 32

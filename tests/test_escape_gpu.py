@@ -36,6 +36,33 @@ def test_counts_equal_oracle(dev, stream, name):
     assert int(got.sum(dtype=np.uint64)) == total
 
 
+@pytest.mark.parametrize("name", ["mandelbrot_1080p", "julia_512", "mandelbrot_ragged"])
+def test_step_by_step_kernel_equals_oracle_too(dev, stream, name):
+    """The same workloads forced onto the kernel that tests on every step."""
+    kind, W, H, x0, y0, dx, dy, kw = workload(name)
+    got = run_gpu(dev, stream, kind, W, H, x0, y0, dx, dy, checked_only=True, **kw)
+    want, _ = oracle.escape_time(kind, W, H, x0, y0, dx, dy, kw["cr"], kw["ci"], kw["max_iter"])
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("max_iter", [2, 7, 8, 9, 15, 16, 17, 100])
+def test_max_iter_around_the_block_length(dev, stream, max_iter):
+    """Counts that stop at max_iter inside, at the edge of and just past an unchecked block."""
+    dx, dy = oracle.grid_steps(-1.6, 1.6, -1.6, 1.6, 260, 96)
+    for kind, cr, ci in ((L.JULIA, -0.8, 0.156), (L.JULIA, 0.0, 0.0), (L.MANDELBROT, 0.0, 0.0)):
+        got = run_gpu(dev, stream, kind, 260, 96, -1.6, -1.6, dx, dy, cr=cr, ci=ci, max_iter=max_iter)
+        want, _ = oracle.escape_time(kind, 260, 96, -1.6, -1.6, dx, dy, cr, ci, max_iter)
+        assert np.array_equal(got, want)
+
+
+def test_interior_heavy_image(dev, stream):
+    """Nearly every pixel runs to max_iter (a zoom into the set): the pool stays full throughout."""
+    dx, dy = oracle.grid_steps(-0.2, 0.2, -0.2, 0.2, 384, 128)
+    got = run_gpu(dev, stream, L.MANDELBROT, 384, 128, -0.2, -0.2, dx, dy, max_iter=1000)
+    want, _ = oracle.escape_time(oracle.MANDELBROT, 384, 128, -0.2, -0.2, dx, dy, max_iter=1000)
+    assert np.array_equal(got, want) and (want == 1000).mean() > 0.9
+
+
 def test_full_size_julia_equals_golden_digest(dev, stream, golden):
     """16384 x 16384, max_iter 4096: compared through the exact digests the oracle produced, and
     row by row on the stored sample rows."""

@@ -38,7 +38,8 @@ def test_row_ops_match_oracle(dev, stream, rows, cols):
     s2, mx2, sm2 = dev.empty(rows, np.float32), dev.empty(rows, np.float32), dev.empty((rows, cols), np.float32)
     ops.row_stats_softmax(stream, M, s2, mx2, sm2, rows, cols)
     stream.check()
-    assert np.array_equal(s2.download(), s.download())
+    # (the one-pass kernel groups the row differently across warps, so its sum may round differently)
+    assert (np.abs(s2.download() - want_sum) <= RTOL * scale + 1e-30).all()
     assert np.array_equal(mx2.download(), mx.download())
     assert np.array_equal(sm2.download(), got)
     for b in (M, s, mx, sm, s2, mx2, sm2):
@@ -99,13 +100,13 @@ def test_col_sum_matches_oracle(dev, stream, rows, cols):
 
 
 def test_rows_errors_and_empty(dev, stream):
-    M = dev.from_numpy(np.zeros((4, 8), np.float32))
-    small = dev.empty(2, np.float32)
+    M = dev.from_numpy(np.zeros((8, 8), np.float32))
+    small = dev.empty(2, np.float32)  # allocations are at least 16 bytes: room for 4 row results, not 8
     with pytest.raises(L.VrhiError) as e:
-        ops.row_sum(stream, M, small, 4, 8)
-    assert e.value.status == L.ERR_SIZE
+        ops.row_sum(stream, M, small, 8, 8)
+    assert e.value.status == L.ERR_SIZE and "argument 1" in e.value.message
     with pytest.raises(L.VrhiError) as e:
-        ops.row_sum(stream, M, small, 8, 8)  # input too small for the declared shape
-    assert e.value.status == L.ERR_SIZE
+        ops.row_sum(stream, M, small, 16, 8)  # input too small for the declared shape
+    assert e.value.status == L.ERR_SIZE and "input" in e.value.message
     ops.row_sum(stream, M, small, 0, 8)  # zero rows: nothing to do, not an error
     stream.check()

@@ -26,6 +26,7 @@ INPUT, OUTPUT, UNIFORM, UNIFORM_CONSTANT, STORAGE_BUFFER, IMAGE, VARYING = range
 
 MANDELBROT, JULIA = 0, 1
 EXACT, FAST = 0, 1
+ESCAPE_FLAG_CHECKED_ONLY = 1
 TEST_NORM2_GT, TEST_NORM_GE = 0, 1
 OUT_COUNT_U32, OUT_COUNT_U16, OUT_COLOR_F32 = 0, 1, 2
 PART_CONTIGUOUS, PART_CYCLIC = 0, 1
@@ -64,7 +65,7 @@ class EscapeParams(C.Structure):
                 ("max_iter", C.c_uint32), ("x0", C.c_float), ("y0", C.c_float), ("dx", C.c_float),
                 ("dy", C.c_float), ("cr", C.c_float), ("ci", C.c_float), ("bound", C.c_float),
                 ("color_scale", C.c_float), ("chunk_rows", C.c_uint32), ("chunk_first", C.c_uint32),
-                ("chunk_step", C.c_uint32), ("chunk_count", C.c_uint32)]
+                ("chunk_step", C.c_uint32), ("chunk_count", C.c_uint32), ("flags", C.c_uint32)]
 
 
 class MapParams(C.Structure):

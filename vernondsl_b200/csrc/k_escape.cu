@@ -14,7 +14,9 @@
 // This file holds the fully checked kernel: one pixel per lane, a test on every step.  It accepts
 // every parameter combination and is the path of record for parameters the regrouping kernel
 // cannot take.
+#include <cstdlib>
 #include <cstring>
+#include <type_traits>
 
 #include "vrhi_internal.h"
 
@@ -112,6 +114,216 @@ __global__ void __launch_bounds__(256) escape_checked_kernel(EscapeDev p, void *
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Regrouping kernel (exact mode, test "a+b > bound" with bound >= 4, |c| <= 1.5).
+//
+// Iteration counts inside a warp differ by orders of magnitude near the set, so one pixel per lane
+// with a test on every step leaves most lanes idle (about 36 % lane efficiency on the 16384^2
+// Julia workload).  This kernel keeps lanes busy and spends fewer instructions per step:
+//
+//  * FAST BLOCKS.  A lane runs U updates with no test and no counter: 6 instructions per step
+//    (a=zr*zr, b=zi*zi, t=zr*zi, zi=fma(2,t,ci), a-b, +cr) for 8 algorithmic operations.  One test
+//    at the end of the block decides whether the whole block was valid.  That is exact because,
+//    for bound >= 4 and |c| <= 1.5, escape is monotonic even in binary32: once a+b > bound then
+//    |z'| >= |z|^2 - |c| > 1.2|z|, so every later a+b is larger still, or Inf/NaN, and the test is
+//    written !(s <= bound) so that NaN counts as escaped.  A lane whose block failed the test (or
+//    would pass max_iter) is put back on its checkpoint and marked "finishing".
+//  * CHECKED BLOCKS.  When at least T lanes are finishing or empty, the warp runs one block of U
+//    steps with the test and the counter on every step; lanes still in flight simply advance,
+//    finishing lanes find their exact count.  Finished pixels are stored and their lanes freed.
+//  * POOL.  Freed lanes are refilled from a per-warp ring in shared memory.  The ring is fed by
+//    INTAKE: 32 fresh pixels of a stolen tile run K checked steps in lock step (most pixels of the
+//    far exterior end there and are stored coalesced); survivors are pushed to the ring with their
+//    state.  Long-lived pixels therefore share warps with other long-lived pixels.
+//  * WORK STEALING.  Warps pull batches of 16 tiles (512 pixels of one row) from a global counter.
+//
+// Nothing here waits on another warp or CTA: no spin loops, no barriers.
+constexpr int kPoolCap = 64;
+
+template <int KIND, int OUT, int U, int T>
+__global__ void __launch_bounds__(256) escape_regroup_kernel(EscapeDev p, void *image, uint32_t *work_counter) {
+  constexpr int K = 8;  // checked steps a fresh pixel gets before it is pooled
+  constexpr bool PER_PIXEL_C = (KIND == VRHI_ESCAPE_MANDELBROT);
+  __shared__ float s_zr[8][kPoolCap], s_zi[8][kPoolCap];
+  __shared__ uint32_t s_idx[8][kPoolCap], s_cnt[8][kPoolCap];
+  __shared__ float s_cr[PER_PIXEL_C ? 8 : 1][kPoolCap], s_ci[PER_PIXEL_C ? 8 : 1][kPoolCap];
+  const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+  const uint32_t lt_mask = (1u << lane) - 1u;
+  const uint32_t FULL = 0xffffffffu;
+  float *pzr = s_zr[warp], *pzi = s_zi[warp];
+  uint32_t *pidx = s_idx[warp], *pcnt = s_cnt[warp];
+  float *pcr = s_cr[PER_PIXEL_C ? warp : 0], *pci = s_ci[PER_PIXEL_C ? warp : 0];
+  const float bound = p.bound;
+  const uint32_t max_iter = p.max_iter;
+  const bool cap_far = max_iter >= (uint32_t)K;                       // intake cannot reach the cap
+  const uint32_t fast_limit = max_iter >= (uint32_t)U ? max_iter - U : 0u;  // cnt <= fast_limit: a whole block fits
+  const bool fast_possible = max_iter >= (uint32_t)U;
+
+  // warp-uniform state
+  uint32_t pool_head = 0, pool_tail = 0, pool_n = 0;
+  bool fresh = true;
+  uint32_t tile = 0, tile_end = 0, row_base = 0;
+  float row_y = 0.f;
+  // lane state (a = zr*zr and b = zi*zi ride along so that a step costs six instructions)
+  float zr = 0.f, zi = 0.f, a = 0.f, b = 0.f, cr = p.cr, ci = p.ci;
+  uint32_t cnt = 0, idx = 0;
+  bool occ = false, fin = false;
+
+  auto intake = [&]() {
+    if (tile >= tile_end) {
+      uint32_t batch = 0;
+      if (lane == 0) batch = atomicAdd(work_counter, 1u);
+      batch = __shfl_sync(FULL, batch, 0);
+      if (batch >= p.n_batches) { fresh = false; return; }
+      const uint32_t r = batch / p.batches_per_row;
+      tile = (batch - r * p.batches_per_row) * p.batch_tiles;
+      tile_end = min(tile + p.batch_tiles, p.tiles_per_row);
+      const uint32_t j = owned_row_to_image_row(p, r);
+      row_y = __fadd_rn(p.y0, __fmul_rn((float)j, p.dy));
+      row_base = j * p.width;
+    }
+    const uint32_t i = tile * 32u + lane;
+    ++tile;
+    const bool valid = i < p.width;
+    const float x = __fadd_rn(p.x0, __fmul_rn((float)i, p.dx));
+    float fzr, fzi, fcr, fci;
+    if (PER_PIXEL_C) { fzr = 0.f; fzi = 0.f; fcr = x; fci = row_y; }
+    else { fzr = x; fzi = row_y; fcr = p.cr; fci = p.ci; }
+    uint32_t fcnt = 0;
+    bool flive = valid;
+    if (cap_far) {
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const float fa = __fmul_rn(fzr, fzr), fb = __fmul_rn(fzi, fzi);
+        flive = flive && (__fadd_rn(fa, fb) <= bound);
+        // most tiles lie far outside the set and die within two or three steps, all lanes together
+        if (k >= 2 && (k & 1) == 0 && !__any_sync(FULL, flive)) break;
+        const float ft = __fmul_rn(fzr, fzi);
+        fzi = __fmaf_rn(2.0f, ft, fci);
+        fzr = __fadd_rn(__fsub_rn(fa, fb), fcr);
+        if (flive) ++fcnt;
+      }
+    } else {
+      for (int k = 0; k < K; ++k) {
+        const float fa = __fmul_rn(fzr, fzr), fb = __fmul_rn(fzi, fzi);
+        flive = flive && (__fadd_rn(fa, fb) <= bound) && (fcnt < max_iter);
+        const float ft = __fmul_rn(fzr, fzi);
+        fzi = __fmaf_rn(2.0f, ft, fci);
+        fzr = __fadd_rn(__fsub_rn(fa, fb), fcr);
+        if (flive) ++fcnt;
+      }
+    }
+    if (PER_PIXEL_C) {
+      // pixels whose own constant is too large for the fast path are finished here, step by step
+      bool slow = flive && !(fmaf(fcr, fcr, fci * fci) <= 2.25f);
+      while (__any_sync(FULL, slow)) {
+        if (slow) {
+          const float fa = __fmul_rn(fzr, fzr), fb = __fmul_rn(fzi, fzi);
+          if (!(__fadd_rn(fa, fb) <= bound) || fcnt >= max_iter) { slow = false; flive = false; }
+          else {
+            const float ft = __fmul_rn(fzr, fzi);
+            fzi = __fmaf_rn(2.0f, ft, fci);
+            fzr = __fadd_rn(__fsub_rn(fa, fb), fcr);
+            ++fcnt;
+          }
+        }
+      }
+    }
+    if (valid && !flive) store_count<OUT>(image, (size_t)row_base + i, fcnt, p.color_scale);
+    const uint32_t m = __ballot_sync(FULL, flive);
+    if (m) {
+      if (flive) {
+        const uint32_t slot = (pool_head + __popc(m & lt_mask)) & (kPoolCap - 1);
+        pzr[slot] = fzr; pzi[slot] = fzi; pidx[slot] = row_base + i; pcnt[slot] = fcnt;
+        if (PER_PIXEL_C) { pcr[slot] = fcr; pci[slot] = fci; }
+      }
+      const uint32_t n = __popc(m);
+      pool_head = (pool_head + n) & (kPoolCap - 1);
+      pool_n += n;
+      __syncwarp();
+    }
+  };
+
+  // One block of U steps with the test on every step.  CAP = false is used when no lane can
+  // reach max_iter inside the block, which saves the counter comparison on every step.
+  auto checked_block = [&](auto cap_tag) {
+    constexpr bool CAP = decltype(cap_tag)::value;
+    a = __fmul_rn(zr, zr);  // finishing lanes were put back on their checkpoint: refresh the squares
+    b = __fmul_rn(zi, zi);
+    bool live = occ;
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      live = live && (__fadd_rn(a, b) <= bound);
+      if (CAP) live = live && (cnt < max_iter);
+      if (live) {
+        const float t = __fmul_rn(zr, zi);
+        zi = __fmaf_rn(2.0f, t, ci);
+        zr = __fadd_rn(__fsub_rn(a, b), cr);
+        a = __fmul_rn(zr, zr);
+        b = __fmul_rn(zi, zi);
+        ++cnt;
+      }
+    }
+    // the block made U tests and up to U updates; a lane whose fast block failed only at its very
+    // last state needs the test of that state too (tests are idempotent, so this changes nothing
+    // for lanes that pass)
+    live = live && (__fadd_rn(a, b) <= bound);
+    if (CAP) live = live && (cnt < max_iter);
+    if (occ && !live) {
+      store_count<OUT>(image, (size_t)idx, cnt, p.color_scale);
+      occ = false;
+    }
+    fin = fin && occ;  // a finishing lane always ends inside the block; anything left keeps waiting
+  };
+
+  for (;;) {
+    // ---- refill: feed the pool until every empty lane can be served, then hand out entries
+    const uint32_t free_mask = __ballot_sync(FULL, !occ);
+    if (free_mask) {
+      const uint32_t need = __popc(free_mask);
+      while (pool_n < need && fresh) intake();
+      if (pool_n) {
+        const uint32_t r = __popc(free_mask & lt_mask);
+        if (!occ && r < pool_n) {
+          const uint32_t slot = (pool_tail + r) & (kPoolCap - 1);
+          zr = pzr[slot]; zi = pzi[slot]; idx = pidx[slot]; cnt = pcnt[slot];
+          if (PER_PIXEL_C) { cr = pcr[slot]; ci = pci[slot]; }
+          a = __fmul_rn(zr, zr); b = __fmul_rn(zi, zi);
+          occ = true; fin = false;
+        }
+        const uint32_t popped = min(need, pool_n);
+        pool_tail = (pool_tail + popped) & (kPoolCap - 1);
+        pool_n -= popped;
+        __syncwarp();
+      }
+    }
+    if (__ballot_sync(FULL, occ) == 0u) break;  // pool empty, no fresh tiles, no lane in flight
+    // ---- fast blocks until enough lanes want attention (all of them once nothing can be refilled)
+    const uint32_t threshold = (!fresh && pool_n == 0) ? 32u : (uint32_t)T;
+    uint32_t waiting = __popc(__ballot_sync(FULL, !occ || fin));
+    while (waiting < threshold) {
+      const float ckr = zr, cki = zi;
+#pragma unroll
+      for (int k = 0; k < U; ++k) {
+        const float t = __fmul_rn(zr, zi);
+        zi = __fmaf_rn(2.0f, t, ci);
+        zr = __fadd_rn(__fsub_rn(a, b), cr);
+        a = __fmul_rn(zr, zr);
+        b = __fmul_rn(zi, zi);
+      }
+      // lanes that are not running (empty or finishing) computed garbage: they, and lanes whose
+      // block failed, go back to the checkpoint; a and b are refreshed by the checked block
+      const bool ok = occ && !fin && (__fadd_rn(a, b) <= bound) && fast_possible && (cnt <= fast_limit);
+      if (ok) cnt += U;
+      else { zr = ckr; zi = cki; fin = occ; }
+      waiting = __popc(__ballot_sync(FULL, !ok));
+    }
+    // ---- one checked block: finishing lanes find their exact count, the others just advance
+    if (__any_sync(FULL, occ && (!fast_possible || cnt > fast_limit))) checked_block(std::true_type{});
+    else checked_block(std::false_type{});
+  }
+}
+
 template <int KIND, int MODE, int TEST>
 static void launch_checked_out(int out, int grid, cudaStream_t s, const EscapeDev &p, void *image, uint32_t *ctr) {
   switch (out) {
@@ -181,6 +393,50 @@ int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const
   const int sms = st->dev->prop.multiProcessorCount;
   uint64_t warps_needed = nb;
   int grid = (int)((warps_needed + 7) / 8 < (uint64_t)sms * 8 ? (warps_needed + 7) / 8 : (uint64_t)sms * 8);
+  // The regrouping kernel takes what its exactness argument covers; everything else, and callers
+  // that ask for it, runs the step-by-step kernel.
+  const double c2 = (double)q.cr * q.cr + (double)q.ci * q.ci;
+  const bool regroup_ok = q.mode == VRHI_ESCAPE_EXACT && q.test == VRHI_TEST_NORM2_GT && q.bound >= 4.0f && q.bound < 3.0e38f &&
+                          q.max_iter <= (1u << 30) && (uint64_t)q.width * q.height <= 0xffffffffull &&
+                          (q.kind == VRHI_ESCAPE_MANDELBROT || c2 <= 2.25) && !(q.flags & VRHI_ESCAPE_FLAG_CHECKED_ONLY);
+  if (regroup_ok) {
+    // 6 CTAs of 256 threads fit per SM at this register count; fewer warps than that when the image is small
+    uint64_t ctas = (nb + 7) / 8;
+    uint64_t cap = (uint64_t)sms * 6;
+    grid = (int)(ctas < cap ? ctas : cap);
+    // Tuning aid: VRHI_ESCAPE_TUNE="U,T[,ctas_per_sm]" selects another block length / refill threshold for
+    // uint32 output (the shipped default is what measurements on B200 favoured).
+    if (const char *tune = getenv("VRHI_ESCAPE_TUNE")) {
+      int tu = 0, tt = 0, tc = 0;
+      int got = sscanf(tune, "%d,%d,%d", &tu, &tt, &tc);
+      if (got >= 2 && q.output == VRHI_OUT_COUNT_U32) {
+        if (got == 3 && tc > 0) { cap = (uint64_t)sms * tc; grid = (int)(ctas < cap ? ctas : cap); }
+        bool hit = true;
+#define TUNE(UU, TT)                                                                                                   \
+  else if (tu == UU && tt == TT) {                                                                                     \
+    if (q.kind == VRHI_ESCAPE_MANDELBROT) escape_regroup_kernel<VRHI_ESCAPE_MANDELBROT, VRHI_OUT_COUNT_U32, UU, TT><<<grid, 256, 0, st->s>>>(p, args[0].ptr, counter); \
+    else escape_regroup_kernel<VRHI_ESCAPE_JULIA, VRHI_OUT_COUNT_U32, UU, TT><<<grid, 256, 0, st->s>>>(p, args[0].ptr, counter); \
+  }
+        if (false) {}
+        TUNE(4, 8) TUNE(8, 4) TUNE(8, 12) TUNE(8, 16) TUNE(12, 8) TUNE(12, 12) TUNE(16, 8) TUNE(16, 12) TUNE(16, 16) TUNE(24, 12) TUNE(32, 16)
+        else hit = false;
+#undef TUNE
+        if (hit) return post_launch(st, "escape_time (regrouping, tuned)");
+      }
+    }
+#define REGROUP(KIND, OUT) escape_regroup_kernel<KIND, OUT, 8, 8><<<grid, 256, 0, st->s>>>(p, args[0].ptr, counter)
+    if (q.kind == VRHI_ESCAPE_MANDELBROT) {
+      if (q.output == VRHI_OUT_COUNT_U32) REGROUP(VRHI_ESCAPE_MANDELBROT, VRHI_OUT_COUNT_U32);
+      else if (q.output == VRHI_OUT_COUNT_U16) REGROUP(VRHI_ESCAPE_MANDELBROT, VRHI_OUT_COUNT_U16);
+      else REGROUP(VRHI_ESCAPE_MANDELBROT, VRHI_OUT_COLOR_F32);
+    } else {
+      if (q.output == VRHI_OUT_COUNT_U32) REGROUP(VRHI_ESCAPE_JULIA, VRHI_OUT_COUNT_U32);
+      else if (q.output == VRHI_OUT_COUNT_U16) REGROUP(VRHI_ESCAPE_JULIA, VRHI_OUT_COUNT_U16);
+      else REGROUP(VRHI_ESCAPE_JULIA, VRHI_OUT_COLOR_F32);
+    }
+#undef REGROUP
+    return post_launch(st, "escape_time (regrouping)");
+  }
   if (q.kind == VRHI_ESCAPE_MANDELBROT) {
     if (q.mode == VRHI_ESCAPE_EXACT) launch_checked_test<VRHI_ESCAPE_MANDELBROT, VRHI_ESCAPE_EXACT>(q.test, q.output, grid, st->s, p, args[0].ptr, counter);
     else launch_checked_test<VRHI_ESCAPE_MANDELBROT, VRHI_ESCAPE_FAST>(q.test, q.output, grid, st->s, p, args[0].ptr, counter);

@@ -11,13 +11,51 @@
 
 namespace vrhi {
 
+// exp(x) to well under one ulp in the normal range: n = round(x*log2e), r = x - n*ln2 with a
+// two-constant split (both steps exact or fused), exp(r) = 1 + (r + r*r*q(r)) with the Taylor
+// polynomial through r^7 (|r| <= 0.3466, next term < 2^-27), scaled by 2^n in two exact factors.
+__device__ __forceinline__ float exp_sub_ulp(float x) {
+  x = fminf(fmaxf(x, -104.0f), 88.72f);
+  const float t = fmaf(x, 1.442695041f, 12582912.0f);
+  const float n = t - 12582912.0f;
+  float r = fmaf(n, -0.693145752f, x);
+  r = fmaf(n, -1.42860677e-06f, r);
+  float q = 1.98412698e-4f;
+  q = fmaf(q, r, 1.38888889e-3f);
+  q = fmaf(q, r, 8.33333333e-3f);
+  q = fmaf(q, r, 4.16666667e-2f);
+  q = fmaf(q, r, 1.66666667e-1f);
+  q = fmaf(q, r, 0.5f);
+  const float p = fmaf(r * r, q, r);
+  const float res = 1.0f + p;
+  const int ni = (int)n, h = ni / 2;
+  return res * __int_as_float((h + 127) << 23) * __int_as_float((ni - h + 127) << 23);
+}
+
+// 1 / (1 + exp(-x)): the rounding of 1 + E is recovered (two-sum) and folded into one Newton
+// step on the reciprocal, so that the result carries little more than the error of E itself.
+__device__ __forceinline__ float sigmoid_accurate(float x) {
+  const float e = exp_sub_ulp(-x);
+  const float d = 1.0f + e;
+  const float dl = (e > 1.0f) ? (e - d) + 1.0f : (1.0f - d) + e;
+  const float r = 1.0f / d;
+  const float err = fmaf(-d, r, 1.0f);
+  return fmaf(r, err - dl * r, r);
+}
+
 __device__ __forceinline__ float4 ld_stream(const float4 *p) { return __ldcs(p); }
 __device__ __forceinline__ void st_stream(float4 *p, float4 v) { __stcs(p, v); }
 
 __device__ __forceinline__ float chain_one(float a, float x, float y) {
   float u = fmaf(a, x, y);
   float th = tanhf(u);
-  float e = expf(-0.5f * x * x);
+  // exp(-x*x/2): the product is rounded once (hx = -x/2 is exact), and its rounding error vl,
+  // recovered exactly by the fma, is folded back in as exp(vh + vl) = exp(vh) * (1 + vl)
+  const float hx = -0.5f * x;
+  const float vh = hx * x;
+  const float vl = fmaf(hx, x, -vh);
+  float e = expf(vh);
+  e = fmaf(e, vl, e);
   float q = sqrtf(fabsf(y) + 1e-3f);
   return fmaf(th, e, q);
 }
@@ -140,7 +178,7 @@ __device__ __forceinline__ void tape_run(const TapeDev &T, float4 *slots /* [slo
       case VRHI_T_EXP: TAPE_U(expf(a)); break;
       case VRHI_T_LOG: TAPE_U(logf(a)); break;
       case VRHI_T_TANH: TAPE_U(tanhf(a)); break;
-      case VRHI_T_SIGMOID: TAPE_U(1.0f / (1.0f + expf(-a))); break;
+      case VRHI_T_SIGMOID: TAPE_U(sigmoid_accurate(a)); break;
       case VRHI_T_RELU: TAPE_U(fmaxf(a, 0.0f)); break;
       case VRHI_T_COS: TAPE_U(cosf(a)); break;
       case VRHI_T_SIN: TAPE_U(sinf(a)); break;
@@ -181,7 +219,7 @@ __global__ void __launch_bounds__(kTapeThreads) map_tape_vec_kernel(const __grid
         if ((T.col_vector_mask >> k) & 1u) {
           const float s = T.in[k][r];
           v = make_float4(s, s, s, s);
-        } else if (!((T.row_vector_mask >> k) & 1u) && in_range) {
+        } else if (!(((T.row_vector_mask | T.scalar_mask) >> k) & 1u) && in_range) {
           v = ld_stream(reinterpret_cast<const float4 *>(T.in[k]) + e4);
         }
         slots[T.in_slot[k] * kTapeThreads + tid] = v;

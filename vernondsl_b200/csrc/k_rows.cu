@@ -85,6 +85,100 @@ __global__ void __launch_bounds__(256) row_warp_kernel(const float4 *__restrict_
   }
 }
 
+// exp(x - m) as 2^(x*log2e - m*log2e): one fused multiply-add and one MUFU.EX2 per element.
+// ml = m*log2e is rounded once per row; that rounding is a common factor of every element of the
+// row and cancels in the normalisation.  Relative error per element stays below 2e-6 for
+// |x - m| < 60 (fma rounding of the exponent plus the 2^-22 of ex2.approx).
+__device__ __forceinline__ float exp2_approx(float t) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(t));
+  return r;
+}
+
+// Softmax rows: WPR warps share one row (8 float4 per thread at most), so a 256-thread CTA works
+// on 8/WPR rows at a time with ~64 registers per thread and 32 resident warps per SM: enough
+// independent warps to keep loads in flight while others are in their exp phase.  The row still
+// makes exactly one trip from HBM and one back.  Cross-warp reductions go through three separate
+// shared arrays (sum, max, normaliser), one CTA barrier each; partials are combined in warp
+// order, so results do not depend on scheduling.
+template <int NV, int WPR, int WHAT>
+__global__ void __launch_bounds__(256) row_group_kernel(const float4 *__restrict__ in, float *__restrict__ out_sum,
+                                                        float *__restrict__ out_max, float4 *__restrict__ out_soft,
+                                                        uint64_t rows, uint32_t cols4) {
+  constexpr int GROUPS = 8 / WPR;
+  constexpr uint32_t TPR = 32u * WPR;  // threads per row
+  __shared__ float red_sum[8], red_max[8], red_z[8];
+  const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+  const uint32_t group = warp / WPR, wig = warp % WPR;
+  const uint32_t t = wig * 32u + lane;
+  const float kLog2e = 1.4426950408889634f;
+  for (uint64_t base = (uint64_t)blockIdx.x * GROUPS; base < rows; base += (uint64_t)gridDim.x * GROUPS) {
+    const uint64_t r = base + group;
+    const bool active = r < rows;
+    const float4 *src = in + r * cols4;
+    float4 v[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const uint32_t c = t + TPR * k;
+      v[k] = (active && c < cols4) ? __ldcs(src + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float s = 0.f, mm = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const uint32_t c = t + TPR * k;
+      if (WHAT & ROW_SUM) s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+      if (c < cols4) mm = fmaxf(mm, fmaxf(fmaxf(v[k].x, v[k].y), fmaxf(v[k].z, v[k].w)));
+    }
+    if (WHAT & ROW_SUM) s = warp_sum(s);
+    mm = warp_max(mm);
+    if (WPR > 1) {
+      if (lane == 0) {
+        if (WHAT & ROW_SUM) red_sum[warp] = s;
+        red_max[warp] = mm;
+      }
+      __syncthreads();
+      s = 0.f; mm = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < WPR; ++j) {
+        if (WHAT & ROW_SUM) s += red_sum[group * WPR + j];
+        mm = fmaxf(mm, red_max[group * WPR + j]);
+      }
+    }
+    if (active && t == 0) {
+      if (WHAT & ROW_SUM) out_sum[r] = s;
+      if (WHAT & ROW_MAX) out_max[r] = mm;
+    }
+    if (WHAT & ROW_SOFTMAX) {
+      const float ml = -mm * kLog2e;
+      float z = 0.f;
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        const uint32_t c = t + TPR * k;
+        if (c < cols4) {
+          v[k].x = exp2_approx(fmaf(v[k].x, kLog2e, ml)); v[k].y = exp2_approx(fmaf(v[k].y, kLog2e, ml));
+          v[k].z = exp2_approx(fmaf(v[k].z, kLog2e, ml)); v[k].w = exp2_approx(fmaf(v[k].w, kLog2e, ml));
+          z += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+        }
+      }
+      z = warp_sum(z);
+      if (WPR > 1) {
+        if (lane == 0) red_z[warp] = z;
+        __syncthreads();
+        z = 0.f;
+#pragma unroll
+        for (int j = 0; j < WPR; ++j) z += red_z[group * WPR + j];
+      }
+      const float inv = 1.0f / z;
+      float4 *dst = out_soft + r * cols4;
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        const uint32_t c = t + TPR * k;
+        if (active && c < cols4) __stcs(dst + c, make_float4(v[k].x * inv, v[k].y * inv, v[k].z * inv, v[k].w * inv));
+      }
+    }
+  }
+}
+
 // Any shape: one 256-thread block per row, scalar accesses, three passes for softmax.
 __device__ __forceinline__ float block_reduce(float v, bool is_max, float *smem) {
   v = is_max ? warp_max(v) : warp_sum(v);
@@ -133,7 +227,31 @@ template <int WHAT>
 static int launch_rows(vrhi_stream_t *st, const float *in, float *osum, float *omax, float *osoft, uint64_t rows, uint64_t cols,
                        const char *name) {
   const int sms = st->dev->prop.multiProcessorCount;
-  if (cols % 4 == 0 && cols <= 4096) {
+  if ((WHAT & ROW_SOFTMAX) && cols % 4 == 0 && cols <= 8192) {
+    const uint32_t cols4 = (uint32_t)(cols / 4);
+    const float4 *i4 = (const float4 *)in;
+    float4 *o4 = (float4 *)osoft;
+    const int wpr = cols4 <= 256 ? 1 : cols4 <= 512 ? 2 : cols4 <= 1024 ? 4 : 8;
+    const uint32_t nv = (cols4 + 32u * wpr - 1) / (32u * wpr);
+    const uint64_t groups = 8 / wpr;
+    uint64_t want = (rows + groups - 1) / groups;
+    uint64_t cap = (uint64_t)sms * 4;  // 4 CTAs of 256 threads are resident per SM at ~64 registers
+    unsigned grid = (unsigned)(want < cap ? want : cap);
+#define GROUP_LAUNCH(NV, WPR) row_group_kernel<NV, WPR, (WHAT | ROW_SOFTMAX)><<<grid, 256, 0, st->s>>>(i4, osum, omax, o4, rows, cols4)
+#define GROUP_NV(WPR)                 \
+  do {                                \
+    if (nv <= 1) GROUP_LAUNCH(1, WPR); \
+    else if (nv <= 2) GROUP_LAUNCH(2, WPR); \
+    else if (nv <= 4) GROUP_LAUNCH(4, WPR); \
+    else GROUP_LAUNCH(8, WPR);        \
+  } while (0)
+    if (wpr == 1) GROUP_NV(1);
+    else if (wpr == 2) GROUP_NV(2);
+    else if (wpr == 4) GROUP_NV(4);
+    else GROUP_NV(8);
+#undef GROUP_NV
+#undef GROUP_LAUNCH
+  } else if (cols % 4 == 0 && cols <= 4096) {
     const uint32_t cols4 = (uint32_t)(cols / 4);
     const uint32_t nv = (cols4 + 31) / 32;
     // softmax keeps the row live across two reductions: fewer resident warps, so more CTAs of

@@ -140,9 +140,9 @@ __global__ void __launch_bounds__(256) escape_checked_kernel(EscapeDev p, void *
 // Nothing here waits on another warp or CTA: no spin loops, no barriers.
 constexpr int kPoolCap = 64;
 
-template <int KIND, int OUT, int U, int T>
-__global__ void __launch_bounds__(256) escape_regroup_kernel(EscapeDev p, void *image, uint32_t *work_counter) {
-  constexpr int K = 8;  // checked steps a fresh pixel gets before it is pooled
+// U = steps per block, T = waiting lanes that trigger a checked block, K = checked steps a fresh pixel gets before it is pooled
+template <int KIND, int OUT, int U, int T, int K = 8>
+__global__ void __launch_bounds__(256, 6) escape_regroup_kernel(EscapeDev p, void *image, uint32_t *work_counter) {
   constexpr bool PER_PIXEL_C = (KIND == VRHI_ESCAPE_MANDELBROT);
   __shared__ float s_zr[8][kPoolCap], s_zi[8][kPoolCap];
   __shared__ uint32_t s_idx[8][kPoolCap], s_cnt[8][kPoolCap];
@@ -153,11 +153,10 @@ __global__ void __launch_bounds__(256) escape_regroup_kernel(EscapeDev p, void *
   float *pzr = s_zr[warp], *pzi = s_zi[warp];
   uint32_t *pidx = s_idx[warp], *pcnt = s_cnt[warp];
   float *pcr = s_cr[PER_PIXEL_C ? warp : 0], *pci = s_ci[PER_PIXEL_C ? warp : 0];
-  const float bound = p.bound;
-  const uint32_t max_iter = p.max_iter;
-  const bool cap_far = max_iter >= (uint32_t)K;                       // intake cannot reach the cap
-  const uint32_t fast_limit = max_iter >= (uint32_t)U ? max_iter - U : 0u;  // cnt <= fast_limit: a whole block fits
-  const bool fast_possible = max_iter >= (uint32_t)U;
+  // parameters live in registers: the hot loops must not go back to the constant bank
+  const float bound = p.bound, x0 = p.x0, dx = p.dx, color_scale = p.color_scale;
+  const uint32_t max_iter = p.max_iter, width = p.width;
+  const uint32_t fast_limit = max_iter - (uint32_t)U;  // the host guarantees max_iter >= U: cnt <= fast_limit means a whole block fits
 
   // warp-uniform state
   uint32_t pool_head = 0, pool_tail = 0, pool_n = 0;
@@ -167,7 +166,8 @@ __global__ void __launch_bounds__(256) escape_regroup_kernel(EscapeDev p, void *
   // lane state (a = zr*zr and b = zi*zi ride along so that a step costs six instructions)
   float zr = 0.f, zi = 0.f, a = 0.f, b = 0.f, cr = p.cr, ci = p.ci;
   uint32_t cnt = 0, idx = 0;
-  bool occ = false, fin = false;
+  bool occ = false;  // the lane holds a pixel
+  bool run = false;  // ... and that pixel may go through unchecked blocks (occ && !run: it is finishing)
 
   auto intake = [&]() {
     if (tile >= tile_end) {
@@ -180,38 +180,29 @@ __global__ void __launch_bounds__(256) escape_regroup_kernel(EscapeDev p, void *
       tile_end = min(tile + p.batch_tiles, p.tiles_per_row);
       const uint32_t j = owned_row_to_image_row(p, r);
       row_y = __fadd_rn(p.y0, __fmul_rn((float)j, p.dy));
-      row_base = j * p.width;
+      row_base = j * width;
     }
     const uint32_t i = tile * 32u + lane;
     ++tile;
-    const bool valid = i < p.width;
-    const float x = __fadd_rn(p.x0, __fmul_rn((float)i, p.dx));
+    const bool valid = i < width;
+    const float x = __fadd_rn(x0, __fmul_rn((float)i, dx));
     float fzr, fzi, fcr, fci;
     if (PER_PIXEL_C) { fzr = 0.f; fzi = 0.f; fcr = x; fci = row_y; }
-    else { fzr = x; fzi = row_y; fcr = p.cr; fci = p.ci; }
+    else { fzr = x; fzi = row_y; fcr = cr; fci = ci; }
     uint32_t fcnt = 0;
     bool flive = valid;
-    if (cap_far) {
+    // K steps with a test on each; dead lanes keep computing (their values are never used), so the
+    // loop body is straight-line code.  The host guarantees max_iter >= K: no cap test in here.
 #pragma unroll
-      for (int k = 0; k < K; ++k) {
-        const float fa = __fmul_rn(fzr, fzr), fb = __fmul_rn(fzi, fzi);
-        flive = flive && (__fadd_rn(fa, fb) <= bound);
-        // most tiles lie far outside the set and die within two or three steps, all lanes together
-        if (k >= 2 && (k & 1) == 0 && !__any_sync(FULL, flive)) break;
-        const float ft = __fmul_rn(fzr, fzi);
-        fzi = __fmaf_rn(2.0f, ft, fci);
-        fzr = __fadd_rn(__fsub_rn(fa, fb), fcr);
-        if (flive) ++fcnt;
-      }
-    } else {
-      for (int k = 0; k < K; ++k) {
-        const float fa = __fmul_rn(fzr, fzr), fb = __fmul_rn(fzi, fzi);
-        flive = flive && (__fadd_rn(fa, fb) <= bound) && (fcnt < max_iter);
-        const float ft = __fmul_rn(fzr, fzi);
-        fzi = __fmaf_rn(2.0f, ft, fci);
-        fzr = __fadd_rn(__fsub_rn(fa, fb), fcr);
-        if (flive) ++fcnt;
-      }
+    for (int k = 0; k < K; ++k) {
+      const float fa = __fmul_rn(fzr, fzr), fb = __fmul_rn(fzi, fzi);
+      flive = flive && (__fadd_rn(fa, fb) <= bound);
+      // most tiles lie far outside the set and die within two or three steps, all lanes together
+      if ((k == 2 || k == 4) && k < K - 1 && !__any_sync(FULL, flive)) break;
+      const float ft = __fmul_rn(fzr, fzi);
+      fzi = __fmaf_rn(2.0f, ft, fci);
+      fzr = __fadd_rn(__fsub_rn(fa, fb), fcr);
+      fcnt += flive ? 1u : 0u;
     }
     if (PER_PIXEL_C) {
       // pixels whose own constant is too large for the fast path are finished here, step by step
@@ -229,7 +220,7 @@ __global__ void __launch_bounds__(256) escape_regroup_kernel(EscapeDev p, void *
         }
       }
     }
-    if (valid && !flive) store_count<OUT>(image, (size_t)row_base + i, fcnt, p.color_scale);
+    if (valid && !flive) store_count<OUT>(image, (size_t)(row_base + i), fcnt, color_scale);
     const uint32_t m = __ballot_sync(FULL, flive);
     if (m) {
       if (flive) {
@@ -244,8 +235,9 @@ __global__ void __launch_bounds__(256) escape_regroup_kernel(EscapeDev p, void *
     }
   };
 
-  // One block of U steps with the test on every step.  CAP = false is used when no lane can
-  // reach max_iter inside the block, which saves the counter comparison on every step.
+  // One block of U steps with the test on every step, straight-line: a lane that has stopped
+  // keeps computing values nobody reads, only its counter is frozen.  CAP = false is used when no
+  // lane can reach max_iter inside the block, which saves the counter comparison on every step.
   auto checked_block = [&](auto cap_tag) {
     constexpr bool CAP = decltype(cap_tag)::value;
     a = __fmul_rn(zr, zr);  // finishing lanes were put back on their checkpoint: refresh the squares
@@ -255,25 +247,21 @@ __global__ void __launch_bounds__(256) escape_regroup_kernel(EscapeDev p, void *
     for (int k = 0; k < U; ++k) {
       live = live && (__fadd_rn(a, b) <= bound);
       if (CAP) live = live && (cnt < max_iter);
-      if (live) {
-        const float t = __fmul_rn(zr, zi);
-        zi = __fmaf_rn(2.0f, t, ci);
-        zr = __fadd_rn(__fsub_rn(a, b), cr);
-        a = __fmul_rn(zr, zr);
-        b = __fmul_rn(zi, zi);
-        ++cnt;
-      }
+      const float t = __fmul_rn(zr, zi);
+      zi = __fmaf_rn(2.0f, t, ci);
+      zr = __fadd_rn(__fsub_rn(a, b), cr);
+      a = __fmul_rn(zr, zr);
+      b = __fmul_rn(zi, zi);
+      cnt += live ? 1u : 0u;
     }
     // the block made U tests and up to U updates; a lane whose fast block failed only at its very
     // last state needs the test of that state too (tests are idempotent, so this changes nothing
     // for lanes that pass)
     live = live && (__fadd_rn(a, b) <= bound);
     if (CAP) live = live && (cnt < max_iter);
-    if (occ && !live) {
-      store_count<OUT>(image, (size_t)idx, cnt, p.color_scale);
-      occ = false;
-    }
-    fin = fin && occ;  // a finishing lane always ends inside the block; anything left keeps waiting
+    if (occ && !live) store_count<OUT>(image, (size_t)idx, cnt, color_scale);
+    occ = live;
+    run = live;  // a finishing lane always ends inside the block
   };
 
   for (;;) {
@@ -289,7 +277,7 @@ __global__ void __launch_bounds__(256) escape_regroup_kernel(EscapeDev p, void *
           zr = pzr[slot]; zi = pzi[slot]; idx = pidx[slot]; cnt = pcnt[slot];
           if (PER_PIXEL_C) { cr = pcr[slot]; ci = pci[slot]; }
           a = __fmul_rn(zr, zr); b = __fmul_rn(zi, zi);
-          occ = true; fin = false;
+          occ = true; run = true;
         }
         const uint32_t popped = min(need, pool_n);
         pool_tail = (pool_tail + popped) & (kPoolCap - 1);
@@ -297,10 +285,10 @@ __global__ void __launch_bounds__(256) escape_regroup_kernel(EscapeDev p, void *
         __syncwarp();
       }
     }
-    if (__ballot_sync(FULL, occ) == 0u) break;  // pool empty, no fresh tiles, no lane in flight
+    uint32_t waiting = __popc(__ballot_sync(FULL, !run));
+    if (waiting == 32u && __ballot_sync(FULL, occ) == 0u) break;  // pool empty, no fresh tiles, no lane in flight
     // ---- fast blocks until enough lanes want attention (all of them once nothing can be refilled)
     const uint32_t threshold = (!fresh && pool_n == 0) ? 32u : (uint32_t)T;
-    uint32_t waiting = __popc(__ballot_sync(FULL, !occ || fin));
     while (waiting < threshold) {
       const float ckr = zr, cki = zi;
 #pragma unroll
@@ -313,13 +301,13 @@ __global__ void __launch_bounds__(256) escape_regroup_kernel(EscapeDev p, void *
       }
       // lanes that are not running (empty or finishing) computed garbage: they, and lanes whose
       // block failed, go back to the checkpoint; a and b are refreshed by the checked block
-      const bool ok = occ && !fin && (__fadd_rn(a, b) <= bound) && fast_possible && (cnt <= fast_limit);
-      if (ok) cnt += U;
-      else { zr = ckr; zi = cki; fin = occ; }
-      waiting = __popc(__ballot_sync(FULL, !ok));
+      run = run && (__fadd_rn(a, b) <= bound) && (cnt <= fast_limit);
+      if (run) cnt += U;
+      else { zr = ckr; zi = cki; }
+      waiting = __popc(__ballot_sync(FULL, !run));
     }
     // ---- one checked block: finishing lanes find their exact count, the others just advance
-    if (__any_sync(FULL, occ && (!fast_possible || cnt > fast_limit))) checked_block(std::true_type{});
+    if (__any_sync(FULL, occ && cnt > fast_limit)) checked_block(std::true_type{});
     else checked_block(std::false_type{});
   }
 }
@@ -380,7 +368,14 @@ int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const
   }
   if (p.rows_owned == 0) return VRHI_OK;  // an empty band is not an error
   p.tiles_per_row = (q.width + 31u) / 32u;
-  p.batch_tiles = 16;
+  {
+    // batch = unit of work stealing: 16 tiles for large images; small images get smaller batches so
+    // that every resident warp still sees several of them and the tail stays short
+    const uint64_t resident_warps = (uint64_t)st->dev->prop.multiProcessorCount * 48;
+    const uint64_t tiles = (uint64_t)p.tiles_per_row * p.rows_owned;
+    uint64_t bt = tiles / (resident_warps * 8);
+    p.batch_tiles = (uint32_t)(bt < 2 ? 2 : bt > 16 ? 16 : bt);
+  }
   p.batches_per_row = (p.tiles_per_row + p.batch_tiles - 1) / p.batch_tiles;
   uint64_t nb = (uint64_t)p.batches_per_row * p.rows_owned;
   if (nb > 0xfffffff0ull) return fail(VRHI_ERR_UNSUPPORTED, "escape_time: image too large for 32-bit batch indices");
@@ -397,7 +392,7 @@ int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const
   // that ask for it, runs the step-by-step kernel.
   const double c2 = (double)q.cr * q.cr + (double)q.ci * q.ci;
   const bool regroup_ok = q.mode == VRHI_ESCAPE_EXACT && q.test == VRHI_TEST_NORM2_GT && q.bound >= 4.0f && q.bound < 3.0e38f &&
-                          q.max_iter <= (1u << 30) && (uint64_t)q.width * q.height <= 0xffffffffull &&
+                          q.max_iter >= 64u && q.max_iter <= (1u << 30) && (uint64_t)q.width * q.height <= 0xffffffffull &&
                           (q.kind == VRHI_ESCAPE_MANDELBROT || c2 <= 2.25) && !(q.flags & VRHI_ESCAPE_FLAG_CHECKED_ONLY);
   if (regroup_ok) {
     // 6 CTAs of 256 threads fit per SM at this register count; fewer warps than that when the image is small
@@ -407,24 +402,27 @@ int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const
     // Tuning aid: VRHI_ESCAPE_TUNE="U,T[,ctas_per_sm]" selects another block length / refill threshold for
     // uint32 output (the shipped default is what measurements on B200 favoured).
     if (const char *tune = getenv("VRHI_ESCAPE_TUNE")) {
-      int tu = 0, tt = 0, tc = 0;
-      int got = sscanf(tune, "%d,%d,%d", &tu, &tt, &tc);
+      int tu = 0, tt = 0, tc = 0, tk = 8;
+      int got = sscanf(tune, "%d,%d,%d,%d", &tu, &tt, &tc, &tk);
       if (got >= 2 && q.output == VRHI_OUT_COUNT_U32) {
-        if (got == 3 && tc > 0) { cap = (uint64_t)sms * tc; grid = (int)(ctas < cap ? ctas : cap); }
+        if (got >= 3 && tc > 0) { cap = (uint64_t)sms * tc; grid = (int)(ctas < cap ? ctas : cap); }
         bool hit = true;
-#define TUNE(UU, TT)                                                                                                   \
-  else if (tu == UU && tt == TT) {                                                                                     \
-    if (q.kind == VRHI_ESCAPE_MANDELBROT) escape_regroup_kernel<VRHI_ESCAPE_MANDELBROT, VRHI_OUT_COUNT_U32, UU, TT><<<grid, 256, 0, st->s>>>(p, args[0].ptr, counter); \
-    else escape_regroup_kernel<VRHI_ESCAPE_JULIA, VRHI_OUT_COUNT_U32, UU, TT><<<grid, 256, 0, st->s>>>(p, args[0].ptr, counter); \
+#define TUNEK(UU, TT, KK)                                                                                              \
+  else if (tu == UU && tt == TT && tk == KK) {                                                                         \
+    if (q.kind == VRHI_ESCAPE_MANDELBROT) escape_regroup_kernel<VRHI_ESCAPE_MANDELBROT, VRHI_OUT_COUNT_U32, UU, TT, KK><<<grid, 256, 0, st->s>>>(p, args[0].ptr, counter); \
+    else escape_regroup_kernel<VRHI_ESCAPE_JULIA, VRHI_OUT_COUNT_U32, UU, TT, KK><<<grid, 256, 0, st->s>>>(p, args[0].ptr, counter); \
   }
+#define TUNE(UU, TT) TUNEK(UU, TT, 8)
         if (false) {}
-        TUNE(4, 8) TUNE(8, 4) TUNE(8, 12) TUNE(8, 16) TUNE(12, 8) TUNE(12, 12) TUNE(16, 8) TUNE(16, 12) TUNE(16, 16) TUNE(24, 12) TUNE(32, 16)
+        TUNE(8, 4) TUNE(8, 8) TUNE(8, 12) TUNE(12, 8) TUNE(12, 12) TUNE(16, 8) TUNE(16, 12) TUNEK(8, 8, 4) TUNEK(8, 8, 6) TUNEK(12, 8, 4) TUNEK(12, 8, 6) TUNEK(12, 8, 12) TUNEK(8, 8, 12) TUNEK(12, 6, 6) TUNEK(12, 10, 6)
         else hit = false;
 #undef TUNE
+#undef TUNEK
         if (hit) return post_launch(st, "escape_time (regrouping, tuned)");
       }
     }
-#define REGROUP(KIND, OUT) escape_regroup_kernel<KIND, OUT, 8, 8><<<grid, 256, 0, st->s>>>(p, args[0].ptr, counter)
+    // U = 12, T = 8, K = 8: the sweep on B200 is flat within 2 % between U = 8..16 and T = 8..12
+#define REGROUP(KIND, OUT) escape_regroup_kernel<KIND, OUT, 12, 8><<<grid, 256, 0, st->s>>>(p, args[0].ptr, counter)
     if (q.kind == VRHI_ESCAPE_MANDELBROT) {
       if (q.output == VRHI_OUT_COUNT_U32) REGROUP(VRHI_ESCAPE_MANDELBROT, VRHI_OUT_COUNT_U32);
       else if (q.output == VRHI_OUT_COUNT_U16) REGROUP(VRHI_ESCAPE_MANDELBROT, VRHI_OUT_COUNT_U16);

@@ -276,6 +276,22 @@ typedef struct vrhi_probe_params {
   uint64_t threads; /* 0 = fill the device */
 } vrhi_probe_params;
 
+/* Column sums without any allocation (no counterpart in the reference).
+ * For callers that cannot afford or are not allowed an allocation at call time: latency-bound
+ * frame or control loops, processes whose device memory was divided up front, code that must
+ * leave the allocator untouched.  out[c] = sum over rows of in[r][c], row-major floats, the same
+ * deterministic two-stage algorithm as the "col_sum" operator, but the per-row-group partial
+ * sums live in a fixed 1 MiB array inside the library image (every GPU that loads the library
+ * holds it until the process exits) instead of the stream arena.  Takes raw device pointers and
+ * a raw CUDA stream handle (NULL = default stream); works on the current device.
+ * Limits: cols <= 262144 (VRHI_ERR_SIZE beyond that); `in` 16-byte aligned.
+ * The first call on a device looks up the array's device address; make that first call before
+ * any stream capture begins.  All calls share the one array: calls whose kernels could overlap
+ * on the GPU (different streams without an ordering between them) race on it.  Nothing in the
+ * array needs clearing: each call writes every partial it later reads. */
+VRHI_API int vrhi_col_sum_static_scratch(const float *in_device, float *out_device, uint64_t rows,
+                                         uint64_t cols, void *cuda_stream);
+
 /* --------------------------------------------------------------- partitioning ----------- */
 /* Host-side planning for N devices in one box, one process per device.  No CUDA calls. */
 enum { VRHI_PART_CONTIGUOUS = 0, VRHI_PART_CYCLIC = 1 };

@@ -148,6 +148,7 @@ PROTOTYPES = {
     "vrhi_op_lookup": [C.c_char_p, _P(_i)],
     "vrhi_op_signature": [_i, _P(C.c_char_p)],
     "vrhi_op_launch": [_vp, _i, _P(Arg), _i, _vp, _sz],
+    "vrhi_col_sum_static_scratch": [_vp, _vp, _u64, _u64, _vp],
     "vrhi_partition_rows": [_u64, C.c_uint32, C.c_uint32, C.c_uint32, _i, _P(RowPartition)],
     "vrhi_partition_leading": [_u64, C.c_uint32, C.c_uint32, _P(_u64), _P(_u64)],
     "vrhi_graph_create": [_vp, _u64, _u64, _P(_vp)],

@@ -399,3 +399,91 @@ int launch_col_sum(vrhi_stream_t *st, const ArgView *args, int n_args, const voi
 }
 
 }  // namespace vrhi
+
+// ---------------------------------------------------------------------------------------------
+// Column sums for callers that must not allocate.
+//
+// Some users of this library sit where an allocation is not an option: a frame or control loop
+// with a hard latency budget (cudaMalloc can take milliseconds and serialises the device), a
+// process whose HBM was carved up front between tenants so that nothing may grow later, or code
+// running between other people's kernels that may not disturb the allocator's state.  Every
+// other operator here takes its scratch from a per-stream arena that is allocated on first use
+// and may grow; this entry point instead keeps the per-row-group partial sums in a fixed array
+// that is part of the library image.  Cost: each GPU that loads the library holds the array
+// (kStaticPartialFloats * 4 bytes = 1 MiB) until the process exits.
+//
+// Use: the first call on a device asks CUDA for the array's device address (a lookup, not an
+// allocation); let that first call happen before any stream capture is begun.  The array is
+// shared by every call on the device and keeps whatever the last call left in it, so two calls
+// whose kernels could run at the same time (different streams with no ordering between them)
+// race; calls on one stream, or ordered by events, are safe.  No call here reaches cudaMalloc,
+// cudaFree or any allocating library routine.
+#include <mutex>
+
+namespace {
+
+constexpr uint64_t kStaticPartialFloats = 262144;  // 1 MiB: e.g. 64 row groups of 4096 columns
+static __device__ __align__(256) float g_static_col_partials[kStaticPartialFloats];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+float *g_static_partials_ptr[kMaxDevices] = {};  // device address of the array, per device ordinal
+int g_static_sm_count[kMaxDevices] = {};
+
+// The array's name is only a host-side stand-in: the device address has to be asked for, once
+// per device, with that device current.
+int static_scratch_for_current_device(float **out_ptr, int *out_sms) {
+  int dev = -1;
+  VRHI_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return vrhi::fail(VRHI_ERR_UNSUPPORTED, "device ordinal %d is beyond the %d this entry point tracks", dev, kMaxDevices);
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (!g_static_partials_ptr[dev]) {
+    void *p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_static_col_partials);
+    if (e != cudaSuccess || !p) return vrhi::fail(VRHI_ERR_CUDA, "cudaGetSymbolAddress(static column partials) failed: %s", cudaGetErrorString(e));
+    int sms = 0;
+    VRHI_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    g_static_sm_count[dev] = sms;
+    g_static_partials_ptr[dev] = static_cast<float *>(p);
+  }
+  *out_ptr = g_static_partials_ptr[dev];
+  *out_sms = g_static_sm_count[dev];
+  return VRHI_OK;
+}
+
+}  // namespace
+
+extern "C" int vrhi_col_sum_static_scratch(const float *in_device, float *out_device, uint64_t rows, uint64_t cols,
+                                           void *cuda_stream) {
+  using namespace vrhi;
+  if (!in_device || !out_device) return fail(VRHI_ERR_INVALID, "col_sum_static_scratch: NULL pointer");
+  if (cols == 0) return VRHI_OK;
+  if (cols > kStaticPartialFloats)
+    return fail(VRHI_ERR_SIZE, "col_sum_static_scratch: %llu columns exceed the fixed scratch (%llu floats); use the col_sum operator", (unsigned long long)cols, (unsigned long long)kStaticPartialFloats);
+  if (rows > (1ull << 40)) return fail(VRHI_ERR_SIZE, "col_sum_static_scratch: row count out of range");
+  if (reinterpret_cast<uintptr_t>(in_device) % 16 || reinterpret_cast<uintptr_t>(out_device) % 4)
+    return fail(VRHI_ERR_SIZE, "col_sum_static_scratch: input must be 16-byte aligned and output 4-byte aligned");
+  cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+  if (rows == 0) {
+    VRHI_CUDA(cudaMemsetAsync(out_device, 0, cols * 4, s));
+    return VRHI_OK;
+  }
+  float *partials = nullptr;
+  int sms = 0;
+  VRHI_TRY(static_scratch_for_current_device(&partials, &sms));
+  const uint64_t gx = (cols + 1023) / 1024;
+  uint64_t gy = ((uint64_t)sms * 8 + gx - 1) / gx;
+  if (gy > rows) gy = rows;
+  if (gy > 1024) gy = 1024;
+  if (gy > kStaticPartialFloats / cols) gy = kStaticPartialFloats / cols;  // >= 1 by the check above
+  // Stage 1 writes every partial that stage 2 reads (gy rows of `cols` floats), so nothing in the
+  // array has to be cleared and whatever an earlier call left behind is never read.
+  dim3 grid((unsigned)gx, (unsigned)gy);
+  col_partial_kernel<<<grid, 256, 0, s>>>(in_device, partials, rows, cols);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(VRHI_ERR_CUDA, "launch of col_sum_static_scratch (partials) failed: %s", cudaGetErrorString(e));
+  col_finalize_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, s>>>(partials, out_device, (uint32_t)gy, cols, 1.0f);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(VRHI_ERR_CUDA, "launch of col_sum_static_scratch (finalize) failed: %s", cudaGetErrorString(e));
+  return VRHI_OK;
+}

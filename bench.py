@@ -67,7 +67,7 @@ class ClockSampler:
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20",
                                           "-i", str(self.gpu)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
@@ -319,6 +319,12 @@ def main():
         run_only(args)
         return
 
+    # NCCL prints its version banner on stdout; the contract is ONE JSON line there.  Everything
+    # a library writes to fd 1 goes to stderr from here on; the JSON line uses the saved descriptor.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+
     import torch
     import torch.distributed as dist
 
@@ -366,11 +372,40 @@ def main():
     def compute():
         ops.escape_time(st, image, params)
 
+    # With N > 1 a step is pipelined: the rank's chunks are computed in GROUPS launches, and the
+    # in-place all-gather of the slabs a launch completed runs on a second stream while the next
+    # launch computes.  The step ends when the last gather has finished.
+    GROUPS = 4
+    n_slabs = plan.part.chunk_count
+    group_params, group_slabs = [], []
+    if world > 1:
+        import copy
+        for gidx in range(GROUPS):
+            k0, k1 = n_slabs * gidx // GROUPS, n_slabs * (gidx + 1) // GROUPS
+            if k1 == k0:
+                continue
+            gp = copy.copy(params)
+            gp.chunk_first = plan.part.chunk_first + k0 * plan.part.chunk_step
+            gp.chunk_count = k1 - k0
+            group_params.append(gp)
+            group_slabs.append((k0, k1))
+        comm_stream = torch.cuda.Stream(device=local)
+
     def step():
-        compute()
-        if world > 1:
-            with torch.cuda.stream(tstream):
-                partition.all_gather_image(image_t, plan)
+        if world == 1:
+            compute()
+            return
+        works = []
+        for gp, (k0, k1) in zip(group_params, group_slabs):
+            ops.escape_time(st, image, gp)
+            ev = torch.cuda.Event()
+            ev.record(tstream)
+            with torch.cuda.stream(comm_stream):
+                comm_stream.wait_event(ev)
+                works += partition.all_gather_image(image_t, plan, async_op=True, slab_range=(k0, k1))
+        with torch.cuda.stream(tstream):
+            for w in works:
+                w.wait()   # the compute stream waits for the gathers: the step is complete after this
 
     def timed(fn, k):
         barrier()
@@ -386,14 +421,23 @@ def main():
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
-    for _ in range(args.warmup):
-        step()
-    launches0 = st.launch_count()
+    # clocks are sampled from the first warm-up step to the end of the timed steps, and on through
+    # ~0.3 s more of the same steps (the timed region alone is tens of milliseconds: too short for
+    # nvidia-smi to see more than one sample of it)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    for _ in range(args.warmup):
+        step()
+    launches0 = st.launch_count()
     total_ms = timed(step, args.steps)
     launches = st.launch_count() - launches0
+    t_hold = time.perf_counter()
+    while time.perf_counter() - t_hold < 0.3:
+        step()
+        torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
     clocks = sampler.stop() if rank == 0 else None
     ms_per_step = total_ms / args.steps
     value = total_iters / (ms_per_step * 1e-3) / 1e9
@@ -468,7 +512,7 @@ def main():
             del image_t
             torch.cuda.empty_cache()
             line["other_workloads"] = other_workloads(dev, st, torch, hbm_peak, peak_kind, fp32_peak)
-        print(json.dumps(line), flush=True)
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
     barrier()
     if world > 1:
         dist.destroy_process_group()

@@ -51,14 +51,16 @@ def owner_of_row(plan: ImagePlan, row: int) -> int:
     return c % plan.world if plan.scheme == L.PART_CYCLIC else c
 
 
-def all_gather_image(image, plan: ImagePlan, group=None, async_op: bool = False):
+def all_gather_image(image, plan: ImagePlan, group=None, async_op: bool = False, slab_range=None):
     """All-gather the row chunks of ``image`` (a [height, width] tensor holding this rank's chunks
     at their true rows) so that every rank ends with the whole image.
 
     Cyclic plans whose chunk count divides evenly gather IN PLACE: the image viewed as
     [slab, rank, chunk_rows*width] already has rank r's data at [:, r, :], which is exactly the
     output layout of an all-gather of each slab.  Anything else falls back to one broadcast per
-    chunk from its owner.  Returns the list of work handles when ``async_op``.
+    chunk from its owner.  ``slab_range=(lo, hi)`` restricts an even cyclic gather to slabs lo..hi-1
+    (slab k holds chunks k*world .. k*world+world-1), so that the gather of finished slabs can overlap
+    the computation of later ones.  Returns the list of work handles when ``async_op``.
     """
     import torch.distributed as dist
 
@@ -71,10 +73,21 @@ def all_gather_image(image, plan: ImagePlan, group=None, async_op: bool = False)
     even = plan.scheme == L.PART_CYCLIC and height % p.chunk_rows == 0 and n_chunks % world == 0
     if even:
         slabs = image.view(n_chunks // world, world, p.chunk_rows * width)
-        for k in range(slabs.shape[0]):
-            w = dist.all_gather_into_tensor(slabs[k].view(-1), slabs[k, plan.rank], group=group, async_op=async_op)
+        lo, hi = slab_range if slab_range is not None else (0, slabs.shape[0])
+        if image.is_cuda and hasattr(dist, "_coalescing_manager") and hi - lo > 1:
+            # one NCCL group for all slabs: a single launch instead of one per slab
+            with dist._coalescing_manager(group=group, device=image.device, async_ops=True) as cm:
+                for k in range(lo, hi):
+                    dist.all_gather_into_tensor(slabs[k].view(-1), slabs[k, plan.rank], group=group)
             if async_op:
-                works.append(w)
+                works.append(cm)
+            else:
+                cm.wait()
+        else:
+            for k in range(lo, hi):
+                w = dist.all_gather_into_tensor(slabs[k].view(-1), slabs[k, plan.rank], group=group, async_op=async_op)
+                if async_op:
+                    works.append(w)
     else:
         for c in range(n_chunks):
             r0 = c * p.chunk_rows

@@ -199,6 +199,10 @@ typedef struct vrhi_escape_params {
 /* Run the kernel that tests on every step even where the faster regrouping kernel applies
  * (exact mode, NORM2_GT with bound >= 4, |c| <= 1.5).  Results are identical either way. */
 #define VRHI_ESCAPE_FLAG_CHECKED_ONLY 1u
+/* The real axis runs along the rows and the imaginary axis along the columns: pixel (row j,
+ * column i) has real part y0 + j*dy and imaginary part x0 + i*dx.  This is the memory order of a
+ * field indexed [i, j] whose first index feeds the real part (fractal.py:8,20). */
+#define VRHI_ESCAPE_FLAG_TRANSPOSED 2u
 
 /* op "fused_map" -- the map chain  out = tanh(a*x + y) * exp(-0.5*x*x) + sqrt(|y| + 1e-3)
  * as one kernel.  args: [0] a, [1] x, [2] y (INPUT, n floats), [3] out (OUTPUT, n floats). */
@@ -265,6 +269,15 @@ typedef struct vrhi_mse_params {
   uint64_t rows, cols;
   double denom;
 } vrhi_mse_params;
+
+/* ops "vertex_transform" and "flat_color": the arithmetic of the reference's shader input
+ * (source/tests/integration/color.mlir) over arrays, no graphics API involved; both take
+ * vrhi_map_params with n = number of vertices / fragments.
+ *   vertex_transform (color.mlir:4-39): args [0] pos INPUT f32[n][3], [1] model, [2] view,
+ *     [3] proj UNIFORM f32[16] row-major, [4] gl_position OUTPUT f32[n][4] =
+ *     proj*(view*(model*(p0,p1,p2,1))), [5] varying VARYING f32[n][3] = pos.
+ *   flat_color (color.mlir:43-59): args [0] color UNIFORM f32[3], [1] fragments IMAGE f32[n][4],
+ *     every fragment = (c0,c1,c2,1). */
 
 /* op "fp32_probe": dependent-free FFMA chains, for measuring the FP32 issue peak the
  * escape-time kernel is bounded by.  args [0] OUTPUT (>= 4 bytes).  Executes

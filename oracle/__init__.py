@@ -195,6 +195,21 @@ def mse_tanh_bwd(W, x, b, t, denom=None):
     return dW, dx, db
 
 
+def vertex_transform(pos, model, view, proj):
+    """-> (gl_position [n,4], varying [n,3]); color.mlir:4-39 over an array of vertices, binary64."""
+    pos, pp = _f32(pos)
+    model, pm = _f32(model)
+    view, pv = _f32(view)
+    proj, pj = _f32(proj)
+    n = pos.shape[0]
+    out, var = np.empty((n, 4), dtype=np.float32), np.empty((n, 3), dtype=np.float32)
+    fn = lib().vo_vertex_transform
+    fn.argtypes = [C.POINTER(C.c_float)] * 4 + [C.c_size_t] + [C.POINTER(C.c_float)] * 2
+    fn.restype = None
+    fn(pp, pm, pv, pj, n, out.ctypes.data_as(C.POINTER(C.c_float)), var.ctypes.data_as(C.POINTER(C.c_float)))
+    return out, var
+
+
 def digest_u32(v, base_index=0):
     """(sum, position-weighted sum mod 2**64) of a uint32 array; exact integers."""
     v = np.ascontiguousarray(v, dtype=np.uint32)

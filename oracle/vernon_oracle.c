@@ -323,6 +323,29 @@ VO_EXPORT void vo_mse_tanh_bwd(const float *W, const float *x, const float *b, c
 }
 
 /*
+ * Vertex stage of the reference's shader input (source/tests/integration/color.mlir:4-39):
+ * gl_position = proj * (view * (model * (p0, p1, p2, 1))) with row-major 4x4 matrices, varying = p.
+ * Evaluated in binary64 from the binary32 inputs, rounded once.
+ */
+static void matvec4d(const float *M, const double *v, double *r) {
+  for (int i = 0; i < 4; ++i)
+    r[i] = (double)M[4 * i] * v[0] + (double)M[4 * i + 1] * v[1] + (double)M[4 * i + 2] * v[2] + (double)M[4 * i + 3] * v[3];
+}
+
+VO_EXPORT void vo_vertex_transform(const float *pos, const float *model, const float *view,
+                                   const float *proj, size_t n, float *gl_position, float *varying) {
+#pragma omp parallel for schedule(static)
+  for (int64_t k = 0; k < (int64_t)n; ++k) {
+    double v[4] = {pos[3 * k], pos[3 * k + 1], pos[3 * k + 2], 1.0}, a[4], b[4], c[4];
+    matvec4d(model, v, a);
+    matvec4d(view, a, b);
+    matvec4d(proj, b, c);
+    for (int i = 0; i < 4; ++i) gl_position[4 * k + i] = (float)c[i];
+    for (int i = 0; i < 3; ++i) varying[3 * k + i] = pos[3 * k + i];
+  }
+}
+
+/*
  * Order-independent digest of a uint32 image: sum of counts, and a position-weighted
  * checksum  sum (k+1)*v[k]  mod 2^64.  Both are exact integer quantities, so a GPU image can
  * be compared with a stored oracle digest at sizes where the oracle takes minutes.

@@ -52,7 +52,7 @@ def test_semantic_vocabulary_matches_reference_strings():
 def test_operator_registry():
     names = ops.op_names()
     for want in ["escape_time", "fused_map", "map_tape", "row_sum", "row_max", "row_softmax", "row_stats_softmax",
-                 "col_sum", "mse_tanh_fwd", "mse_tanh_bwd", "fp32_probe"]:
+                 "col_sum", "mse_tanh_fwd", "mse_tanh_bwd", "fp32_probe", "vertex_transform", "flat_color"]:
         assert want in names
         assert names[ops.op_id(want)] == want
     with pytest.raises(L.VrhiError) as e:

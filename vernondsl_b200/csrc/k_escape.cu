@@ -31,6 +31,7 @@ struct EscapeDev {
   uint32_t batch_tiles;      // tiles per stolen batch (a batch never straddles a row)
   uint32_t batches_per_row;
   uint32_t n_batches;
+  uint32_t transposed;       // 1: the row coordinate is the real part and the column coordinate the imaginary part
 };
 
 template <int MODE>
@@ -89,9 +90,9 @@ __global__ void __launch_bounds__(256) escape_checked_kernel(EscapeDev p, void *
       const float x = __fadd_rn(p.x0, __fmul_rn((float)i, p.dx));
       float zr, zi, cr, ci;
       if (KIND == VRHI_ESCAPE_MANDELBROT) {
-        zr = 0.f; zi = 0.f; cr = x; ci = y;
+        zr = 0.f; zi = 0.f; cr = p.transposed ? y : x; ci = p.transposed ? x : y;
       } else {
-        zr = x; zi = y; cr = p.cr; ci = p.ci;
+        zr = p.transposed ? y : x; zi = p.transposed ? x : y; cr = p.cr; ci = p.ci;
       }
       uint32_t count = 0;
       for (;;) {
@@ -156,6 +157,7 @@ __global__ void __launch_bounds__(256, 6) escape_regroup_kernel(EscapeDev p, voi
   // parameters live in registers: the hot loops must not go back to the constant bank
   const float bound = p.bound, x0 = p.x0, dx = p.dx, color_scale = p.color_scale;
   const uint32_t max_iter = p.max_iter, width = p.width;
+  const bool transposed = p.transposed != 0;
   const uint32_t fast_limit = max_iter - (uint32_t)U;  // the host guarantees max_iter >= U: cnt <= fast_limit means a whole block fits
 
   // warp-uniform state
@@ -187,8 +189,9 @@ __global__ void __launch_bounds__(256, 6) escape_regroup_kernel(EscapeDev p, voi
     const bool valid = i < width;
     const float x = __fadd_rn(x0, __fmul_rn((float)i, dx));
     float fzr, fzi, fcr, fci;
-    if (PER_PIXEL_C) { fzr = 0.f; fzi = 0.f; fcr = x; fci = row_y; }
-    else { fzr = x; fzi = row_y; fcr = cr; fci = ci; }
+    const float re = transposed ? row_y : x, im = transposed ? x : row_y;
+    if (PER_PIXEL_C) { fzr = 0.f; fzi = 0.f; fcr = re; fci = im; }
+    else { fzr = re; fzi = im; fcr = cr; fci = ci; }
     uint32_t fcnt = 0;
     bool flive = valid;
     // K steps with a test on each; dead lanes keep computing (their values are never used), so the
@@ -347,6 +350,7 @@ int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const
   p.width = q.width; p.height = q.height; p.max_iter = q.max_iter;
   p.x0 = q.x0; p.y0 = q.y0; p.dx = q.dx; p.dy = q.dy; p.cr = q.cr; p.ci = q.ci;
   p.bound = q.bound; p.color_scale = q.color_scale;
+  p.transposed = (q.flags & VRHI_ESCAPE_FLAG_TRANSPOSED) ? 1u : 0u;
   if (q.chunk_rows == 0) {
     p.chunk_rows = q.height; p.chunk_first = 0; p.chunk_step = 1; p.rows_owned = q.height;
   } else {

@@ -66,6 +66,11 @@ static const OpDef kOps[] = {
     {"mse_tanh_bwd", "args: W,x,b,t(INPUT), dW,dx,db(OUTPUT)[, loss(OUTPUT f32[1])]; params: vrhi_mse_params",
      launch_mse_tanh_bwd},
     {"fp32_probe", "args: out(OUTPUT >=4 bytes); params: vrhi_probe_params", launch_fp32_probe},
+    {"vertex_transform",
+     "args: pos(INPUT f32[n][3]), model,view,proj(UNIFORM f32[16] row-major), gl_position(OUTPUT f32[n][4]), "
+     "varying(VARYING f32[n][3]); params: vrhi_map_params",
+     launch_vertex_transform},
+    {"flat_color", "args: color(UNIFORM f32[3]), fragments(IMAGE f32[n][4]); params: vrhi_map_params", launch_flat_color},
 };
 static const int kNumOps = int(sizeof(kOps) / sizeof(kOps[0]));
 

@@ -100,6 +100,8 @@ int launch_col_sum(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
 int launch_mse_tanh_fwd(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
 int launch_mse_tanh_bwd(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
 int launch_fp32_probe(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
+int launch_vertex_transform(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
+int launch_flat_color(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
 
 // Copies a caller's parameter block into a zero-initialised struct of the current layout,
 // honouring the leading size field (older, shorter callers leave new fields zero).

@@ -53,14 +53,15 @@ def grid_steps(x0: float, x1: float, y0: float, y1: float, width: int, height: i
 def escape_params(kind: int, width: int, height: int, x0: float, y0: float, dx: float, dy: float, *, cr: float = 0.0,
                   ci: float = 0.0, max_iter: int = 256, mode: int = L.EXACT, test: int = L.TEST_NORM2_GT,
                   bound: float = 4.0, output: int = L.OUT_COUNT_U32, color_scale: float = 0.0,
-                  partition: Optional[L.RowPartition] = None, checked_only: bool = False) -> L.EscapeParams:
+                  partition: Optional[L.RowPartition] = None, checked_only: bool = False,
+                  transposed: bool = False) -> L.EscapeParams:
     p = L.EscapeParams()
     p.size = C.sizeof(L.EscapeParams)
     p.kind, p.mode, p.test, p.output = kind, mode, test, output
     p.width, p.height, p.max_iter = width, height, max_iter
     p.x0, p.y0, p.dx, p.dy = x0, y0, dx, dy
     p.cr, p.ci, p.bound, p.color_scale = cr, ci, bound, color_scale
-    p.flags = 1 if checked_only else 0
+    p.flags = (1 if checked_only else 0) | (2 if transposed else 0)
     if partition is not None:
         p.chunk_rows, p.chunk_first = partition.chunk_rows, partition.chunk_first
         p.chunk_step, p.chunk_count = partition.chunk_step, partition.chunk_count
@@ -185,6 +186,22 @@ def mse_tanh_bwd(stream: Stream, W: Buffer, x: Buffer, b: Buffer, t: Buffer, dW:
     if loss is not None:
         args.append(loss.arg(L.OUTPUT))
     launch(stream, "mse_tanh_bwd", args, _mse(rows, cols, denom))
+
+
+def vertex_transform(stream: Stream, pos: Buffer, model: Buffer, view: Buffer, proj: Buffer, gl_position: Buffer,
+                     varying: Buffer, n: int) -> None:
+    """color.mlir:4-39 over an array of n vertices: gl_position = proj*(view*(model*(p,1))), varying = p."""
+    p = L.MapParams()
+    p.size, p.n = C.sizeof(L.MapParams), int(n)
+    launch(stream, "vertex_transform", [pos.arg(L.INPUT), model.arg(L.UNIFORM), view.arg(L.UNIFORM), proj.arg(L.UNIFORM),
+                                        gl_position.arg(L.OUTPUT), varying.arg(L.VARYING)], p)
+
+
+def flat_color(stream: Stream, color: Buffer, fragments: Buffer, n: int) -> None:
+    """color.mlir:43-59 over n fragments: every fragment = (c0, c1, c2, 1)."""
+    p = L.MapParams()
+    p.size, p.n = C.sizeof(L.MapParams), int(n)
+    launch(stream, "flat_color", [color.arg(L.UNIFORM), fragments.arg(L.IMAGE)], p)
 
 
 def fp32_probe(stream: Stream, out: Buffer, ffma_per_thread: int, threads: int = 0) -> None:

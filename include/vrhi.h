@@ -126,6 +126,20 @@ VRHI_API int vrhi_buffer_fill_u8(vrhi_buffer buf, uint64_t offset, int value, ui
                                  vrhi_stream stream);
 VRHI_API int vrhi_host_alloc(uint64_t bytes, void **out_host); /* pinned */
 VRHI_API int vrhi_host_free(void *host);
+/* Device-to-device copy of `rows` runs of `width_bytes` bytes (pitches in bytes; rows = 1 is a
+ * plain copy).  Source and destination may live on different GPUs of one box, including a
+ * destination opened with vrhi_buffer_ipc_open: the copy engines move the data over NVLink
+ * without occupying SMs, so it overlaps kernels on other streams. */
+VRHI_API int vrhi_buffer_copy_2d(vrhi_buffer dst, uint64_t dst_offset, uint64_t dst_pitch, vrhi_buffer src,
+                                 uint64_t src_offset, uint64_t src_pitch, uint64_t width_bytes, uint64_t rows,
+                                 vrhi_stream stream);
+/* Multi-process sharing inside one box (one process per GPU): export a 64-byte handle of a buffer
+ * this library allocated, and open another process's handle as a buffer that can be a copy
+ * destination.  Destroying an opened buffer closes the mapping, not the memory. */
+#define VRHI_IPC_HANDLE_BYTES 64
+VRHI_API int vrhi_buffer_ipc_export(vrhi_buffer buf, void *out_handle /* VRHI_IPC_HANDLE_BYTES */);
+VRHI_API int vrhi_buffer_ipc_open(vrhi_device dev, const void *handle, uint64_t bytes, int arg_class,
+                                  vrhi_buffer *out_buf);
 
 /* ---------------------------------------------------------------- streams / events ------ */
 VRHI_API int vrhi_stream_create(vrhi_device dev, vrhi_stream *out_stream);

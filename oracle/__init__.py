@@ -94,12 +94,22 @@ def grid_steps(x0, x1, y0, y1, width, height):
 
 def escape_time(kind, width, height, x0, y0, dx, dy, cr=0.0, ci=0.0, max_iter=256,
                 test=TEST_NORM2_GT, bound=4.0, row_begin=0, row_step=1, row_count=None,
-                want_image=True):
-    """Counts for rows row_begin, row_begin+row_step, ... -> (uint32 [row_count, width], sum)."""
+                want_image=True, fast=False):
+    """Counts for rows row_begin, row_begin+row_step, ... -> (uint32 [row_count, width], sum).
+    ``fast=True`` evaluates the contracted rounding sequence (see vo_escape_time_fast)."""
     if row_count is None:
         row_count = (height - row_begin + row_step - 1) // row_step
     out = np.empty((row_count, width), dtype=np.uint32) if want_image else None
     ptr = out.ctypes.data_as(C.POINTER(C.c_uint32)) if want_image else None
+    if fast:
+        if test != TEST_NORM2_GT:
+            raise ValueError("the contracted mode only has the squared-norm test")
+        fn = lib().vo_escape_time_fast
+        fn.restype = C.c_uint64
+        fn.argtypes = [C.c_int, C.c_uint32, C.c_uint32, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float,
+                       C.c_float, C.c_uint32, C.c_float, C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_uint32)]
+        return out, int(fn(kind, width, height, x0, y0, dx, dy, cr, ci, max_iter, bound, row_begin, row_step,
+                           row_count, ptr))
     total = lib().vo_escape_time(kind, width, height, x0, y0, dx, dy, cr, ci, max_iter, test,
                                  bound, row_begin, row_step, row_count, ptr)
     return out, int(total)

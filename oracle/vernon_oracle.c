@@ -115,6 +115,52 @@ VO_EXPORT uint64_t vo_escape_time(int kind, uint32_t width, uint32_t height, flo
   return total;
 }
 
+/*
+ * The contracted ("fast") arithmetic mode: the same loop with multiply-adds fused, as a compiler
+ * with contraction enabled could emit it.  It is a different, but equally well-defined, rounding
+ * sequence (fmaf is a single correctly rounded operation):
+ *     test    s = fma(zi, zi, zr*zr)
+ *     update  zi' = fma(zr+zr, zi, ci);   zr' = fma(zr, zr, fma(-zi, zi, cr))
+ * Only the test "s > bound" exists in this mode.
+ */
+static inline uint32_t escape_pixel_fast(float zr, float zi, float cr, float ci, uint32_t max_iter,
+                                         float bound) {
+  uint32_t it = 0;
+  for (;;) {
+    float s = fmaf(zi, zi, zr * zr);
+    if (!(s <= bound) || it >= max_iter) break;
+    float nzi = fmaf(zr + zr, zi, ci);
+    zr = fmaf(zr, zr, fmaf(-zi, zi, cr));
+    zi = nzi;
+    ++it;
+  }
+  return it;
+}
+
+VO_EXPORT uint64_t vo_escape_time_fast(int kind, uint32_t width, uint32_t height, float x0, float y0,
+                                       float dx, float dy, float cr, float ci, uint32_t max_iter,
+                                       float bound, uint32_t row_begin, uint32_t row_step,
+                                       uint32_t row_count, uint32_t *out) {
+  uint64_t total = 0;
+  (void)height;
+#pragma omp parallel for schedule(dynamic, 1) reduction(+ : total)
+  for (int64_t r = 0; r < (int64_t)row_count; ++r) {
+    uint32_t j = row_begin + (uint32_t)r * row_step;
+    float y = y0 + (float)j * dy;
+    uint32_t *dst = out ? out + (size_t)r * width : NULL;
+    uint64_t rowsum = 0;
+    for (uint32_t i = 0; i < width; ++i) {
+      float x = x0 + (float)i * dx;
+      uint32_t it = (kind == VO_MANDELBROT) ? escape_pixel_fast(0.0f, 0.0f, x, y, max_iter, bound)
+                                            : escape_pixel_fast(x, y, cr, ci, max_iter, bound);
+      if (dst) dst[i] = it;
+      rowsum += it;
+    }
+    total += rowsum;
+  }
+  return total;
+}
+
 /* Colour written by fractal.py:25 from a count:  1 - iterations * scale  (binary32). */
 VO_EXPORT void vo_escape_color(const uint32_t *counts, size_t n, float scale, float *out) {
 #pragma omp parallel for schedule(static)

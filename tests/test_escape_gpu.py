@@ -166,6 +166,15 @@ def test_fast_mode_is_close_but_reported_separately(dev, stream):
     kind, W, H, x0, y0, dx, dy, kw = workload("julia_512")
     exact = run_gpu(dev, stream, kind, W, H, x0, y0, dx, dy, **kw)
     fast = run_gpu(dev, stream, kind, W, H, x0, y0, dx, dy, mode=L.FAST, **kw)
+    # the contracted mode is itself a fixed rounding sequence: both kernels reproduce the oracle's bits
+    want_fast, _ = oracle.escape_time(kind, W, H, x0, y0, dx, dy, kw["cr"], kw["ci"], kw["max_iter"], fast=True)
+    assert np.array_equal(fast, want_fast)
+    fast_checked = run_gpu(dev, stream, kind, W, H, x0, y0, dx, dy, mode=L.FAST, checked_only=True, **kw)
+    assert np.array_equal(fast_checked, want_fast)
+    mkind, mW, mH, mx0, my0, mdx, mdy, mkw = workload("mandelbrot_ragged")
+    mfast = run_gpu(dev, stream, mkind, mW, mH, mx0, my0, mdx, mdy, mode=L.FAST, **mkw)
+    mwant, _ = oracle.escape_time(mkind, mW, mH, mx0, my0, mdx, mdy, max_iter=mkw["max_iter"], fast=True)
+    assert np.array_equal(mfast, mwant)
     mismatch = float((exact != fast).mean())
     assert mismatch < 0.05  # contraction changes roundings: some boundary pixels move
     assert abs(int(fast.sum(dtype=np.int64)) - int(exact.sum(dtype=np.int64))) < 0.02 * exact.sum(dtype=np.int64)

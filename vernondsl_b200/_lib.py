@@ -131,6 +131,9 @@ PROTOTYPES = {
     "vrhi_buffer_fill_u8": [_vp, _u64, _i, _u64, _vp],
     "vrhi_host_alloc": [_u64, _P(_vp)],
     "vrhi_host_free": [_vp],
+    "vrhi_buffer_copy_2d": [_vp, _u64, _u64, _vp, _u64, _u64, _u64, _u64, _vp],
+    "vrhi_buffer_ipc_export": [_vp, _vp],
+    "vrhi_buffer_ipc_open": [_vp, _vp, _u64, _i, _P(_vp)],
     "vrhi_stream_create": [_vp, _P(_vp)],
     "vrhi_stream_wrap": [_vp, _vp, _P(_vp)],
     "vrhi_stream_destroy": [_vp],

@@ -34,17 +34,31 @@ struct EscapeDev {
   uint32_t transposed;       // 1: the row coordinate is the real part and the column coordinate the imaginary part
 };
 
+// Step primitives.  EXACT keeps a = zr*zr and b = zi*zi alongside z so that one update costs six
+// instructions; FAST lets multiply-adds fuse (four instructions per update) and is a different,
+// equally well-defined rounding sequence:
+//     test  s = fma(zi, zi, zr*zr)        update  zi' = fma(zr+zr, zi, ci);  zr' = fma(zr, zr, fma(-zi, zi, cr))
 template <int MODE>
-__device__ __forceinline__ void escape_step(float &zr, float &zi, float a, float b, float cr, float ci) {
+__device__ __forceinline__ void z_squares(float zr, float zi, float &a, float &b) {
+  if (MODE == VRHI_ESCAPE_EXACT) { a = __fmul_rn(zr, zr); b = __fmul_rn(zi, zi); }
+}
+template <int MODE>
+__device__ __forceinline__ float z_norm2(float zr, float zi, float a, float b) {
+  if (MODE == VRHI_ESCAPE_EXACT) return __fadd_rn(a, b);
+  return __fmaf_rn(zi, zi, __fmul_rn(zr, zr));
+}
+template <int MODE>
+__device__ __forceinline__ void z_advance(float &zr, float &zi, float &a, float &b, float cr, float ci) {
   if (MODE == VRHI_ESCAPE_EXACT) {
-    float t = __fmul_rn(zr, zi);
+    const float t = __fmul_rn(zr, zi);
     zi = __fmaf_rn(2.0f, t, ci);
     zr = __fadd_rn(__fsub_rn(a, b), cr);
+    a = __fmul_rn(zr, zr);
+    b = __fmul_rn(zi, zi);
   } else {
-    // contracted: fewer roundings, not bit-identical to the exact order
-    float t = zr + zr;
-    zi = fmaf(t, zi, ci);
-    zr = (a - b) + cr;
+    const float nzi = __fmaf_rn(__fadd_rn(zr, zr), zi, ci);
+    zr = __fmaf_rn(zr, zr, __fmaf_rn(-zi, zi, cr));
+    zi = nzi;
   }
 }
 
@@ -95,19 +109,11 @@ __global__ void __launch_bounds__(256) escape_checked_kernel(EscapeDev p, void *
         zr = p.transposed ? y : x; zi = p.transposed ? x : y; cr = p.cr; ci = p.ci;
       }
       uint32_t count = 0;
+      float a = 0.f, b = 0.f;
+      z_squares<MODE>(zr, zi, a, b);
       for (;;) {
-        float a, b, s;
-        if (MODE == VRHI_ESCAPE_EXACT) {
-          a = __fmul_rn(zr, zr);
-          b = __fmul_rn(zi, zi);
-          s = __fadd_rn(a, b);
-        } else {
-          a = zr * zr;
-          b = zi * zi;
-          s = fmaf(zi, zi, a);
-        }
-        if (escaped<TEST>(s, p.bound) || count >= p.max_iter) break;
-        escape_step<MODE>(zr, zi, a, b, cr, ci);
+        if (escaped<TEST>(z_norm2<MODE>(zr, zi, a, b), p.bound) || count >= p.max_iter) break;
+        z_advance<MODE>(zr, zi, a, b, cr, ci);
         ++count;
       }
       store_count<OUT>(image, row_base + i, count, p.color_scale);
@@ -142,7 +148,7 @@ __global__ void __launch_bounds__(256) escape_checked_kernel(EscapeDev p, void *
 constexpr int kPoolCap = 64;
 
 // U = steps per block, T = waiting lanes that trigger a checked block, K = checked steps a fresh pixel gets before it is pooled
-template <int KIND, int OUT, int U, int T, int K = 8>
+template <int KIND, int OUT, int U, int T, int K = 8, int MODE = VRHI_ESCAPE_EXACT>
 __global__ void __launch_bounds__(256, 6) escape_regroup_kernel(EscapeDev p, void *image, uint32_t *work_counter) {
   constexpr bool PER_PIXEL_C = (KIND == VRHI_ESCAPE_MANDELBROT);
   __shared__ float s_zr[8][kPoolCap], s_zi[8][kPoolCap];
@@ -194,17 +200,16 @@ __global__ void __launch_bounds__(256, 6) escape_regroup_kernel(EscapeDev p, voi
     else { fzr = re; fzi = im; fcr = cr; fci = ci; }
     uint32_t fcnt = 0;
     bool flive = valid;
+    float fa = 0.f, fb = 0.f;
+    z_squares<MODE>(fzr, fzi, fa, fb);
     // K steps with a test on each; dead lanes keep computing (their values are never used), so the
     // loop body is straight-line code.  The host guarantees max_iter >= K: no cap test in here.
 #pragma unroll
     for (int k = 0; k < K; ++k) {
-      const float fa = __fmul_rn(fzr, fzr), fb = __fmul_rn(fzi, fzi);
-      flive = flive && (__fadd_rn(fa, fb) <= bound);
+      flive = flive && (z_norm2<MODE>(fzr, fzi, fa, fb) <= bound);
       // most tiles lie far outside the set and die within two or three steps, all lanes together
       if ((k == 2 || k == 4) && k < K - 1 && !__any_sync(FULL, flive)) break;
-      const float ft = __fmul_rn(fzr, fzi);
-      fzi = __fmaf_rn(2.0f, ft, fci);
-      fzr = __fadd_rn(__fsub_rn(fa, fb), fcr);
+      z_advance<MODE>(fzr, fzi, fa, fb, fcr, fci);
       fcnt += flive ? 1u : 0u;
     }
     if (PER_PIXEL_C) {
@@ -212,12 +217,9 @@ __global__ void __launch_bounds__(256, 6) escape_regroup_kernel(EscapeDev p, voi
       bool slow = flive && !(fmaf(fcr, fcr, fci * fci) <= 2.25f);
       while (__any_sync(FULL, slow)) {
         if (slow) {
-          const float fa = __fmul_rn(fzr, fzr), fb = __fmul_rn(fzi, fzi);
-          if (!(__fadd_rn(fa, fb) <= bound) || fcnt >= max_iter) { slow = false; flive = false; }
+          if (!(z_norm2<MODE>(fzr, fzi, fa, fb) <= bound) || fcnt >= max_iter) { slow = false; flive = false; }
           else {
-            const float ft = __fmul_rn(fzr, fzi);
-            fzi = __fmaf_rn(2.0f, ft, fci);
-            fzr = __fadd_rn(__fsub_rn(fa, fb), fcr);
+            z_advance<MODE>(fzr, fzi, fa, fb, fcr, fci);
             ++fcnt;
           }
         }
@@ -243,24 +245,19 @@ __global__ void __launch_bounds__(256, 6) escape_regroup_kernel(EscapeDev p, voi
   // lane can reach max_iter inside the block, which saves the counter comparison on every step.
   auto checked_block = [&](auto cap_tag) {
     constexpr bool CAP = decltype(cap_tag)::value;
-    a = __fmul_rn(zr, zr);  // finishing lanes were put back on their checkpoint: refresh the squares
-    b = __fmul_rn(zi, zi);
+    z_squares<MODE>(zr, zi, a, b);  // finishing lanes were put back on their checkpoint: refresh the squares
     bool live = occ;
 #pragma unroll
     for (int k = 0; k < U; ++k) {
-      live = live && (__fadd_rn(a, b) <= bound);
+      live = live && (z_norm2<MODE>(zr, zi, a, b) <= bound);
       if (CAP) live = live && (cnt < max_iter);
-      const float t = __fmul_rn(zr, zi);
-      zi = __fmaf_rn(2.0f, t, ci);
-      zr = __fadd_rn(__fsub_rn(a, b), cr);
-      a = __fmul_rn(zr, zr);
-      b = __fmul_rn(zi, zi);
+      z_advance<MODE>(zr, zi, a, b, cr, ci);
       cnt += live ? 1u : 0u;
     }
     // the block made U tests and up to U updates; a lane whose fast block failed only at its very
     // last state needs the test of that state too (tests are idempotent, so this changes nothing
     // for lanes that pass)
-    live = live && (__fadd_rn(a, b) <= bound);
+    live = live && (z_norm2<MODE>(zr, zi, a, b) <= bound);
     if (CAP) live = live && (cnt < max_iter);
     if (occ && !live) store_count<OUT>(image, (size_t)idx, cnt, color_scale);
     occ = live;
@@ -279,7 +276,7 @@ __global__ void __launch_bounds__(256, 6) escape_regroup_kernel(EscapeDev p, voi
           const uint32_t slot = (pool_tail + r) & (kPoolCap - 1);
           zr = pzr[slot]; zi = pzi[slot]; idx = pidx[slot]; cnt = pcnt[slot];
           if (PER_PIXEL_C) { cr = pcr[slot]; ci = pci[slot]; }
-          a = __fmul_rn(zr, zr); b = __fmul_rn(zi, zi);
+          z_squares<MODE>(zr, zi, a, b);
           occ = true; run = true;
         }
         const uint32_t popped = min(need, pool_n);
@@ -295,16 +292,10 @@ __global__ void __launch_bounds__(256, 6) escape_regroup_kernel(EscapeDev p, voi
     while (waiting < threshold) {
       const float ckr = zr, cki = zi;
 #pragma unroll
-      for (int k = 0; k < U; ++k) {
-        const float t = __fmul_rn(zr, zi);
-        zi = __fmaf_rn(2.0f, t, ci);
-        zr = __fadd_rn(__fsub_rn(a, b), cr);
-        a = __fmul_rn(zr, zr);
-        b = __fmul_rn(zi, zi);
-      }
+      for (int k = 0; k < U; ++k) z_advance<MODE>(zr, zi, a, b, cr, ci);
       // lanes that are not running (empty or finishing) computed garbage: they, and lanes whose
       // block failed, go back to the checkpoint; a and b are refreshed by the checked block
-      run = run && (__fadd_rn(a, b) <= bound) && (cnt <= fast_limit);
+      run = run && (z_norm2<MODE>(zr, zi, a, b) <= bound) && (cnt <= fast_limit);
       if (run) cnt += U;
       else { zr = ckr; zi = cki; }
       waiting = __popc(__ballot_sync(FULL, !run));
@@ -395,7 +386,7 @@ int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const
   // The regrouping kernel takes what its exactness argument covers; everything else, and callers
   // that ask for it, runs the step-by-step kernel.
   const double c2 = (double)q.cr * q.cr + (double)q.ci * q.ci;
-  const bool regroup_ok = q.mode == VRHI_ESCAPE_EXACT && q.test == VRHI_TEST_NORM2_GT && q.bound >= 4.0f && q.bound < 3.0e38f &&
+  const bool regroup_ok = q.test == VRHI_TEST_NORM2_GT && q.bound >= 4.0f && q.bound < 3.0e38f &&
                           q.max_iter >= 64u && q.max_iter <= (1u << 30) && (uint64_t)q.width * q.height <= 0xffffffffull &&
                           (q.kind == VRHI_ESCAPE_MANDELBROT || c2 <= 2.25) && !(q.flags & VRHI_ESCAPE_FLAG_CHECKED_ONLY);
   if (regroup_ok) {
@@ -408,7 +399,7 @@ int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const
     if (const char *tune = getenv("VRHI_ESCAPE_TUNE")) {
       int tu = 0, tt = 0, tc = 0, tk = 8;
       int got = sscanf(tune, "%d,%d,%d,%d", &tu, &tt, &tc, &tk);
-      if (got >= 2 && q.output == VRHI_OUT_COUNT_U32) {
+      if (got >= 2 && q.output == VRHI_OUT_COUNT_U32 && q.mode == VRHI_ESCAPE_EXACT) {
         if (got >= 3 && tc > 0) { cap = (uint64_t)sms * tc; grid = (int)(ctas < cap ? ctas : cap); }
         bool hit = true;
 #define TUNEK(UU, TT, KK)                                                                                              \
@@ -426,7 +417,11 @@ int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const
       }
     }
     // U = 12, T = 8, K = 8: the sweep on B200 is flat within 2 % between U = 8..16 and T = 8..12
-#define REGROUP(KIND, OUT) escape_regroup_kernel<KIND, OUT, 12, 8><<<grid, 256, 0, st->s>>>(p, args[0].ptr, counter)
+#define REGROUP(KIND, OUT)                                                                                             \
+  do {                                                                                                                 \
+    if (q.mode == VRHI_ESCAPE_EXACT) escape_regroup_kernel<KIND, OUT, 12, 8, 8, VRHI_ESCAPE_EXACT><<<grid, 256, 0, st->s>>>(p, args[0].ptr, counter); \
+    else escape_regroup_kernel<KIND, OUT, 12, 8, 8, VRHI_ESCAPE_FAST><<<grid, 256, 0, st->s>>>(p, args[0].ptr, counter);   \
+  } while (0)
     if (q.kind == VRHI_ESCAPE_MANDELBROT) {
       if (q.output == VRHI_OUT_COUNT_U32) REGROUP(VRHI_ESCAPE_MANDELBROT, VRHI_OUT_COUNT_U32);
       else if (q.output == VRHI_OUT_COUNT_U16) REGROUP(VRHI_ESCAPE_MANDELBROT, VRHI_OUT_COUNT_U16);

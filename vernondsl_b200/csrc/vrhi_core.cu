@@ -251,7 +251,11 @@ int vrhi_buffer_wrap(vrhi_device dev, void *device_ptr, uint64_t bytes, int arg_
 int vrhi_buffer_destroy(vrhi_buffer buf) {
   if (!buf) return VRHI_OK;
   int rc = VRHI_OK;
-  if (buf->owned) {
+  if (buf->ipc) {
+    cudaSetDevice(buf->dev->ordinal);
+    cudaError_t e = cudaIpcCloseMemHandle(buf->ptr);
+    if (e != cudaSuccess) rc = fail(VRHI_ERR_CUDA, "cudaIpcCloseMemHandle failed: %s", cudaGetErrorString(e));
+  } else if (buf->owned) {
     cudaSetDevice(buf->dev->ordinal);
     cudaError_t e = cudaFree(buf->ptr);
     if (e != cudaSuccess) rc = fail(VRHI_ERR_CUDA, "cudaFree failed: %s", cudaGetErrorString(e));
@@ -340,6 +344,57 @@ int vrhi_host_alloc(uint64_t bytes, void **out_host) {
 int vrhi_host_free(void *host) {
   if (!host) return VRHI_OK;
   VRHI_CUDA(cudaFreeHost(host));
+  return VRHI_OK;
+}
+
+int vrhi_buffer_copy_2d(vrhi_buffer dst, uint64_t dst_offset, uint64_t dst_pitch, vrhi_buffer src, uint64_t src_offset,
+                        uint64_t src_pitch, uint64_t width_bytes, uint64_t rows, vrhi_stream stream) {
+  if (!dst || !src) return fail(VRHI_ERR_INVALID, "NULL buffer");
+  if (width_bytes == 0 || rows == 0) return VRHI_OK;
+  if (rows > 1 && (dst_pitch < width_bytes || src_pitch < width_bytes)) return fail(VRHI_ERR_SIZE, "pitch smaller than the row width");
+  const uint64_t dst_span = (rows - 1) * dst_pitch + width_bytes, src_span = (rows - 1) * src_pitch + width_bytes;
+  if (dst_offset > dst->bytes || dst_span > dst->bytes - dst_offset) return fail(VRHI_ERR_SIZE, "copy exceeds the destination buffer");
+  if (src_offset > src->bytes || src_span > src->bytes - src_offset) return fail(VRHI_ERR_SIZE, "copy exceeds the source buffer");
+  if (dst->cls == VRHI_INPUT || dst->cls == VRHI_UNIFORM || dst->cls == VRHI_UNIFORM_CONSTANT)
+    return fail(VRHI_ERR_INVALID, "copy destination is read-only (class %s)", vrhi_arg_class_name(dst->cls));
+  VRHI_TRY(set_device(src->dev));
+  cudaStream_t s = stream ? stream->s : nullptr;
+  char *d = static_cast<char *>(dst->ptr) + dst_offset;
+  const char *sp = static_cast<const char *>(src->ptr) + src_offset;
+  if (rows == 1)
+    VRHI_CUDA(cudaMemcpyAsync(d, sp, width_bytes, cudaMemcpyDeviceToDevice, s));
+  else
+    VRHI_CUDA(cudaMemcpy2DAsync(d, dst_pitch, sp, src_pitch, width_bytes, rows, cudaMemcpyDeviceToDevice, s));
+  return VRHI_OK;
+}
+
+int vrhi_buffer_ipc_export(vrhi_buffer buf, void *out_handle) {
+  if (!buf || !out_handle) return fail(VRHI_ERR_INVALID, "NULL argument");
+  if (!buf->owned) return fail(VRHI_ERR_INVALID, "only buffers this library allocated can be exported");
+  static_assert(sizeof(cudaIpcMemHandle_t) == VRHI_IPC_HANDLE_BYTES, "handle size");
+  VRHI_TRY(set_device(buf->dev));
+  cudaIpcMemHandle_t h;
+  VRHI_CUDA(cudaIpcGetMemHandle(&h, buf->ptr));
+  memcpy(out_handle, &h, sizeof h);
+  return VRHI_OK;
+}
+
+int vrhi_buffer_ipc_open(vrhi_device dev, const void *handle, uint64_t bytes, int arg_class, vrhi_buffer *out_buf) {
+  if (!dev || !handle || !out_buf) return fail(VRHI_ERR_INVALID, "NULL argument");
+  *out_buf = nullptr;
+  VRHI_TRY(check_class(arg_class));
+  if (bytes == 0) return fail(VRHI_ERR_SIZE, "zero-sized buffer");
+  VRHI_TRY(set_device(dev));
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof h);
+  void *p = nullptr;
+  VRHI_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+  vrhi_buffer_t *b = new (std::nothrow) vrhi_buffer_t{dev, p, bytes, arg_class, false, true};
+  if (!b) {
+    cudaIpcCloseMemHandle(p);
+    return fail(VRHI_ERR_OOM, "host allocation failed");
+  }
+  *out_buf = b;
   return VRHI_OK;
 }
 

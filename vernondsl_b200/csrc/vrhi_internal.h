@@ -24,6 +24,7 @@ struct vrhi_buffer_t {
   uint64_t bytes;
   int cls;
   bool owned;
+  bool ipc;  // mapping of another process's allocation (closed, not freed, on destroy)
 };
 
 // Per-stream scratch arena.  Kernels launched on one stream are ordered, so they may share it.

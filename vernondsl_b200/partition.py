@@ -113,3 +113,60 @@ def all_reduce_sum(tensors, group=None) -> None:
 def leading_slice(n: int, world: int, rank: int) -> Tuple[int, int]:
     """(begin, count) of this rank's share of a leading axis of length n."""
     return ops.partition_leading(n, world, rank)
+
+
+class PeerImageExchange:
+    """All-gather of an image's row chunks by peer copies instead of a collective kernel.
+
+    Every rank maps every other rank's image (CUDA IPC inside one box) and pushes its own chunks
+    into them with strided device-to-device copies: chunks of one rank lie ``world`` chunks apart, so
+    one 2-D copy per peer moves a whole range of slabs.  The copy engines carry the data over
+    NVLink without occupying SMs, so pushes of finished slabs overlap the kernel computing the
+    next ones.  ``finish`` orders a one-element all-reduce after this rank's pushes: when it
+    completes, every peer's pushes into this rank's image have completed too.
+
+    Needs an even cyclic plan (the in-place layout of :func:`all_gather_image`) and an image buffer
+    allocated by the library (``Device.empty``); anything else should use :func:`all_gather_image`.
+    """
+
+    def __init__(self, dev, image, plan: ImagePlan, row_bytes: int, group=None):
+        import torch
+        import torch.distributed as dist
+
+        p = plan.part
+        n_chunks = -(-plan.height // p.chunk_rows)
+        if not (plan.scheme == L.PART_CYCLIC and plan.height % p.chunk_rows == 0 and n_chunks % plan.world == 0):
+            raise ValueError("peer exchange needs a cyclic plan whose chunk count divides evenly")
+        self.image, self.plan, self.group = image, plan, group
+        self.chunk_bytes = p.chunk_rows * row_bytes
+        self.n_slabs = n_chunks // plan.world
+        handles = [None] * plan.world
+        dist.all_gather_object(handles, image.ipc_handle(), group=group)
+        self.peers = {r: dev.open_ipc(handles[r], image.nbytes, L.IMAGE) for r in range(plan.world) if r != plan.rank}
+        self._flag = torch.zeros(1, device=f"cuda:{dev.ordinal}")
+
+    def push(self, stream, slab_range=None) -> None:
+        """Enqueue on ``stream`` the copies of this rank's chunks of slabs lo..hi-1 into every peer."""
+        lo, hi = slab_range if slab_range is not None else (0, self.n_slabs)
+        if hi <= lo:
+            return
+        world, rank = self.plan.world, self.plan.rank
+        offset = (lo * world + rank) * self.chunk_bytes
+        pitch = world * self.chunk_bytes
+        # start with the next rank so that, at any moment, the ranks write to different peers
+        for step in range(1, world):
+            peer = self.peers[(rank + step) % world]
+            self.image.copy_2d_to(peer, offset, pitch, offset, pitch, self.chunk_bytes, hi - lo, stream)
+
+    def finish(self, torch_stream) -> None:
+        """Stream-ordered completion: after this, all ranks' pushes are visible in this rank's image."""
+        import torch
+        import torch.distributed as dist
+
+        with torch.cuda.stream(torch_stream):
+            dist.all_reduce(self._flag, group=self.group)
+
+    def close(self) -> None:
+        for b in self.peers.values():
+            b.close()
+        self.peers = {}

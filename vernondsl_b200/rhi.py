@@ -91,6 +91,13 @@ class Device:
         b.shape = tuple(tensor.shape)
         return b
 
+    def open_ipc(self, handle: bytes, nbytes: int, arg_class: int = L.STORAGE_BUFFER) -> "Buffer":
+        """Map a buffer that another process of this box exported with :meth:`Buffer.ipc_handle`."""
+        h = C.c_void_p()
+        raw = C.create_string_buffer(bytes(handle), 64)
+        check(lib().vrhi_buffer_ipc_open(self._h, raw, int(nbytes), int(arg_class), C.byref(h)))
+        return Buffer(self, h, int(nbytes), arg_class)
+
     # -- streams / events ----------------------------------------------------------------------
     def stream(self) -> "Stream":
         h = C.c_void_p()
@@ -144,6 +151,18 @@ class Buffer:
     def fill(self, byte: int, offset: int = 0, nbytes: Optional[int] = None, stream: Optional["Stream"] = None) -> None:
         check(lib().vrhi_buffer_fill_u8(self._h, int(offset), int(byte), int(self.nbytes - offset if nbytes is None else nbytes),
                                         stream._h if stream else None))
+
+    def ipc_handle(self) -> bytes:
+        """64-byte handle another process of this box can open with :meth:`Device.open_ipc`."""
+        raw = C.create_string_buffer(64)
+        check(lib().vrhi_buffer_ipc_export(self._h, raw))
+        return raw.raw
+
+    def copy_2d_to(self, dst: "Buffer", dst_offset: int, dst_pitch: int, src_offset: int, src_pitch: int, width_bytes: int,
+                   rows: int, stream: Optional["Stream"] = None) -> None:
+        """Copy `rows` runs of `width_bytes` from this buffer into `dst` (possibly on a peer GPU) with the copy engines."""
+        check(lib().vrhi_buffer_copy_2d(dst._h, int(dst_offset), int(dst_pitch), self._h, int(src_offset), int(src_pitch),
+                                        int(width_bytes), int(rows), stream._h if stream else None))
 
     def arg(self, arg_class: Optional[int] = None, offset: int = 0, nbytes: int = 0) -> L.Arg:
         a = L.Arg()

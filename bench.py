@@ -387,7 +387,7 @@ def main():
     # With N > 1 a step is pipelined: the rank's chunks are computed in GROUPS launches, and the
     # in-place all-gather of the slabs a launch completed runs on a second stream while the next
     # launch computes.  The step ends when the last gather has finished.
-    GROUPS = 4
+    GROUPS = int(os.environ.get("VRHI_BENCH_GROUPS", "4"))  # launches per step; finished slabs are exchanged while the next launch computes
     exchange = None
     n_slabs = plan.part.chunk_count
     group_params, group_slabs = [], []
@@ -422,6 +422,7 @@ def main():
             ev.record(tstream)
             comm_stream.wait_event(ev)
             if exchange is not None:
+                # one stream for all peers: pushes to several peers at once measured slower on this box
                 exchange.push(comm_st, (k0, k1))      # copy engines: overlaps the next group's kernel
             else:
                 with torch.cuda.stream(comm_stream):
@@ -558,6 +559,8 @@ def main():
             line["other_workloads"] = other_workloads(dev, st, torch, hbm_peak, peak_kind, fp32_peak)
         os.write(json_fd, (json.dumps(line) + "\n").encode())
     barrier()
+    if exchange is not None:
+        exchange.close()
     if world > 1:
         dist.destroy_process_group()
 

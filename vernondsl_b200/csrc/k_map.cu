@@ -114,24 +114,31 @@ int launch_fused_map(vrhi_stream_t *st, const ArgView *args, int n_args, const v
 
 // ---------------------------------------------------------------------------------------------
 // Generic fused tape.  The caller's tape is in SSA form (instruction t defines value
-// n_inputs + t).  The host assigns each value a physical slot by a linear scan over live ranges;
-// the kernel keeps one float4 per slot per thread in shared memory ([slot][thread], conflict
-// free) and walks the tape once per group of four elements.  Every branch on the opcode is
-// uniform across the CTA, so there is no divergence; the decode cost is hidden while the kernel
-// waits on HBM for short chains and shows as instruction pressure for long ones.
+// n_inputs + t).  The host turns it into a short physical program:
+//   * constants become immediate operands (no instruction, no storage);
+//   * a value consumed only by the very next instruction stays in registers ("PREV" operand);
+//   * every other value gets a slot, assigned by a linear scan over live ranges.
+// The kernel keeps one float4 per slot per element group per thread in shared memory
+// ([slot][group][thread], conflict free), handles G groups (4*G elements) per thread per trip so
+// that decoding an instruction is paid once per 4*G elements, and walks the program with
+// branches that are uniform across the CTA (no divergence).  Long chains are bound by
+// instruction issue and shared-memory traffic rather than HBM; the specialised kernels above
+// exist for the chains that matter most.
 
 constexpr int kTapeThreads = 128;
-constexpr int kTapeMaxSlots = 24;  // 24 slots * 128 threads * 16 B = 48 KiB, the default dynamic limit
+constexpr int kTapeSlotBytes = 48 * 1024;  // the default dynamic shared-memory limit
+
+enum { OPK_SLOT = 0, OPK_PREV = 1, OPK_IMM = 2, OPK_NONE = 3 };
 
 struct TapeInstrDev {
-  uint8_t op, dst, a, b, c, pad[3];
+  uint8_t op, dst, keep, ka, kb, kc, a, b, c, pad[3];
   float imm;
 };
 
 struct TapeDev {
   uint32_t n_inputs, n_outputs, n_instr, n_slots;
   uint32_t row_vector_mask, col_vector_mask, scalar_mask;
-  uint8_t in_slot[VRHI_TAPE_MAX_INPUTS];
+  uint8_t in_slot[VRHI_TAPE_MAX_INPUTS];   // 255: the input is never read
   uint8_t out_slot[VRHI_TAPE_MAX_OUTPUTS];
   TapeInstrDev instr[VRHI_TAPE_MAX_INSTR];
   const float *in[VRHI_TAPE_MAX_INPUTS];
@@ -139,36 +146,62 @@ struct TapeDev {
   uint64_t rows, cols;
 };
 
-#define TAPE_U(EXPR)                                                        \
-  do {                                                                      \
-    { const float a = va.x; res.x = (EXPR); } { const float a = va.y; res.y = (EXPR); } \
-    { const float a = va.z; res.z = (EXPR); } { const float a = va.w; res.w = (EXPR); } \
-  } while (0)
-#define TAPE_B(EXPR)                                                        \
-  do {                                                                      \
-    { const float a = va.x, b = vb.x; res.x = (EXPR); } { const float a = va.y, b = vb.y; res.y = (EXPR); } \
-    { const float a = va.z, b = vb.z; res.z = (EXPR); } { const float a = va.w, b = vb.w; res.w = (EXPR); } \
-  } while (0)
+#define TAPE_U(EXPR)                                                                              \
+  _Pragma("unroll") for (int g = 0; g < G; ++g) {                                                 \
+    { const float a = va[g].x; res[g].x = (EXPR); } { const float a = va[g].y; res[g].y = (EXPR); } \
+    { const float a = va[g].z; res[g].z = (EXPR); } { const float a = va[g].w; res[g].w = (EXPR); } \
+  }
+#define TAPE_B(EXPR)                                                                              \
+  _Pragma("unroll") for (int g = 0; g < G; ++g) {                                                 \
+    { const float a = va[g].x, b = vb[g].x; res[g].x = (EXPR); } { const float a = va[g].y, b = vb[g].y; res[g].y = (EXPR); } \
+    { const float a = va[g].z, b = vb[g].z; res[g].z = (EXPR); } { const float a = va[g].w, b = vb[g].w; res[g].w = (EXPR); } \
+  }
 
-// Executes the tape on the float4 group held in the slots of this thread.
-__device__ __forceinline__ void tape_run(const TapeDev &T, float4 *slots /* [slot][kTapeThreads] */) {
+template <int G>
+__device__ __forceinline__ void tape_fetch(float4 (&v)[G], int kind, int idx, float imm, const float4 (&prev)[G],
+                                           const float4 *slots, int tid) {
+  if (kind == OPK_SLOT) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) v[g] = slots[(idx * G + g) * kTapeThreads + tid];
+  } else if (kind == OPK_PREV) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) v[g] = prev[g];
+  } else {
+#pragma unroll
+    for (int g = 0; g < G; ++g) v[g] = make_float4(imm, imm, imm, imm);
+  }
+}
+
+// Executes the program on the G float4 groups held in the slots of this thread.
+template <int G>
+__device__ __forceinline__ void tape_run(const TapeDev &T, float4 *slots /* [slot][G][kTapeThreads] */) {
   const int tid = threadIdx.x;
+  float4 prev[G];
+#pragma unroll
+  for (int g = 0; g < G; ++g) prev[g] = make_float4(0.f, 0.f, 0.f, 0.f);
   for (uint32_t t = 0; t < T.n_instr; ++t) {
     const TapeInstrDev I = T.instr[t];
-    float4 va = slots[I.a * kTapeThreads + tid];
-    float4 vb = slots[I.b * kTapeThreads + tid];
-    float4 vc;
-    float4 res;
-    const float imm = I.imm;
+    float4 va[G], vb[G], res[G];
+    tape_fetch<G>(va, I.ka, I.a, I.imm, prev, slots, tid);
+    if (I.kb != OPK_NONE) tape_fetch<G>(vb, I.kb, I.b, I.imm, prev, slots, tid);
     switch (I.op) {
-      case VRHI_T_CONST: res = make_float4(imm, imm, imm, imm); break;
+      case VRHI_T_CONST: TAPE_U(a); break;  // a materialised constant: operand a is the immediate
       case VRHI_T_ADD: TAPE_B(a + b); break;
       case VRHI_T_SUB: TAPE_B(a - b); break;
       case VRHI_T_MUL: TAPE_B(a * b); break;
       case VRHI_T_DIV: TAPE_B(a / b); break;
       case VRHI_T_MAX: TAPE_B(fmaxf(a, b)); break;
       case VRHI_T_MIN: TAPE_B(fminf(a, b)); break;
-      case VRHI_T_FMA: vc = slots[I.c * kTapeThreads + tid]; { res.x = fmaf(va.x, vb.x, vc.x); res.y = fmaf(va.y, vb.y, vc.y); res.z = fmaf(va.z, vb.z, vc.z); res.w = fmaf(va.w, vb.w, vc.w); }; break;
+      case VRHI_T_FMA: {
+        float4 vc[G];
+        tape_fetch<G>(vc, I.kc, I.c, I.imm, prev, slots, tid);
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          res[g].x = fmaf(va[g].x, vb[g].x, vc[g].x); res[g].y = fmaf(va[g].y, vb[g].y, vc[g].y);
+          res[g].z = fmaf(va[g].z, vb[g].z, vc[g].z); res[g].w = fmaf(va[g].w, vb[g].w, vc[g].w);
+        }
+        break;
+      }
       case VRHI_T_NEG: TAPE_U(-a); break;
       case VRHI_T_ABS: TAPE_U(fabsf(a)); break;
       case VRHI_T_SQUARE: TAPE_U(a * a); break;
@@ -185,14 +218,23 @@ __device__ __forceinline__ void tape_run(const TapeDev &T, float4 *slots /* [slo
       case VRHI_T_SIGN: TAPE_U((a > 0.f) ? 1.f : ((a < 0.f) ? -1.f : 0.f)); break;
       case VRHI_T_STEP: TAPE_U(a > 0.f ? 1.f : 0.f); break;
       case VRHI_T_EQ: TAPE_B(a == b ? 1.f : 0.f); break;
-      default: res = make_float4(0.f, 0.f, 0.f, 0.f); break;
+      default:
+#pragma unroll
+        for (int g = 0; g < G; ++g) res[g] = make_float4(0.f, 0.f, 0.f, 0.f);
+        break;
     }
-    slots[I.dst * kTapeThreads + tid] = res;
+    if (I.keep) {
+#pragma unroll
+      for (int g = 0; g < G; ++g) slots[(I.dst * G + g) * kTapeThreads + tid] = res[g];
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) prev[g] = res[g];
   }
 }
 
 // Vector path: cols % 4 == 0.  blockIdx.x walks column groups of kTapeThreads float4s,
-// blockIdx.y strides over rows, so a broadcast row vector is loaded once per thread.
+// blockIdx.y strides over rows (G rows per trip), so a broadcast row vector is loaded once per thread.
+template <int G>
 __global__ void __launch_bounds__(kTapeThreads) map_tape_vec_kernel(const __grid_constant__ TapeDev T) {
   extern __shared__ float4 slots[];
   const int tid = threadIdx.x;
@@ -210,26 +252,36 @@ __global__ void __launch_bounds__(kTapeThreads) map_tape_vec_kernel(const __grid
       rowvec[k] = make_float4(s, s, s, s);
     }
   }
-  for (uint64_t r = blockIdx.y; r < T.rows; r += gridDim.y) {
-    const uint64_t e4 = r * cols4 + cg;
+  for (uint64_t r0 = (uint64_t)blockIdx.y * G; r0 < T.rows; r0 += (uint64_t)gridDim.y * G) {
 #pragma unroll
     for (int k = 0; k < VRHI_TAPE_MAX_INPUTS; ++k) {
-      if (k < (int)T.n_inputs) {
-        float4 v = rowvec[k];
-        if ((T.col_vector_mask >> k) & 1u) {
-          const float s = T.in[k][r];
-          v = make_float4(s, s, s, s);
-        } else if (!(((T.row_vector_mask | T.scalar_mask) >> k) & 1u) && in_range) {
-          v = ld_stream(reinterpret_cast<const float4 *>(T.in[k]) + e4);
+      if (k < (int)T.n_inputs && T.in_slot[k] != 255) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          const uint64_t r = r0 + g;
+          float4 v = rowvec[k];
+          if (r < T.rows) {
+            if ((T.col_vector_mask >> k) & 1u) {
+              const float s = T.in[k][r];
+              v = make_float4(s, s, s, s);
+            } else if (!(((T.row_vector_mask | T.scalar_mask) >> k) & 1u) && in_range) {
+              v = ld_stream(reinterpret_cast<const float4 *>(T.in[k]) + r * cols4 + cg);
+            }
+          }
+          slots[(T.in_slot[k] * G + g) * kTapeThreads + tid] = v;
         }
-        slots[T.in_slot[k] * kTapeThreads + tid] = v;
       }
     }
-    tape_run(T, slots);
+    tape_run<G>(T, slots);
     if (in_range) {
 #pragma unroll
       for (int k = 0; k < VRHI_TAPE_MAX_OUTPUTS; ++k)
-        if (k < (int)T.n_outputs) st_stream(reinterpret_cast<float4 *>(T.out[k]) + e4, slots[T.out_slot[k] * kTapeThreads + tid]);
+        if (k < (int)T.n_outputs) {
+#pragma unroll
+          for (int g = 0; g < G; ++g)
+            if (r0 + g < T.rows)
+              st_stream(reinterpret_cast<float4 *>(T.out[k]) + (r0 + g) * cols4 + cg, slots[(T.out_slot[k] * G + g) * kTapeThreads + tid]);
+        }
     }
   }
 }
@@ -245,6 +297,7 @@ __global__ void __launch_bounds__(kTapeThreads) map_tape_scalar_kernel(const __g
     const bool in_range = e < n;
     const uint64_t col = in_range ? e % T.cols : 0;
     for (uint32_t k = 0; k < T.n_inputs; ++k) {
+      if (T.in_slot[k] == 255) continue;
       float v = 0.f;
       if (in_range) {
         if ((T.row_vector_mask >> k) & 1u) v = T.in[k][col];
@@ -254,7 +307,7 @@ __global__ void __launch_bounds__(kTapeThreads) map_tape_scalar_kernel(const __g
       }
       slots[T.in_slot[k] * kTapeThreads + tid] = make_float4(v, v, v, v);
     }
-    tape_run(T, slots);
+    tape_run<1>(T, slots);
     if (in_range)
       for (uint32_t k = 0; k < T.n_outputs; ++k) T.out[k][e] = slots[T.out_slot[k] * kTapeThreads + tid].x;
   }
@@ -269,60 +322,124 @@ static int tape_arity(int op) {
   }
 }
 
-// Linear-scan slot assignment: a value's slot is freed after its last use.
-static int assign_slots(const vrhi_tape_params &q, TapeDev *T) {
-  const uint32_t nv = q.n_inputs + q.n_instr;
-  int last_use[VRHI_TAPE_MAX_INPUTS + VRHI_TAPE_MAX_INSTR];
-  int slot_of[VRHI_TAPE_MAX_INPUTS + VRHI_TAPE_MAX_INSTR];
-  for (uint32_t v = 0; v < nv; ++v) { last_use[v] = -1; slot_of[v] = -1; }
-  for (uint32_t t = 0; t < q.n_instr; ++t) {
+// SSA tape -> physical program (see the comment at the top of this section).
+static int plan_tape(const vrhi_tape_params &q, TapeDev *T, int max_slots) {
+  const int NI = (int)q.n_inputs, NT = (int)q.n_instr, NV = NI + NT;
+  constexpr int MAXV = VRHI_TAPE_MAX_INPUTS + VRHI_TAPE_MAX_INSTR;
+  bool is_const[MAXV] = {}, is_output[MAXV] = {};
+  float const_val[MAXV] = {};
+  int phys_of[MAXV];    // value -> index of the physical instruction defining it (-1: input or folded constant)
+  int last_use[MAXV];   // value -> last physical instruction reading it (NP for outputs)
+  bool far_use[MAXV] = {};  // read by something other than the next physical instruction
+  for (int v = 0; v < NV; ++v) { phys_of[v] = -1; last_use[v] = -1; }
+  // validate, mark constants
+  for (int t = 0; t < NT; ++t) {
     const vrhi_tape_instr &I = q.instr[t];
-    if (I.op >= VRHI_T_OPCOUNT) return fail(VRHI_ERR_INVALID, "map_tape: instruction %u has unknown opcode %u", t, I.op);
+    if (I.op >= VRHI_T_OPCOUNT) return fail(VRHI_ERR_INVALID, "map_tape: instruction %d has unknown opcode %u", t, I.op);
     const int ar = tape_arity(I.op);
     const uint16_t src[3] = {I.a, I.b, I.c};
-    for (int s = 0; s < ar; ++s) {
-      if (src[s] >= q.n_inputs + t) return fail(VRHI_ERR_INVALID, "map_tape: instruction %u reads value %u before it is defined", t, src[s]);
-      last_use[src[s]] = (int)t;
-    }
+    for (int s = 0; s < ar; ++s)
+      if (src[s] >= NI + t) return fail(VRHI_ERR_INVALID, "map_tape: instruction %d reads value %u before it is defined", t, src[s]);
+    if (I.op == VRHI_T_CONST) { is_const[NI + t] = true; const_val[NI + t] = I.imm; }
   }
   for (uint32_t k = 0; k < q.n_outputs; ++k) {
-    if (q.out_value[k] >= nv) return fail(VRHI_ERR_INVALID, "map_tape: output %u names value %u, which does not exist", k, q.out_value[k]);
-    last_use[q.out_value[k]] = (int)q.n_instr;  // live to the end
+    if ((int)q.out_value[k] >= NV) return fail(VRHI_ERR_INVALID, "map_tape: output %u names value %u, which does not exist", k, q.out_value[k]);
+    is_output[q.out_value[k]] = true;
   }
-  bool busy[kTapeMaxSlots] = {};
+  // physical instruction list: every non-constant instruction; a constant is materialised only
+  // where it cannot be an immediate (second immediate of one instruction, or an output)
+  struct Phys { int ssa; int op; int src[3]; int ar; bool mat_const; float imm; };
+  Phys phys[VRHI_TAPE_MAX_INSTR * 2];
+  int NP = 0;
+  auto materialise = [&](int v) -> int {
+    if (phys_of[v] >= 0) return VRHI_OK;
+    if (NP >= VRHI_TAPE_MAX_INSTR) return fail(VRHI_ERR_UNSUPPORTED, "map_tape: program too long after materialising constants");
+    phys[NP] = Phys{v, VRHI_T_CONST, {0, 0, 0}, 0, true, const_val[v]};
+    phys_of[v] = NP++;
+    return VRHI_OK;
+  };
+  for (uint32_t k = 0; k < q.n_outputs; ++k)
+    if (is_const[q.out_value[k]]) VRHI_TRY(materialise((int)q.out_value[k]));
+  for (int t = 0; t < NT; ++t) {
+    const vrhi_tape_instr &I = q.instr[t];
+    if (I.op == VRHI_T_CONST) continue;
+    const int ar = tape_arity(I.op);
+    const int src[3] = {I.a, I.b, I.c};
+    bool have_imm = false;
+    float first_imm = 0.f;
+    for (int s = 0; s < ar; ++s)
+      if (is_const[src[s]] && phys_of[src[s]] < 0) {
+        // the first constant operand rides along as the instruction's immediate; a second one can
+        // share it only if it is the same number, otherwise it becomes a stored value
+        if (!have_imm) { have_imm = true; first_imm = const_val[src[s]]; }
+        else if (memcmp(&const_val[src[s]], &first_imm, sizeof(float)) != 0) VRHI_TRY(materialise(src[s]));
+      }
+    if (NP >= VRHI_TAPE_MAX_INSTR) return fail(VRHI_ERR_UNSUPPORTED, "map_tape: program too long after materialising constants");
+    phys[NP] = Phys{NI + t, (int)I.op, {src[0], src[1], src[2]}, ar, false, 0.f};
+    phys_of[NI + t] = NP++;
+  }
+  // uses
+  for (int p = 0; p < NP; ++p)
+    for (int s = 0; s < phys[p].ar; ++s) {
+      const int v = phys[p].src[s];
+      if (is_const[v] && phys_of[v] < 0) continue;  // immediate
+      last_use[v] = p;
+      if (phys_of[v] < 0 || phys_of[v] != p - 1) far_use[v] = true;  // inputs are always "far": they live in slots
+    }
+  for (int v = 0; v < NV; ++v)
+    if (is_output[v]) { last_use[v] = NP; far_use[v] = true; }
+  // slots by linear scan
+  bool busy[64] = {};
+  int slot_of[MAXV];
+  for (int v = 0; v < NV; ++v) slot_of[v] = -1;
   int n_slots = 0;
   auto take = [&]() -> int {
-    for (int s = 0; s < kTapeMaxSlots; ++s)
+    for (int s = 0; s < max_slots; ++s)
       if (!busy[s]) { busy[s] = true; if (s + 1 > n_slots) n_slots = s + 1; return s; }
     return -1;
   };
-  for (uint32_t k = 0; k < q.n_inputs; ++k) {
+  for (int k = 0; k < NI; ++k) {
+    T->in_slot[k] = 255;
+    if (last_use[k] < 0) continue;  // never read
     int s = take();
-    if (s < 0) return fail(VRHI_ERR_UNSUPPORTED, "map_tape: more than %d values live at once", kTapeMaxSlots);
+    if (s < 0) return fail(VRHI_ERR_UNSUPPORTED, "map_tape: more than %d values live at once", max_slots);
     slot_of[k] = s;
     T->in_slot[k] = (uint8_t)s;
   }
-  for (uint32_t t = 0; t < q.n_instr; ++t) {
-    const vrhi_tape_instr &I = q.instr[t];
-    const int ar = tape_arity(I.op);
-    const uint16_t src[3] = {I.a, I.b, I.c};
+  for (int p = 0; p < NP; ++p) {
+    const Phys &P = phys[p];
     TapeInstrDev D{};
-    D.op = (uint8_t)I.op;
-    D.imm = I.imm;
-    uint8_t ss[3] = {0, 0, 0};
-    for (int s = 0; s < ar; ++s) ss[s] = (uint8_t)slot_of[src[s]];
-    D.a = ss[0]; D.b = ar >= 2 ? ss[1] : ss[0]; D.c = ar >= 3 ? ss[2] : ss[0];
-    // sources whose last use is this instruction release their slot before the result is placed
-    for (int s = 0; s < ar; ++s)
-      if (last_use[src[s]] == (int)t) busy[slot_of[src[s]]] = false;
-    int d = take();
-    if (d < 0) return fail(VRHI_ERR_UNSUPPORTED, "map_tape: more than %d values live at once", kTapeMaxSlots);
-    slot_of[q.n_inputs + t] = d;
-    D.dst = (uint8_t)d;
-    if (last_use[q.n_inputs + t] < 0) busy[d] = false;  // dead value
-    T->instr[t] = D;
+    D.op = (uint8_t)P.op;
+    D.ka = D.kb = D.kc = OPK_NONE;
+    uint8_t *kinds[3] = {&D.ka, &D.kb, &D.kc}, *idxs[3] = {&D.a, &D.b, &D.c};
+    if (P.mat_const) { D.ka = OPK_IMM; D.imm = P.imm; }
+    for (int s = 0; s < P.ar; ++s) {
+      const int v = P.src[s];
+      if (is_const[v] && phys_of[v] < 0) { *kinds[s] = OPK_IMM; D.imm = const_val[v]; }
+      else if (phys_of[v] >= 0 && phys_of[v] == p - 1) *kinds[s] = OPK_PREV;
+      else { *kinds[s] = OPK_SLOT; *idxs[s] = (uint8_t)slot_of[v]; }
+    }
+    // operands whose last use is here release their slot before the result is placed
+    for (int s = 0; s < P.ar; ++s) {
+      const int v = P.src[s];
+      if (slot_of[v] >= 0 && last_use[v] == p) busy[slot_of[v]] = false;
+    }
+    const int v = P.ssa;
+    if (far_use[v]) {
+      int d = take();
+      if (d < 0) return fail(VRHI_ERR_UNSUPPORTED, "map_tape: more than %d values live at once", max_slots);
+      slot_of[v] = d;
+      D.dst = (uint8_t)d;
+      D.keep = 1;
+    }
+    T->instr[p] = D;
   }
-  for (uint32_t k = 0; k < q.n_outputs; ++k) T->out_slot[k] = (uint8_t)slot_of[q.out_value[k]];
+  for (uint32_t k = 0; k < q.n_outputs; ++k) {
+    const int v = (int)q.out_value[k];
+    if (slot_of[v] < 0) return fail(VRHI_ERR_INVALID, "map_tape: output %u has no storage", k);
+    T->out_slot[k] = (uint8_t)slot_of[v];
+  }
+  T->n_instr = (uint32_t)NP;
   T->n_slots = (uint32_t)n_slots;
   return VRHI_OK;
 }
@@ -335,13 +452,14 @@ int launch_map_tape(vrhi_stream_t *st, const ArgView *args, int n_args, const vo
   if (n_args != (int)(q.n_inputs + q.n_outputs)) return fail(VRHI_ERR_INVALID, "map_tape: %d arguments passed, tape declares %u inputs + %u outputs", n_args, q.n_inputs, q.n_outputs);
   const uint64_t n = q.rows * q.cols;
   if (n == 0) return VRHI_OK;
-  TapeDev T{};
-  T.n_inputs = q.n_inputs; T.n_outputs = q.n_outputs; T.n_instr = q.n_instr;
-  T.row_vector_mask = q.row_vector_mask; T.col_vector_mask = q.col_vector_mask; T.scalar_mask = q.scalar_mask;
-  T.rows = q.rows; T.cols = q.cols;
   if ((q.row_vector_mask & q.col_vector_mask) | (q.row_vector_mask & q.scalar_mask) | (q.col_vector_mask & q.scalar_mask))
     return fail(VRHI_ERR_INVALID, "map_tape: an input is marked with more than one broadcast shape");
-  VRHI_TRY(assign_slots(q, &T));
+  TapeDev T{};
+  T.n_inputs = q.n_inputs; T.n_outputs = q.n_outputs;
+  T.row_vector_mask = q.row_vector_mask; T.col_vector_mask = q.col_vector_mask; T.scalar_mask = q.scalar_mask;
+  T.rows = q.rows; T.cols = q.cols;
+  const int slot_capacity = kTapeSlotBytes / (kTapeThreads * (int)sizeof(float4));  // 24 slots of one group
+  VRHI_TRY(plan_tape(q, &T, slot_capacity));
   for (uint32_t k = 0; k < q.n_inputs; ++k) {
     uint64_t need = ((q.row_vector_mask >> k) & 1u) ? q.cols * 4 : ((q.col_vector_mask >> k) & 1u) ? q.rows * 4 : ((q.scalar_mask >> k) & 1u) ? 4 : n * 4;
     if (args[k].bytes < need) return fail(VRHI_ERR_SIZE, "map_tape: input %u holds %llu bytes, %llu needed", k, (unsigned long long)args[k].bytes, (unsigned long long)need);
@@ -353,20 +471,26 @@ int launch_map_tape(vrhi_stream_t *st, const ArgView *args, int n_args, const vo
     if (!writable(o)) return fail(VRHI_ERR_INVALID, "map_tape: output %u is read-only (class %s)", k, vrhi_arg_class_name(o.buf_cls));
     T.out[k] = (float *)o.ptr;
   }
-  const size_t smem = (size_t)(T.n_slots ? T.n_slots : 1) * kTapeThreads * sizeof(float4);
   const int sms = st->dev->prop.multiProcessorCount;
+  const uint32_t ns = T.n_slots ? T.n_slots : 1;
   if (q.cols % 4 == 0) {
+    // two row groups per thread when the slots of both fit in 48 KiB of shared memory and there are rows to pair
+    const int G = (ns * 2 <= (uint32_t)slot_capacity && q.rows >= 2) ? 2 : 1;
+    const size_t smem = (size_t)ns * G * kTapeThreads * sizeof(float4);
     uint64_t cols4 = q.cols / 4;
     uint64_t gx = (cols4 + kTapeThreads - 1) / kTapeThreads;
     if (gx > 0x7fffffffull) return fail(VRHI_ERR_UNSUPPORTED, "map_tape: too many columns");
     uint64_t target = (uint64_t)sms * 8;
     uint64_t gy = (target + gx - 1) / gx;
-    if (gy > q.rows) gy = q.rows;
+    uint64_t row_groups = (q.rows + G - 1) / G;
+    if (gy > row_groups) gy = row_groups;
     if (gy > 65535) gy = 65535;
     if (gy == 0) gy = 1;
     dim3 grid((unsigned)gx, (unsigned)gy);
-    map_tape_vec_kernel<<<grid, kTapeThreads, smem, st->s>>>(T);
+    if (G == 2) map_tape_vec_kernel<2><<<grid, kTapeThreads, smem, st->s>>>(T);
+    else map_tape_vec_kernel<1><<<grid, kTapeThreads, smem, st->s>>>(T);
   } else {
+    const size_t smem = (size_t)ns * kTapeThreads * sizeof(float4);
     uint64_t want = (n + kTapeThreads - 1) / kTapeThreads;
     uint64_t cap = (uint64_t)sms * 8;
     map_tape_scalar_kernel<<<(unsigned)(want < cap ? want : cap), kTapeThreads, smem, st->s>>>(T);

@@ -210,7 +210,9 @@ static int mse_plan(vrhi_stream_t *st, const ArgView *args, int n_in_out, const 
   pl->denom = q.denom > 0.0 ? q.denom : (double)q.rows * (double)q.cols;
   const int sms = st->dev->prop.multiProcessorCount;
   const uint64_t gx = (q.cols + 1023) / 1024;
-  uint64_t gy = ((uint64_t)sms * 8 + gx - 1) / gx;
+  // four 256-thread CTAs are resident per SM at this kernel's register count: one full wave,
+  // and as few partial rows for the finalize kernels as that allows
+  uint64_t gy = ((uint64_t)sms * 4 + gx - 1) / gx;
   if (gy > q.rows) gy = q.rows;
   if (gy > 4096) gy = 4096;
   if (gx > 0x7fffffffull) return fail(VRHI_ERR_UNSUPPORTED, "%s: too many columns", name);

@@ -363,16 +363,23 @@ __global__ void __launch_bounds__(256) col_partial_kernel(const float *__restric
 
 __global__ void __launch_bounds__(256) col_finalize_kernel(const float *__restrict__ partial, float *__restrict__ out,
                                                            uint32_t groups, uint64_t cols, float scale) {
-  const uint64_t c = (uint64_t)blockIdx.x * 256 + threadIdx.x;
+  const uint64_t c = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= cols) return;
-  float s = 0.f;
-  for (uint32_t g = 0; g < groups; ++g) s += partial[(uint64_t)g * cols + c];
-  out[c] = s * scale;
+  // eight interleaved partial sums keep eight loads in flight; they are combined in a fixed tree,
+  // so the result depends on `groups` only, never on scheduling
+  float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  uint32_t g = 0;
+  for (; g + 8 <= groups; g += 8) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) s[k] += partial[(uint64_t)(g + k) * cols + c];
+  }
+  for (int k = 0; g < groups; ++g, ++k) s[k] += partial[(uint64_t)g * cols + c];
+  out[c] = (((s[0] + s[1]) + (s[2] + s[3])) + ((s[4] + s[5]) + (s[6] + s[7]))) * scale;
 }
 
 // Shared with the backward kernel: sums `groups` partial rows of `cols` floats into out.
 int col_finalize(vrhi_stream_t *st, const float *partial, float *out, uint32_t groups, uint64_t cols, float scale) {
-  col_finalize_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, st->s>>>(partial, out, groups, cols, scale);
+  col_finalize_kernel<<<(unsigned)((cols + 63) / 64), 64, 0, st->s>>>(partial, out, groups, cols, scale);
   return post_launch(st, "col_finalize");
 }
 
@@ -482,7 +489,7 @@ extern "C" int vrhi_col_sum_static_scratch(const float *in_device, float *out_de
   col_partial_kernel<<<grid, 256, 0, s>>>(in_device, partials, rows, cols);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(VRHI_ERR_CUDA, "launch of col_sum_static_scratch (partials) failed: %s", cudaGetErrorString(e));
-  col_finalize_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, s>>>(partials, out_device, (uint32_t)gy, cols, 1.0f);
+  col_finalize_kernel<<<(unsigned)((cols + 63) / 64), 64, 0, s>>>(partials, out_device, (uint32_t)gy, cols, 1.0f);
   e = cudaGetLastError();
   if (e != cudaSuccess) return fail(VRHI_ERR_CUDA, "launch of col_sum_static_scratch (finalize) failed: %s", cudaGetErrorString(e));
   return VRHI_OK;

@@ -146,7 +146,9 @@ class PeerImageExchange:
         self._flag = torch.zeros(1, device=f"cuda:{dev.ordinal}")
 
     def push(self, stream, slab_range=None) -> None:
-        """Enqueue on ``stream`` the copies of this rank's chunks of slabs lo..hi-1 into every peer."""
+        """Enqueue the copies of this rank's chunks of slabs lo..hi-1 into every peer.  ``stream`` is one
+        stream, or a list with one stream per peer so that the pushes to different peers run on
+        different copy engines at the same time."""
         lo, hi = slab_range if slab_range is not None else (0, self.n_slabs)
         if hi <= lo:
             return
@@ -154,9 +156,10 @@ class PeerImageExchange:
         offset = (lo * world + rank) * self.chunk_bytes
         pitch = world * self.chunk_bytes
         # start with the next rank so that, at any moment, the ranks write to different peers
+        streams = stream if isinstance(stream, (list, tuple)) else [stream] * (world - 1)
         for step in range(1, world):
             peer = self.peers[(rank + step) % world]
-            self.image.copy_2d_to(peer, offset, pitch, offset, pitch, self.chunk_bytes, hi - lo, stream)
+            self.image.copy_2d_to(peer, offset, pitch, offset, pitch, self.chunk_bytes, hi - lo, streams[step - 1])
 
     def finish(self, torch_stream) -> None:
         """Stream-ordered completion: after this, all ranks' pushes are visible in this rank's image."""

@@ -502,13 +502,41 @@ def main():
     chunks = plan.chunks() if world > 1 else [(0, H)]
     host = vd.PinnedArray((sum(n for _, n in chunks), W), np.uint32)
 
+    # The rank's rows are computed in E2E_GROUPS launches; the download of a finished group runs on a
+    # copy stream while the next group computes, so a step costs about max(compute, PCIe transfer).
+    E2E_GROUPS = 8
+    own = ops.partition_rows(H, world, rank, L.PART_CYCLIC, 128)
+    e2e_groups = []
+    row_cursor = 0
+    for gidx in range(E2E_GROUPS):
+        k0, k1 = own.chunk_count * gidx // E2E_GROUPS, own.chunk_count * (gidx + 1) // E2E_GROUPS
+        if k1 == k0:
+            continue
+        gp = ops.escape_params(L.JULIA, W, H, J["x0"], J["y0"], dx, dy, cr=J["cr"], ci=J["ci"], max_iter=J["max_iter"], partition=own)
+        gp.chunk_first = own.chunk_first + k0 * own.chunk_step
+        gp.chunk_count = k1 - k0
+        spans = []
+        for k in range(k0, k1):
+            r0 = (own.chunk_first + k * own.chunk_step) * own.chunk_rows
+            n = min(H, r0 + own.chunk_rows) - r0
+            if spans and world == 1 and spans[-1][0] + spans[-1][1] == r0:
+                spans[-1] = (spans[-1][0], spans[-1][1] + n, spans[-1][2])   # contiguous on one GPU: one copy
+            else:
+                spans.append((r0, n, row_cursor))
+            row_cursor += n
+        e2e_groups.append((gp, spans))
+    copy_tstream = torch.cuda.Stream(device=local)
+    copy_st = dev.wrap_stream(copy_tstream.cuda_stream)
+
     def e2e_step():
-        compute()
-        row = 0
-        for r0, n in chunks:
-            image.download(host.array[row:row + n], offset=r0 * W * 4, stream=st)
-            row += n
-        st.synchronize()
+        for gp, spans in e2e_groups:
+            ops.escape_time(st, image, gp)
+            ev = torch.cuda.Event()
+            ev.record(tstream)
+            copy_tstream.wait_event(ev)
+            for r0, n, dst_row in spans:
+                image.download(host.array[dst_row:dst_row + n], offset=r0 * W * 4, stream=copy_st)
+        copy_st.synchronize()
 
     for _ in range(2):
         e2e_step()

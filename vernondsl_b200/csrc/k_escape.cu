@@ -390,9 +390,13 @@ int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const
                           q.max_iter >= 64u && q.max_iter <= (1u << 30) && (uint64_t)q.width * q.height <= 0xffffffffull &&
                           (q.kind == VRHI_ESCAPE_MANDELBROT || c2 <= 2.25) && !(q.flags & VRHI_ESCAPE_FLAG_CHECKED_ONLY);
   if (regroup_ok) {
-    // 6 CTAs of 256 threads fit per SM at this register count; fewer warps than that when the image is small
+    // Measured on B200: 3-4 CTAs of 256 threads per SM are as fast as the 6 that fit (the kernel is
+    // issue-bound, not latency-bound); small images run faster still with 2, because each warp then
+    // owns enough tiles to keep its pool busy and the drain at the end is shorter.
     uint64_t ctas = (nb + 7) / 8;
-    uint64_t cap = (uint64_t)sms * 6;
+    const uint64_t tiles_total = (uint64_t)p.tiles_per_row * p.rows_owned;
+    const uint64_t per_sm = tiles_total / ((uint64_t)sms * 4 * 8) < 32 ? 2 : 4;
+    uint64_t cap = (uint64_t)sms * per_sm;
     grid = (int)(ctas < cap ? ctas : cap);
     // Tuning aid: VRHI_ESCAPE_TUNE="U,T[,ctas_per_sm]" selects another block length / refill threshold for
     // uint32 output (the shipped default is what measurements on B200 favoured).

@@ -114,32 +114,34 @@ int launch_fused_map(vrhi_stream_t *st, const ArgView *args, int n_args, const v
 
 // ---------------------------------------------------------------------------------------------
 // Generic fused tape.  The caller's tape is in SSA form (instruction t defines value
-// n_inputs + t).  The host turns it into a short physical program:
-//   * constants become immediate operands (no instruction, no storage);
-//   * a value consumed only by the very next instruction stays in registers ("PREV" operand);
-//   * every other value gets a slot, assigned by a linear scan over live ranges.
-// The kernel keeps one float4 per slot per element group per thread in shared memory
-// ([slot][group][thread], conflict free), handles G groups (4*G elements) per thread per trip so
-// that decoding an instruction is paid once per 4*G elements, and walks the program with
-// branches that are uniform across the CTA (no divergence).  Long chains are bound by
-// instruction issue and shared-memory traffic rather than HBM; the specialised kernels above
-// exist for the chains that matter most.
+// n_inputs + t).  The host turns it into a short physical program over SLOTS: every input, every
+// constant and every intermediate value lives in a slot (one float4 per element group per
+// thread, in shared memory, laid out [slot][group][thread] so that accesses are conflict free);
+// slots are assigned by a linear scan over live ranges and constants are written once per
+// kernel.  The kernel handles G groups (4*G elements) per thread per trip, so that decoding an
+// instruction is paid once per 4*G elements, and dispatches in two levels (operation class, then
+// operation) with branches that are uniform across the CTA.  Long chains are bound by instruction
+// issue and shared-memory traffic rather than by HBM; the specialised kernels above exist for the
+// chains that matter most.
 
 constexpr int kTapeThreads = 128;
-constexpr int kTapeSlotBytes = 48 * 1024;  // the default dynamic shared-memory limit
+constexpr int kTapeSlotBytes = 44 * 1024;  // slots; the staged programs (4 KiB) share the default 48 KiB limit
 
-enum { OPK_SLOT = 0, OPK_PREV = 1, OPK_IMM = 2, OPK_NONE = 3 };
+enum { CLS_BINARY = 0, CLS_UNARY = 1, CLS_TRANS = 2, CLS_FMA = 3 };
 
+// One physical instruction: 32 bytes, word-sized fields (no byte unpacking on the device).
+// dst / a / b / c are slot indices.
 struct TapeInstrDev {
-  uint8_t op, dst, keep, ka, kb, kc, a, b, c, pad[3];
-  float imm;
+  uint32_t cls, op, dst, a, b, c, pad0, pad1;
 };
 
 struct TapeDev {
-  uint32_t n_inputs, n_outputs, n_instr, n_slots;
+  uint32_t n_inputs, n_outputs, n_instr, n_slots, n_consts;
   uint32_t row_vector_mask, col_vector_mask, scalar_mask;
   uint8_t in_slot[VRHI_TAPE_MAX_INPUTS];   // 255: the input is never read
   uint8_t out_slot[VRHI_TAPE_MAX_OUTPUTS];
+  uint8_t const_slot[16];
+  float const_val[16];
   TapeInstrDev instr[VRHI_TAPE_MAX_INSTR];
   const float *in[VRHI_TAPE_MAX_INPUTS];
   float *out[VRHI_TAPE_MAX_OUTPUTS];
@@ -148,148 +150,197 @@ struct TapeDev {
 
 #define TAPE_U(EXPR)                                                                              \
   _Pragma("unroll") for (int g = 0; g < G; ++g) {                                                 \
-    { const float a = va[g].x; res[g].x = (EXPR); } { const float a = va[g].y; res[g].y = (EXPR); } \
-    { const float a = va[g].z; res[g].z = (EXPR); } { const float a = va[g].w; res[g].w = (EXPR); } \
+    const float4 va = pa[g * kTapeThreads];                                                       \
+    float4 r;                                                                                     \
+    { const float a = va.x; r.x = (EXPR); } { const float a = va.y; r.y = (EXPR); }               \
+    { const float a = va.z; r.z = (EXPR); } { const float a = va.w; r.w = (EXPR); }               \
+    pd[g * kTapeThreads] = r;                                                                     \
   }
 #define TAPE_B(EXPR)                                                                              \
   _Pragma("unroll") for (int g = 0; g < G; ++g) {                                                 \
-    { const float a = va[g].x, b = vb[g].x; res[g].x = (EXPR); } { const float a = va[g].y, b = vb[g].y; res[g].y = (EXPR); } \
-    { const float a = va[g].z, b = vb[g].z; res[g].z = (EXPR); } { const float a = va[g].w, b = vb[g].w; res[g].w = (EXPR); } \
+    const float4 va = pa[g * kTapeThreads], vb = pb[g * kTapeThreads];                            \
+    float4 r;                                                                                     \
+    { const float a = va.x, b = vb.x; r.x = (EXPR); } { const float a = va.y, b = vb.y; r.y = (EXPR); } \
+    { const float a = va.z, b = vb.z; r.z = (EXPR); } { const float a = va.w, b = vb.w; r.w = (EXPR); } \
+    pd[g * kTapeThreads] = r;                                                                     \
   }
-
-template <int G>
-__device__ __forceinline__ void tape_fetch(float4 (&v)[G], int kind, int idx, float imm, const float4 (&prev)[G],
-                                           const float4 *slots, int tid) {
-  if (kind == OPK_SLOT) {
-#pragma unroll
-    for (int g = 0; g < G; ++g) v[g] = slots[(idx * G + g) * kTapeThreads + tid];
-  } else if (kind == OPK_PREV) {
-#pragma unroll
-    for (int g = 0; g < G; ++g) v[g] = prev[g];
-  } else {
-#pragma unroll
-    for (int g = 0; g < G; ++g) v[g] = make_float4(imm, imm, imm, imm);
-  }
-}
 
 // Executes the program on the G float4 groups held in the slots of this thread.
+// `mine` points at this thread's element of slot 0, group 0.
+// `prog` is the CTA's copy of the program in shared memory (broadcast reads, short latency).
 template <int G>
-__device__ __forceinline__ void tape_run(const TapeDev &T, float4 *slots /* [slot][G][kTapeThreads] */) {
-  const int tid = threadIdx.x;
-  float4 prev[G];
-#pragma unroll
-  for (int g = 0; g < G; ++g) prev[g] = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (uint32_t t = 0; t < T.n_instr; ++t) {
-    const TapeInstrDev I = T.instr[t];
-    float4 va[G], vb[G], res[G];
-    tape_fetch<G>(va, I.ka, I.a, I.imm, prev, slots, tid);
-    if (I.kb != OPK_NONE) tape_fetch<G>(vb, I.kb, I.b, I.imm, prev, slots, tid);
-    switch (I.op) {
-      case VRHI_T_CONST: TAPE_U(a); break;  // a materialised constant: operand a is the immediate
-      case VRHI_T_ADD: TAPE_B(a + b); break;
-      case VRHI_T_SUB: TAPE_B(a - b); break;
-      case VRHI_T_MUL: TAPE_B(a * b); break;
-      case VRHI_T_DIV: TAPE_B(a / b); break;
-      case VRHI_T_MAX: TAPE_B(fmaxf(a, b)); break;
-      case VRHI_T_MIN: TAPE_B(fminf(a, b)); break;
-      case VRHI_T_FMA: {
-        float4 vc[G];
-        tape_fetch<G>(vc, I.kc, I.c, I.imm, prev, slots, tid);
+__device__ __forceinline__ void tape_run(const TapeInstrDev *prog, uint32_t n_instr, float4 *mine) {
+  constexpr int kSlotStride = G * kTapeThreads;  // float4s between consecutive slots
+  TapeInstrDev I = prog[0];
+  for (uint32_t t = 0; t < n_instr; ++t) {
+    const TapeInstrDev cur = I;
+    I = prog[t + 1 < n_instr ? t + 1 : t];  // fetch the next instruction while this one executes
+    const float4 *pa = mine + cur.a * kSlotStride;
+    const float4 *pb = mine + cur.b * kSlotStride;
+    float4 *pd = mine + cur.dst * kSlotStride;
+    switch (cur.cls) {
+      case CLS_BINARY:
+        switch (cur.op) {
+          case VRHI_T_ADD: TAPE_B(a + b); break;
+          case VRHI_T_SUB: TAPE_B(a - b); break;
+          case VRHI_T_MUL: TAPE_B(a * b); break;
+          case VRHI_T_DIV: TAPE_B(a / b); break;
+          case VRHI_T_MAX: TAPE_B(fmaxf(a, b)); break;
+          case VRHI_T_MIN: TAPE_B(fminf(a, b)); break;
+          default: TAPE_B(a == b ? 1.f : 0.f); break;  // VRHI_T_EQ
+        }
+        break;
+      case CLS_UNARY:
+        switch (cur.op) {
+          case VRHI_T_NEG: TAPE_U(-a); break;
+          case VRHI_T_ABS: TAPE_U(fabsf(a)); break;
+          case VRHI_T_SQUARE: TAPE_U(a * a); break;
+          case VRHI_T_RELU: TAPE_U(fmaxf(a, 0.0f)); break;
+          case VRHI_T_SIGN: TAPE_U((a > 0.f) ? 1.f : ((a < 0.f) ? -1.f : 0.f)); break;
+          case VRHI_T_STEP: TAPE_U(a > 0.f ? 1.f : 0.f); break;
+          default: TAPE_U(a); break;  // VRHI_T_CONST as an output: copy of its slot
+        }
+        break;
+      case CLS_TRANS:
+        switch (cur.op) {
+          case VRHI_T_SQRT: TAPE_U(sqrtf(a)); break;
+          case VRHI_T_RSQRT: TAPE_U(1.0f / sqrtf(a)); break;
+          case VRHI_T_RECIP: TAPE_U(1.0f / a); break;
+          case VRHI_T_EXP: TAPE_U(expf(a)); break;
+          case VRHI_T_LOG: TAPE_U(logf(a)); break;
+          case VRHI_T_TANH: TAPE_U(tanhf(a)); break;
+          case VRHI_T_SIGMOID: TAPE_U(sigmoid_accurate(a)); break;
+          case VRHI_T_COS: TAPE_U(cosf(a)); break;
+          default: TAPE_U(sinf(a)); break;  // VRHI_T_SIN
+        }
+        break;
+      default: {  // CLS_FMA
+        const float4 *pc = mine + cur.c * kSlotStride;
 #pragma unroll
         for (int g = 0; g < G; ++g) {
-          res[g].x = fmaf(va[g].x, vb[g].x, vc[g].x); res[g].y = fmaf(va[g].y, vb[g].y, vc[g].y);
-          res[g].z = fmaf(va[g].z, vb[g].z, vc[g].z); res[g].w = fmaf(va[g].w, vb[g].w, vc[g].w);
+          const float4 va = pa[g * kTapeThreads], vb = pb[g * kTapeThreads], vc = pc[g * kTapeThreads];
+          pd[g * kTapeThreads] = make_float4(fmaf(va.x, vb.x, vc.x), fmaf(va.y, vb.y, vc.y), fmaf(va.z, vb.z, vc.z), fmaf(va.w, vb.w, vc.w));
         }
         break;
       }
-      case VRHI_T_NEG: TAPE_U(-a); break;
-      case VRHI_T_ABS: TAPE_U(fabsf(a)); break;
-      case VRHI_T_SQUARE: TAPE_U(a * a); break;
-      case VRHI_T_SQRT: TAPE_U(sqrtf(a)); break;
-      case VRHI_T_RSQRT: TAPE_U(1.0f / sqrtf(a)); break;
-      case VRHI_T_RECIP: TAPE_U(1.0f / a); break;
-      case VRHI_T_EXP: TAPE_U(expf(a)); break;
-      case VRHI_T_LOG: TAPE_U(logf(a)); break;
-      case VRHI_T_TANH: TAPE_U(tanhf(a)); break;
-      case VRHI_T_SIGMOID: TAPE_U(sigmoid_accurate(a)); break;
-      case VRHI_T_RELU: TAPE_U(fmaxf(a, 0.0f)); break;
-      case VRHI_T_COS: TAPE_U(cosf(a)); break;
-      case VRHI_T_SIN: TAPE_U(sinf(a)); break;
-      case VRHI_T_SIGN: TAPE_U((a > 0.f) ? 1.f : ((a < 0.f) ? -1.f : 0.f)); break;
-      case VRHI_T_STEP: TAPE_U(a > 0.f ? 1.f : 0.f); break;
-      case VRHI_T_EQ: TAPE_B(a == b ? 1.f : 0.f); break;
-      default:
-#pragma unroll
-        for (int g = 0; g < G; ++g) res[g] = make_float4(0.f, 0.f, 0.f, 0.f);
-        break;
     }
-    if (I.keep) {
-#pragma unroll
-      for (int g = 0; g < G; ++g) slots[(I.dst * G + g) * kTapeThreads + tid] = res[g];
-    }
-#pragma unroll
-    for (int g = 0; g < G; ++g) prev[g] = res[g];
   }
 }
 
+template <int G>
+__device__ __forceinline__ void tape_fill_consts(const TapeDev &T, float4 *mine) {
+  for (uint32_t k = 0; k < T.n_consts; ++k) {
+    const float v = T.const_val[k];
+#pragma unroll
+    for (int g = 0; g < G; ++g) mine[(T.const_slot[k] * G + g) * kTapeThreads] = make_float4(v, v, v, v);
+  }
+}
+
+__device__ __forceinline__ void cp_async_16(void *smem_dst, const void *gmem_src) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 // Vector path: cols % 4 == 0.  blockIdx.x walks column groups of kTapeThreads float4s,
 // blockIdx.y strides over rows (G rows per trip), so a broadcast row vector is loaded once per thread.
+//
+// Inputs are double buffered: slots [0, NI) hold the inputs of even trips, slots [NI, 2*NI) those of
+// odd trips, and the program exists in two copies that differ only in which of the two ranges they
+// name.  While the program of one trip runs, the full-size inputs of the next trip are already on
+// their way from HBM into the other range (cp.async, 16 bytes per thread per input per row, no
+// registers held), so the memory latency of a trip hides behind the arithmetic of the previous one.
 template <int G>
-__global__ void __launch_bounds__(kTapeThreads) map_tape_vec_kernel(const __grid_constant__ TapeDev T) {
+__global__ void __launch_bounds__(kTapeThreads, 8) map_tape_vec_kernel(const __grid_constant__ TapeDev T) {
   extern __shared__ float4 slots[];
   const int tid = threadIdx.x;
+  float4 *mine = slots + tid;
+  __shared__ TapeInstrDev prog[2][VRHI_TAPE_MAX_INSTR];
+  const uint32_t NI = T.n_inputs;
+  auto other = [NI](uint32_t s) -> uint32_t { return s < NI ? s + NI : (s < 2 * NI ? s - NI : s); };
+  for (uint32_t k = tid; k < T.n_instr; k += kTapeThreads) {
+    TapeInstrDev I = T.instr[k];
+    prog[0][k] = I;
+    I.dst = other(I.dst); I.a = other(I.a); I.b = other(I.b); I.c = other(I.c);
+    prog[1][k] = I;
+  }
+  tape_fill_consts<G>(T, mine);
+  __syncthreads();
   const uint64_t cols4 = T.cols / 4;
   const uint64_t cg = (uint64_t)blockIdx.x * kTapeThreads + tid;
   const bool in_range = cg < cols4;
+  const uint32_t bcast_mask = T.row_vector_mask | T.col_vector_mask | T.scalar_mask;
   float4 rowvec[VRHI_TAPE_MAX_INPUTS];
 #pragma unroll
   for (int k = 0; k < VRHI_TAPE_MAX_INPUTS; ++k) {
     rowvec[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (k < (int)T.n_inputs && ((T.row_vector_mask >> k) & 1u) && in_range)
+    if (k < (int)NI && ((T.row_vector_mask >> k) & 1u) && in_range)
       rowvec[k] = reinterpret_cast<const float4 *>(T.in[k])[cg];
-    if (k < (int)T.n_inputs && ((T.scalar_mask >> k) & 1u)) {
+    if (k < (int)NI && ((T.scalar_mask >> k) & 1u)) {
       const float s = T.in[k][0];
       rowvec[k] = make_float4(s, s, s, s);
     }
   }
-  for (uint64_t r0 = (uint64_t)blockIdx.y * G; r0 < T.rows; r0 += (uint64_t)gridDim.y * G) {
+  // asynchronous loads of the full-size inputs of the trip that starts at row r0 into range `stage`
+  auto prefetch = [&](uint64_t r0, uint32_t stage) {
+    if (in_range && r0 < T.rows) {
+      for (uint32_t k = 0; k < NI; ++k) {
+        if (((bcast_mask >> k) & 1u) || T.in_slot[k] == 255) continue;
 #pragma unroll
-    for (int k = 0; k < VRHI_TAPE_MAX_INPUTS; ++k) {
-      if (k < (int)T.n_inputs && T.in_slot[k] != 255) {
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-          const uint64_t r = r0 + g;
-          float4 v = rowvec[k];
-          if (r < T.rows) {
-            if ((T.col_vector_mask >> k) & 1u) {
-              const float s = T.in[k][r];
-              v = make_float4(s, s, s, s);
-            } else if (!(((T.row_vector_mask | T.scalar_mask) >> k) & 1u) && in_range) {
-              v = ld_stream(reinterpret_cast<const float4 *>(T.in[k]) + r * cols4 + cg);
-            }
-          }
-          slots[(T.in_slot[k] * G + g) * kTapeThreads + tid] = v;
-        }
+        for (int g = 0; g < G; ++g)
+          if (r0 + g < T.rows)
+            cp_async_16(mine + ((k + stage * NI) * G + g) * kTapeThreads, reinterpret_cast<const float4 *>(T.in[k]) + (r0 + g) * cols4 + cg);
       }
     }
-    tape_run<G>(T, slots);
+    cp_async_commit();
+  };
+  const uint64_t step = (uint64_t)gridDim.y * G;
+  uint64_t r0 = (uint64_t)blockIdx.y * G;
+  uint32_t stage = 0;
+  prefetch(r0, 0);
+  for (; r0 < T.rows; r0 += step, stage ^= 1u) {
+    prefetch(r0 + step, stage ^ 1u);  // commits a (possibly empty) group, so the wait below is uniform
+    cp_async_wait<1>();                // everything but the group just committed has landed
+    // broadcast inputs are written from registers into the current range
+    for (uint32_t k = 0; k < NI; ++k) {
+      if (!((bcast_mask >> k) & 1u) || T.in_slot[k] == 255) continue;
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float4 v = rowvec[k];
+        if (((T.col_vector_mask >> k) & 1u) && r0 + g < T.rows) {
+          const float s = T.in[k][r0 + g];
+          v = make_float4(s, s, s, s);
+        }
+        mine[((k + stage * NI) * G + g) * kTapeThreads] = v;
+      }
+    }
+    tape_run<G>(prog[stage], T.n_instr, mine);
     if (in_range) {
 #pragma unroll
       for (int k = 0; k < VRHI_TAPE_MAX_OUTPUTS; ++k)
         if (k < (int)T.n_outputs) {
+          const uint32_t os = stage ? other(T.out_slot[k]) : T.out_slot[k];
 #pragma unroll
           for (int g = 0; g < G; ++g)
             if (r0 + g < T.rows)
-              st_stream(reinterpret_cast<float4 *>(T.out[k]) + (r0 + g) * cols4 + cg, slots[(T.out_slot[k] * G + g) * kTapeThreads + tid]);
+              st_stream(reinterpret_cast<float4 *>(T.out[k]) + (r0 + g) * cols4 + cg, mine[(os * G + g) * kTapeThreads]);
         }
     }
   }
+  cp_async_wait<0>();
 }
 
 // Scalar path for any shape: one element per thread per trip (lane .x of the float4 slot).
 __global__ void __launch_bounds__(kTapeThreads) map_tape_scalar_kernel(const __grid_constant__ TapeDev T) {
   extern __shared__ float4 slots[];
   const int tid = threadIdx.x;
+  float4 *mine = slots + tid;
+  __shared__ TapeInstrDev prog[VRHI_TAPE_MAX_INSTR];
+  for (uint32_t k = tid; k < T.n_instr; k += kTapeThreads) prog[k] = T.instr[k];
+  tape_fill_consts<1>(T, mine);
+  __syncthreads();
   const uint64_t n = T.rows * T.cols;
   const uint64_t stride = (uint64_t)gridDim.x * kTapeThreads;
   for (uint64_t base = (uint64_t)blockIdx.x * kTapeThreads; base < n; base += stride) {
@@ -307,7 +358,7 @@ __global__ void __launch_bounds__(kTapeThreads) map_tape_scalar_kernel(const __g
       }
       slots[T.in_slot[k] * kTapeThreads + tid] = make_float4(v, v, v, v);
     }
-    tape_run<1>(T, slots);
+    tape_run<1>(prog, T.n_instr, mine);
     if (in_range)
       for (uint32_t k = 0; k < T.n_outputs; ++k) T.out[k][e] = slots[T.out_slot[k] * kTapeThreads + tid].x;
   }
@@ -327,118 +378,87 @@ static int plan_tape(const vrhi_tape_params &q, TapeDev *T, int max_slots) {
   const int NI = (int)q.n_inputs, NT = (int)q.n_instr, NV = NI + NT;
   constexpr int MAXV = VRHI_TAPE_MAX_INPUTS + VRHI_TAPE_MAX_INSTR;
   bool is_const[MAXV] = {}, is_output[MAXV] = {};
-  float const_val[MAXV] = {};
-  int phys_of[MAXV];    // value -> index of the physical instruction defining it (-1: input or folded constant)
-  int last_use[MAXV];   // value -> last physical instruction reading it (NP for outputs)
-  bool far_use[MAXV] = {};  // read by something other than the next physical instruction
-  for (int v = 0; v < NV; ++v) { phys_of[v] = -1; last_use[v] = -1; }
-  // validate, mark constants
+  int last_use[MAXV], slot_of[MAXV];
+  for (int v = 0; v < NV; ++v) { last_use[v] = -1; slot_of[v] = -1; }
   for (int t = 0; t < NT; ++t) {
     const vrhi_tape_instr &I = q.instr[t];
     if (I.op >= VRHI_T_OPCOUNT) return fail(VRHI_ERR_INVALID, "map_tape: instruction %d has unknown opcode %u", t, I.op);
     const int ar = tape_arity(I.op);
     const uint16_t src[3] = {I.a, I.b, I.c};
-    for (int s = 0; s < ar; ++s)
+    for (int s = 0; s < ar; ++s) {
       if (src[s] >= NI + t) return fail(VRHI_ERR_INVALID, "map_tape: instruction %d reads value %u before it is defined", t, src[s]);
-    if (I.op == VRHI_T_CONST) { is_const[NI + t] = true; const_val[NI + t] = I.imm; }
+      last_use[src[s]] = t;
+    }
+    if (I.op == VRHI_T_CONST) is_const[NI + t] = true;
   }
   for (uint32_t k = 0; k < q.n_outputs; ++k) {
     if ((int)q.out_value[k] >= NV) return fail(VRHI_ERR_INVALID, "map_tape: output %u names value %u, which does not exist", k, q.out_value[k]);
     is_output[q.out_value[k]] = true;
   }
-  // physical instruction list: every non-constant instruction; a constant is materialised only
-  // where it cannot be an immediate (second immediate of one instruction, or an output)
-  struct Phys { int ssa; int op; int src[3]; int ar; bool mat_const; float imm; };
-  Phys phys[VRHI_TAPE_MAX_INSTR * 2];
-  int NP = 0;
-  auto materialise = [&](int v) -> int {
-    if (phys_of[v] >= 0) return VRHI_OK;
-    if (NP >= VRHI_TAPE_MAX_INSTR) return fail(VRHI_ERR_UNSUPPORTED, "map_tape: program too long after materialising constants");
-    phys[NP] = Phys{v, VRHI_T_CONST, {0, 0, 0}, 0, true, const_val[v]};
-    phys_of[v] = NP++;
-    return VRHI_OK;
-  };
-  for (uint32_t k = 0; k < q.n_outputs; ++k)
-    if (is_const[q.out_value[k]]) VRHI_TRY(materialise((int)q.out_value[k]));
-  for (int t = 0; t < NT; ++t) {
-    const vrhi_tape_instr &I = q.instr[t];
-    if (I.op == VRHI_T_CONST) continue;
-    const int ar = tape_arity(I.op);
-    const int src[3] = {I.a, I.b, I.c};
-    bool have_imm = false;
-    float first_imm = 0.f;
-    for (int s = 0; s < ar; ++s)
-      if (is_const[src[s]] && phys_of[src[s]] < 0) {
-        // the first constant operand rides along as the instruction's immediate; a second one can
-        // share it only if it is the same number, otherwise it becomes a stored value
-        if (!have_imm) { have_imm = true; first_imm = const_val[src[s]]; }
-        else if (memcmp(&const_val[src[s]], &first_imm, sizeof(float)) != 0) VRHI_TRY(materialise(src[s]));
-      }
-    if (NP >= VRHI_TAPE_MAX_INSTR) return fail(VRHI_ERR_UNSUPPORTED, "map_tape: program too long after materialising constants");
-    phys[NP] = Phys{NI + t, (int)I.op, {src[0], src[1], src[2]}, ar, false, 0.f};
-    phys_of[NI + t] = NP++;
-  }
-  // uses
-  for (int p = 0; p < NP; ++p)
-    for (int s = 0; s < phys[p].ar; ++s) {
-      const int v = phys[p].src[s];
-      if (is_const[v] && phys_of[v] < 0) continue;  // immediate
-      last_use[v] = p;
-      if (phys_of[v] < 0 || phys_of[v] != p - 1) far_use[v] = true;  // inputs are always "far": they live in slots
-    }
-  for (int v = 0; v < NV; ++v)
-    if (is_output[v]) { last_use[v] = NP; far_use[v] = true; }
-  // slots by linear scan
   bool busy[64] = {};
-  int slot_of[MAXV];
-  for (int v = 0; v < NV; ++v) slot_of[v] = -1;
   int n_slots = 0;
   auto take = [&]() -> int {
-    for (int s = 0; s < max_slots; ++s)
+    for (int s = 0; s < max_slots && s < 64; ++s)
       if (!busy[s]) { busy[s] = true; if (s + 1 > n_slots) n_slots = s + 1; return s; }
     return -1;
   };
+  const char *too_many = "map_tape: more than %d values (inputs, constants, intermediates) live at once";
+  // inputs own slots 0..NI-1; slots NI..2*NI-1 are the second input buffer of the vector kernel
+  // and are never handed to intermediates (see map_tape_vec_kernel)
   for (int k = 0; k < NI; ++k) {
-    T->in_slot[k] = 255;
-    if (last_use[k] < 0) continue;  // never read
     int s = take();
-    if (s < 0) return fail(VRHI_ERR_UNSUPPORTED, "map_tape: more than %d values live at once", max_slots);
+    if (s != k) return fail(VRHI_ERR_UNSUPPORTED, too_many, max_slots);
     slot_of[k] = s;
-    T->in_slot[k] = (uint8_t)s;
+    T->in_slot[k] = (last_use[k] < 0 && !is_output[k]) ? 255 : (uint8_t)s;
   }
-  for (int p = 0; p < NP; ++p) {
-    const Phys &P = phys[p];
+  for (int k = 0; k < NI; ++k)
+    if (take() != NI + k) return fail(VRHI_ERR_UNSUPPORTED, too_many, max_slots);
+  // constants that are read hold a slot for the whole kernel (written once, before the first trip);
+  // equal constants share one
+  T->n_consts = 0;
+  for (int t = 0; t < NT; ++t) {
+    const int v = NI + t;
+    if (!is_const[v] || (last_use[v] < 0 && !is_output[v])) continue;
+    int found = -1;
+    for (uint32_t k = 0; k < T->n_consts; ++k)
+      if (memcmp(&T->const_val[k], &q.instr[t].imm, sizeof(float)) == 0) found = (int)k;
+    if (found < 0) {
+      if (T->n_consts >= 16) return fail(VRHI_ERR_UNSUPPORTED, "map_tape: more than 16 distinct constants");
+      int s = take();
+      if (s < 0) return fail(VRHI_ERR_UNSUPPORTED, too_many, max_slots);
+      found = (int)T->n_consts++;
+      T->const_slot[found] = (uint8_t)s;
+      T->const_val[found] = q.instr[t].imm;
+    }
+    slot_of[v] = T->const_slot[found];
+  }
+  int NP = 0;
+  for (int t = 0; t < NT; ++t) {
+    const vrhi_tape_instr &I = q.instr[t];
+    const int v = NI + t;
+    if (I.op == VRHI_T_CONST) continue;
+    const int ar = tape_arity(I.op);
+    const int src[3] = {I.a, I.b, I.c};
     TapeInstrDev D{};
-    D.op = (uint8_t)P.op;
-    D.ka = D.kb = D.kc = OPK_NONE;
-    uint8_t *kinds[3] = {&D.ka, &D.kb, &D.kc}, *idxs[3] = {&D.a, &D.b, &D.c};
-    if (P.mat_const) { D.ka = OPK_IMM; D.imm = P.imm; }
-    for (int s = 0; s < P.ar; ++s) {
-      const int v = P.src[s];
-      if (is_const[v] && phys_of[v] < 0) { *kinds[s] = OPK_IMM; D.imm = const_val[v]; }
-      else if (phys_of[v] >= 0 && phys_of[v] == p - 1) *kinds[s] = OPK_PREV;
-      else { *kinds[s] = OPK_SLOT; *idxs[s] = (uint8_t)slot_of[v]; }
-    }
-    // operands whose last use is here release their slot before the result is placed
-    for (int s = 0; s < P.ar; ++s) {
-      const int v = P.src[s];
-      if (slot_of[v] >= 0 && last_use[v] == p) busy[slot_of[v]] = false;
-    }
-    const int v = P.ssa;
-    if (far_use[v]) {
-      int d = take();
-      if (d < 0) return fail(VRHI_ERR_UNSUPPORTED, "map_tape: more than %d values live at once", max_slots);
-      slot_of[v] = d;
-      D.dst = (uint8_t)d;
-      D.keep = 1;
-    }
-    T->instr[p] = D;
+    D.op = I.op;
+    D.cls = ar == 3 ? CLS_FMA : ar == 2 ? CLS_BINARY
+            : (I.op == VRHI_T_NEG || I.op == VRHI_T_ABS || I.op == VRHI_T_SQUARE || I.op == VRHI_T_RELU || I.op == VRHI_T_SIGN || I.op == VRHI_T_STEP) ? CLS_UNARY
+                                                                                                                                                     : CLS_TRANS;
+    D.a = (uint32_t)slot_of[src[0]];
+    D.b = ar >= 2 ? (uint32_t)slot_of[src[1]] : D.a;
+    D.c = ar >= 3 ? (uint32_t)slot_of[src[2]] : D.a;
+    // operands whose last use is here release their slot before the result is placed (a result
+    // may overwrite its own operand: each thread reads its elements before it writes them)
+    for (int s = 0; s < ar; ++s)
+      if (!is_const[src[s]] && !is_output[src[s]] && last_use[src[s]] == t && slot_of[src[s]] >= 0) busy[slot_of[src[s]]] = false;
+    int d = take();
+    if (d < 0) return fail(VRHI_ERR_UNSUPPORTED, too_many, max_slots);
+    slot_of[v] = d;
+    D.dst = (uint32_t)d;
+    if (last_use[v] < 0 && !is_output[v]) busy[d] = false;  // dead value
+    T->instr[NP++] = D;
   }
-  for (uint32_t k = 0; k < q.n_outputs; ++k) {
-    const int v = (int)q.out_value[k];
-    if (slot_of[v] < 0) return fail(VRHI_ERR_INVALID, "map_tape: output %u has no storage", k);
-    T->out_slot[k] = (uint8_t)slot_of[v];
-  }
+  for (uint32_t k = 0; k < q.n_outputs; ++k) T->out_slot[k] = (uint8_t)slot_of[q.out_value[k]];
   T->n_instr = (uint32_t)NP;
   T->n_slots = (uint32_t)n_slots;
   return VRHI_OK;

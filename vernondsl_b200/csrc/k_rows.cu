@@ -366,23 +366,24 @@ __global__ void __launch_bounds__(256) col_partial_kernel(const float *__restric
 
 __global__ void __launch_bounds__(256) col_finalize_kernel(const float *__restrict__ partial, float *__restrict__ out,
                                                            uint32_t groups, uint64_t cols, float scale) {
-  const uint64_t c = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
-  // eight interleaved partial sums keep eight loads in flight; they are combined in a fixed tree,
-  // so the result depends on `groups` only, never on scheduling
-  float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  uint32_t g = 0;
-  for (; g + 8 <= groups; g += 8) {
-#pragma unroll
-    for (int k = 0; k < 8; ++k) s[k] += partial[(uint64_t)(g + k) * cols + c];
-  }
-  for (int k = 0; g < groups; ++g, ++k) s[k] += partial[(uint64_t)g * cols + c];
-  out[c] = (((s[0] + s[1]) + (s[2] + s[3])) + ((s[4] + s[5]) + (s[6] + s[7]))) * scale;
+  // A block owns 32 adjacent columns; its eight warps each add every eighth partial row (so the
+  // loads of one warp are coalesced and independent), and the eight slice sums are combined in a
+  // fixed tree.  The result depends on `groups` only, never on scheduling.
+  __shared__ float sm[8][33];
+  const uint32_t lane = threadIdx.x & 31u, slice = threadIdx.x >> 5;
+  const uint64_t c = (uint64_t)blockIdx.x * 32 + lane;
+  float s = 0.f;
+  if (c < cols)
+    for (uint32_t g = slice; g < groups; g += 8) s += partial[(uint64_t)g * cols + c];
+  sm[slice][lane] = s;
+  __syncthreads();
+  if (slice == 0 && c < cols)
+    out[c] = (((sm[0][lane] + sm[1][lane]) + (sm[2][lane] + sm[3][lane])) + ((sm[4][lane] + sm[5][lane]) + (sm[6][lane] + sm[7][lane]))) * scale;
 }
 
 // Shared with the backward kernel: sums `groups` partial rows of `cols` floats into out.
 int col_finalize(vrhi_stream_t *st, const float *partial, float *out, uint32_t groups, uint64_t cols, float scale) {
-  col_finalize_kernel<<<(unsigned)((cols + 63) / 64), 64, 0, st->s>>>(partial, out, groups, cols, scale);
+  col_finalize_kernel<<<(unsigned)((cols + 31) / 32), 256, 0, st->s>>>(partial, out, groups, cols, scale);
   return post_launch(st, "col_finalize");
 }
 
@@ -492,7 +493,7 @@ extern "C" int vrhi_col_sum_static_scratch(const float *in_device, float *out_de
   col_partial_kernel<<<grid, 256, 0, s>>>(in_device, partials, rows, cols);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(VRHI_ERR_CUDA, "launch of col_sum_static_scratch (partials) failed: %s", cudaGetErrorString(e));
-  col_finalize_kernel<<<(unsigned)((cols + 63) / 64), 64, 0, s>>>(partials, out_device, (uint32_t)gy, cols, 1.0f);
+  col_finalize_kernel<<<(unsigned)((cols + 31) / 32), 256, 0, s>>>(partials, out_device, (uint32_t)gy, cols, 1.0f);
   e = cudaGetLastError();
   if (e != cudaSuccess) return fail(VRHI_ERR_CUDA, "launch of col_sum_static_scratch (finalize) failed: %s", cudaGetErrorString(e));
   return VRHI_OK;

@@ -108,6 +108,8 @@ def run_reference(args):
 
     J = JULIA
     dx, dy = oracle.grid_steps(J["x0"], J["x1"], J["y0"], J["y1"], J["W"], J["H"])
+    # torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU arm is meant to use the whole host
+    oracle.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
     cores = oracle.num_threads()
 
     def sample(stride):
@@ -575,6 +577,7 @@ def main():
         if world == 1 and not args.no_cpu_baseline:
             import oracle
 
+            oracle.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
             t0 = time.perf_counter()
             _, tot = oracle.escape_time(oracle.JULIA, W, H, J["x0"], J["y0"], dx, dy, J["cr"], J["ci"], J["max_iter"], want_image=False)
             secs = time.perf_counter() - t0

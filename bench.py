@@ -567,7 +567,9 @@ def main():
             "verified_bit_exact": verified,
             "compute_only": {"value": compute_value, "ms_per_step": compute_ms},
             "roofline": {"bound": "fp32", "achieved": achieved, "peak": fp32_peak, "unit": "Gop/s", "frac": achieved / fp32_peak,
-                         "traffic": 4 * 209.86e6,  # DRAM bytes per launch: ncu capture of the 8192^2 image x 4 (profiles/escape_regroup_julia_8192.md) "peak_kind": "FFMA-chain probe in this run (lane-instructions/s)",
+                         # DRAM bytes per image: ncu capture of the 8192^2 image x 4 (profiles/escape_regroup_julia_8192.md)
+                         "traffic": 4 * 209.86e6,
+                         "peak_kind": "FFMA-chain probe in this run (lane-instructions/s)",
                          "peak_nominal": fp32_nominal, "frac_of_nominal": achieved / fp32_nominal,
                          "algorithmic": f"{OPS_PER_ITER} f32 ops per pixel-iteration x {total_iters} iterations per image, per GPU"},
             "e2e": {"value": e2e_value, "unit": "Gpixel-iters/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": d2h,

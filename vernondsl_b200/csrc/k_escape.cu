@@ -122,7 +122,8 @@ __global__ void __launch_bounds__(256) escape_checked_kernel(EscapeDev p, void *
 }
 
 // ---------------------------------------------------------------------------------------------
-// Regrouping kernel (exact mode, test "a+b > bound" with bound >= 4, |c| <= 1.5).
+// Regrouping kernel (test "a+b > bound" with bound >= 4, |c| <= 1.5; MODE selects the exact or the
+// contracted rounding sequence, the machinery is the same).
 //
 // Iteration counts inside a warp differ by orders of magnitude near the set, so one pixel per lane
 // with a test on every step leaves most lanes idle (about 36 % lane efficiency on the 16384^2
@@ -142,7 +143,9 @@ __global__ void __launch_bounds__(256) escape_checked_kernel(EscapeDev p, void *
 //    INTAKE: 32 fresh pixels of a stolen tile run K checked steps in lock step (most pixels of the
 //    far exterior end there and are stored coalesced); survivors are pushed to the ring with their
 //    state.  Long-lived pixels therefore share warps with other long-lived pixels.
-//  * WORK STEALING.  Warps pull batches of 16 tiles (512 pixels of one row) from a global counter.
+//  * WORK STEALING.  Warps pull batches of up to 16 tiles (512 pixels of one row) from a global
+//    counter.  The host launches 4 CTAs per SM (2 for small images): the kernel is bound by
+//    instruction issue, so the 6 CTAs the launch bounds allow bring nothing more.
 //
 // Nothing here waits on another warp or CTA: no spin loops, no barriers.
 constexpr int kPoolCap = 64;

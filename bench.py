@@ -190,6 +190,33 @@ def other_workloads(dev, st, torch, hbm_peak, peak_kind, fp32_peak):
                              "frac": OPS_PER_ITER * rate / 1e9 / fp32_peak}})
     img.close()
 
+    # The reference program's own frame (fractal.py:7-25): 640 x 320 binary32 colour, |z| < 20, at most 50
+    # steps, a new uniform every frame (fractal.py:30-31).  Such a frame costs a few microseconds of
+    # arithmetic, so the launch is what is timed: plain launches against one recorded sequence.
+    n_half, frames = 320, 256
+    ring = [dev.empty((2 * n_half, n_half), np.float32, L.IMAGE) for _ in range(4)]  # field shape (2n, n): the real part follows the row index
+    d = float(np.float32(2.0 / n_half))
+    fparams = [ops.escape_params(L.JULIA, n_half, 2 * n_half, -1.0, -2.0, d, d, cr=-0.8, transposed=True,
+                                 ci=float(np.float32(np.cos(np.float32(k * 0.03))) * np.float32(0.2)), max_iter=50,
+                                 test=L.TEST_NORM_GE, bound=20.0, output=L.OUT_COLOR_F32, color_scale=0.02)
+               for k in range(frames)]
+
+    def run_frames():
+        for k, fp in enumerate(fparams):
+            ops.escape_time(st, ring[k % 4], fp)
+
+    ms_plain = time_launches(dev, st, run_frames, 5) / frames
+    with st.record() as seq:
+        run_frames()
+    ms_seq = time_launches(dev, st, lambda: seq.launch(), 5) / frames
+    out.append({"workload": f"fractal.py frame 640x320 f32 colour, max_iter=50, {frames} frames with a new uniform each, ring of 4 device frames",
+                "kernel": "escape_time", "ms_per_frame_plain_launches": ms_plain, "ms_per_frame_recorded_sequence": ms_seq,
+                "frames_per_s_recorded_sequence": 1e3 / ms_seq,
+                "note": "launch-bound: one CUDA graph submission for all frames against one launch call per frame"})
+    seq.close()
+    for b in ring:
+        b.close()
+
     # fused map chain, 2^28 elements
     n = 1 << 28
     gen.manual_seed(1003)
@@ -320,8 +347,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workloads", default="all", choices=["all", "main"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--gather", default="p2p", choices=["p2p", "nccl"],
-                    help="N > 1: exchange image chunks by peer copies (copy engines over NVLink) or by NCCL all-gather")
+    ap.add_argument("--gather", default="p2p16", choices=["p2p16", "p2p", "nccl"],
+                    help="N > 1: exchange image chunks by peer copies of uint16 counts widened on arrival (p2p16), by peer "
+                         "copies of the uint32 rows (p2p), or by NCCL all-gather")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
@@ -407,11 +435,15 @@ def main():
         comm_stream = torch.cuda.Stream(device=local)
         comm_st = dev.wrap_stream(comm_stream.cuda_stream)
         exchange = None
-        if args.gather == "p2p":
+        if args.gather in ("p2p", "p2p16"):
             try:
-                exchange = partition.PeerImageExchange(dev, image, plan, W * 4)
+                exchange = (partition.WireImageExchange(dev, image, plan, W) if args.gather == "p2p16"
+                            else partition.PeerImageExchange(dev, image, plan, W * 4))
             except Exception as exc:  # no peer mapping on this box: fall back to the NCCL gather
                 print(f"peer exchange unavailable ({exc}); using the NCCL all-gather", file=sys.stderr)
+
+    wire = exchange.wire if isinstance(exchange, partition.WireImageExchange) else None
+    SYNC_PER_GROUP = os.environ.get("VRHI_BENCH_SYNC", "group") == "group"
 
     def step():
         if world == 1:
@@ -419,18 +451,23 @@ def main():
             return
         works = []
         for gp, (k0, k1) in zip(group_params, group_slabs):
-            ops.escape_time(st, image, gp)
+            ops.escape_time(st, image, gp, wire=wire)
             ev = torch.cuda.Event()
             ev.record(tstream)
             comm_stream.wait_event(ev)
             if exchange is not None:
                 # one stream for all peers: pushes to several peers at once measured slower on this box
                 exchange.push(comm_st, (k0, k1))      # copy engines: overlaps the next group's kernel
+                if wire is not None and SYNC_PER_GROUP:
+                    exchange.finish(comm_stream, comm_st, (k0, k1))   # widen what has arrived while later groups compute
             else:
                 with torch.cuda.stream(comm_stream):
                     works += partition.all_gather_image(image_t, plan, async_op=True, slab_range=(k0, k1))
         if exchange is not None:
-            exchange.finish(comm_stream)
+            if wire is None:
+                exchange.finish(comm_stream)
+            elif not SYNC_PER_GROUP:
+                exchange.finish(comm_stream, comm_st)
             tstream.wait_stream(comm_stream)
         else:
             with torch.cuda.stream(tstream):
@@ -562,7 +599,7 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": WORKLOAD_NAME, "partition": f"cyclic 128-row chunks over {world} rank(s)",
-                       "collective": ("none" if world == 1 else "image chunks pushed into every peer's image by strided peer copies (copy engines over NVLink), overlapped with compute; one 4-byte NCCL all-reduce orders completion" if exchange is not None else "in-place NCCL all-gather of the image each step, overlapped with compute"),
+                       "collective": ("none" if world == 1 else "counts pushed as uint16 into every peer's wire image by strided peer copies (copy engines over NVLink) and widened into the uint32 image on arrival, overlapped with compute; 4-byte NCCL all-reduces order completion" if wire is not None else "image chunks pushed into every peer's image by strided peer copies (copy engines over NVLink), overlapped with compute; one 4-byte NCCL all-reduce orders completion" if exchange is not None else "in-place NCCL all-gather of the image each step, overlapped with compute"),
                        "l2": "no inputs; the 1 GiB output image written each step exceeds L2 (126 MB)"},
             "verified_bit_exact": verified,
             "compute_only": {"value": compute_value, "ms_per_step": compute_ms},

@@ -79,6 +79,7 @@ typedef struct vrhi_buffer_t *vrhi_buffer;
 typedef struct vrhi_stream_t *vrhi_stream;
 typedef struct vrhi_event_t *vrhi_event;
 typedef struct vrhi_graph_t *vrhi_graph;
+typedef struct vrhi_sequence_t *vrhi_sequence;
 
 /* ------------------------------------------------------------------- device ------------- */
 /* Stands in for fractal.py:5 (ti.init(arch=...)): choose and open the compute device. */
@@ -159,6 +160,28 @@ VRHI_API int vrhi_event_synchronize(vrhi_event event);
 VRHI_API int vrhi_event_elapsed_ms(vrhi_event start, vrhi_event stop, float *out_ms);
 VRHI_API int vrhi_stream_wait_event(vrhi_stream stream, vrhi_event event);
 
+/* ---- recorded launch sequences ------------------------------------------------------------
+ * The frame loop of fractal.py:30-33 relaunches one kernel with a new uniform per frame.  For
+ * small frames the cost of a frame is the launch, not the arithmetic, so a run of frames is
+ * recorded once and replayed as one CUDA graph launch.
+ *
+ * vrhi_sequence_begin puts the stream into recording: every vrhi_op_launch, vrhi_graph_launch,
+ * vrhi_buffer_fill and device-to-device copy issued on it until vrhi_sequence_end is recorded
+ * instead of executed.  Uniforms are part of what is recorded.  vrhi_sequence_end with
+ * *inout_seq == NULL builds a new sequence; with an existing sequence it re-targets that
+ * sequence in place (same launches, new uniforms or buffers: no rebuild) and rebuilds only when the
+ * shape of the recording changed.  Each operator must have run once on the stream before it is
+ * recorded (its scratch is sized then; nothing may be allocated while recording, and a
+ * launch that would need to allocate returns VRHI_ERR_INVALID).  Host transfers and
+ * synchronisation are not recordable.
+ * Reference counterpart: none; fractal.py leaves launching to its runtime. */
+VRHI_API int vrhi_sequence_begin(vrhi_stream stream);
+VRHI_API int vrhi_sequence_end(vrhi_stream stream, vrhi_sequence *inout_seq);
+VRHI_API int vrhi_sequence_launch(vrhi_sequence seq, vrhi_stream stream);
+/* kernels per replay, times the sequence was re-targeted in place, times it was rebuilt */
+VRHI_API int vrhi_sequence_stats(vrhi_sequence seq, uint64_t *out_kernels, uint64_t *out_retargets, uint64_t *out_rebuilds);
+VRHI_API int vrhi_sequence_destroy(vrhi_sequence seq); /* NULL is accepted */
+
 /* ------------------------------------------------------------------ operators ----------- */
 /* Stands in for fractal.py:16,31 (@ti.kernel definition and its launch): a registry of named
  * kernels, each launched with buffer arguments and a small POD parameter block ("uniforms").
@@ -217,6 +240,24 @@ typedef struct vrhi_escape_params {
  * column i) has real part y0 + j*dy and imaginary part x0 + i*dx.  This is the memory order of a
  * field indexed [i, j] whose first index feeds the real part (fractal.py:8,20). */
 #define VRHI_ESCAPE_FLAG_TRANSPOSED 2u
+
+/* op "escape_time", optional second argument: a uint16 image of the same [height][width]
+ * geometry that receives every count a second time (uint32 counts only, max_iter <= 65535).
+ * It is the form in which a rank sends its rows to its peers when the image is gathered over
+ * NVLink: half the bytes, nothing lost.
+ *
+ * op "widen_rows_u16" -- the receiving side: copies uint16 counts into the uint32 image for the
+ * rows of slabs slab_first .. slab_first+slab_count-1 (a slab = `world` consecutive chunks of
+ * chunk_rows rows), leaving out the chunks of `skip_rank` (the caller's own, already present in
+ * full width); skip_rank >= world widens every chunk.
+ * args: [0] wire (uint16 [height][width]), [1] image (uint32 [height][width], writable).
+ * Reference counterpart: none (the reference runs on one device). */
+typedef struct vrhi_widen_params {
+  uint32_t size;
+  uint32_t width, height;
+  uint32_t chunk_rows, world, skip_rank;
+  uint32_t slab_first, slab_count;
+} vrhi_widen_params;
 
 /* op "fused_map" -- the map chain  out = tanh(a*x + y) * exp(-0.5*x*x) + sqrt(|y| + 1e-3)
  * as one kernel.  args: [0] a, [1] x, [2] y (INPUT, n floats), [3] out (OUTPUT, n floats). */

@@ -1,0 +1,125 @@
+"""GPU: recorded launch sequences and the headless frame loop.
+
+The reference's program re-launches its kernel with a new uniform every frame and blits the field
+to a window (fractal.py:28-33).  Here a run of frames is recorded once and replayed with one
+submission into a ring of device frames; every frame must equal what a plain launch with that
+frame's uniform produces, and the CPU oracle's image, bit for bit."""
+import numpy as np
+import pytest
+
+import oracle
+import vernondsl_b200 as vd
+import vernondsl_b200.lang as ti
+from vernondsl_b200 import _lib as L
+from vernondsl_b200 import ops
+
+pytestmark = pytest.mark.gpu
+
+
+def _oracle_frame(half, phase):
+    ci = float(np.float32(np.cos(np.float32(phase))) * np.float32(0.2))
+    d = np.float32(2.0 / half)
+    counts, _ = oracle.escape_time(oracle.JULIA, 2 * half, half, -2.0, -1.0, d, d, -0.8, ci, 50,
+                                   test=oracle.TEST_NORM_GE, bound=20.0)
+    return oracle.escape_color(counts, 0.02).T
+
+
+def test_frame_loop_replays_a_run_of_frames_into_the_ring():
+    ti.init()
+    half = 160                      # the reference's own frame: 640 x 320 at n = 320; half of it here
+    canvas = ti.field(dtype=float, shape=(half * 2, half))
+
+    @ti.kernel
+    def draw(phase: float):
+        for a, b in canvas:
+            k = ti.Vector([-0.8, ti.cos(phase) * 0.2])
+            w = ti.Vector([a / half - 1, b / half - 0.5]) * 2
+            steps = 0
+            while w.norm() < 20 and steps < 50:
+                w = ti.Vector([w[0] ** 2 - w[1] ** 2, w[1] * w[0] * 2]) + k
+                steps += 1
+            canvas[a, b] = 1 - steps * 0.02
+
+    loop = ti.FrameLoop(draw, canvas, ring=4)
+    phases = [k * 0.03 for k in range(6)]
+    loop.record(phases)
+    st = loop.stream
+    before = st.launch_count()
+    loop.play()
+    assert st.launch_count() - before == 6          # six kernels, one submission
+    for k in (2, 3, 4, 5):                          # the ring holds the last four
+        assert np.array_equal(loop.frame(k), _oracle_frame(half, phases[k])), k
+    with pytest.raises(IndexError):
+        loop.frame(1)
+    # new uniforms: the recording is re-targeted in place, not rebuilt
+    phases2 = [1.0 + k * 0.05 for k in range(6)]
+    loop.record(phases2)
+    assert loop.seq.stats() == {"kernels": 6, "retargets": 1, "rebuilds": 0}
+    loop.play()
+    loop.play()                                     # a replay is repeatable
+    for k in (2, 5):
+        assert np.array_equal(loop.frame(k), _oracle_frame(half, phases2[k])), k
+    # a different number of frames changes the shape of the recording: rebuilt, still right
+    loop.record(phases[:3])
+    assert loop.seq.stats()["rebuilds"] == 1
+    loop.play()
+    assert np.array_equal(loop.frame(2), _oracle_frame(half, phases[2]))
+    # the field itself is untouched as the kernel's target
+    draw(0.5)
+    assert np.array_equal(canvas.to_numpy(), _oracle_frame(half, 0.5))
+    loop.close()
+
+
+def test_sequence_of_mixed_operators_matches_plain_launches():
+    dev = vd.Device(0)
+    st = dev.stream()
+    rng = np.random.default_rng(11)
+    R, Cc = 256, 1024
+    a = rng.uniform(-1, 1, R * Cc).astype(np.float32)
+    x = rng.standard_normal(R * Cc).astype(np.float32)
+    y = rng.standard_normal(R * Cc).astype(np.float32)
+    da, dx, dy = (dev.from_numpy(v, L.INPUT) for v in (a, x, y))
+    mid = dev.empty((R, Cc), np.float32, L.STORAGE_BUFFER)
+    sums = dev.empty((R,), np.float32, L.OUTPUT)
+    cols = dev.empty((Cc,), np.float32, L.OUTPUT)
+    soft = dev.empty((R, Cc), np.float32, L.OUTPUT)
+
+    def chain():
+        ops.fused_map(st, da, dx, dy, mid, R * Cc)
+        ops.row_sum(st, mid, sums, R, Cc)
+        ops.col_sum(st, mid, cols, R, Cc)
+        ops.row_softmax(st, mid, soft, R, Cc)
+
+    chain()                                         # plain launches (also sizes the stream scratch)
+    st.check()
+    want = [b.download(dtype=np.float32) for b in (mid, sums, cols, soft)]
+    for b in (mid, sums, cols, soft):
+        b.fill(0, stream=st)
+    with st.record() as seq:
+        chain()
+    st.check()
+    assert not np.any(sums.download(dtype=np.float32)), "recording must not execute"
+    assert seq.stats()["kernels"] >= 4
+    seq.launch()
+    st.check()
+    got = [b.download(dtype=np.float32) for b in (mid, sums, cols, soft)]
+    for g, w in zip(got, want):
+        assert np.array_equal(g, w)                 # same kernels, same order of operations: same bits
+    seq.close()
+    st.close()
+
+
+def test_recording_refuses_an_operator_whose_scratch_does_not_exist_yet():
+    dev = vd.Device(0)
+    st = dev.stream()                               # fresh stream: no scratch yet
+    img = dev.empty((64, 64), np.uint32, L.IMAGE)
+    p = ops.escape_params(L.MANDELBROT, 64, 64, -2.5, -1.0, 3.5 / 64, 2.0 / 64, max_iter=128)
+    with pytest.raises(vd.VrhiError) as err:
+        with st.record():
+            ops.escape_time(st, img, p)
+    assert err.value.status == L.ERR_INVALID and "before recording" in str(err.value)
+    ops.escape_time(st, img, p)                     # the stream is usable afterwards
+    st.check()
+    want, _ = oracle.escape_time(oracle.MANDELBROT, 64, 64, -2.5, -1.0, np.float32(3.5 / 64), np.float32(2.0 / 64), max_iter=128)
+    assert np.array_equal(img.download(dtype=np.uint32, shape=(64, 64)), want)
+    st.close()

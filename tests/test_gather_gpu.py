@@ -1,0 +1,95 @@
+"""GPU: the uint16 wire copy of the escape-time counts and the widening kernel of the image gather.
+
+The two ranks of a world are played one after the other on one GPU (each computes its own chunks into
+its own image and wire image), the peer push is a strided device copy between the wire images, and
+the widened result must equal the CPU oracle's whole image bit for bit."""
+import numpy as np
+import pytest
+
+import oracle
+import vernondsl_b200 as vd
+from vernondsl_b200 import _lib as L
+from vernondsl_b200 import ops
+
+pytestmark = pytest.mark.gpu
+
+J = dict(x0=-1.6, y0=-1.6, cr=-0.8, ci=0.156)
+
+
+def _julia(W, H, max_iter):
+    dx, dy = ops.grid_steps(-1.6, 1.6, -1.6, 1.6, W, H)
+    want, _ = oracle.escape_time(oracle.JULIA, W, H, J["x0"], J["y0"], dx, dy, J["cr"], J["ci"], max_iter)
+    return dx, dy, want
+
+
+@pytest.mark.parametrize("max_iter,checked", [(300, False), (300, True), (40, False)])
+def test_wire_copy_equals_the_counts(max_iter, checked):
+    dev = vd.Device(0)
+    st = dev.stream()
+    W, H = 520, 96                      # width not a multiple of 32: ragged last tile
+    dx, dy, want = _julia(W, H, max_iter)
+    img = dev.empty((H, W), np.uint32, L.IMAGE)
+    wire = dev.empty((H, W), np.uint16, L.IMAGE)
+    p = ops.escape_params(L.JULIA, W, H, J["x0"], J["y0"], dx, dy, cr=J["cr"], ci=J["ci"], max_iter=max_iter, checked_only=checked)
+    ops.escape_time(st, img, p, wire=wire)
+    st.check()
+    assert np.array_equal(img.download(dtype=np.uint32, shape=(H, W)), want)
+    assert np.array_equal(wire.download(dtype=np.uint16, shape=(H, W)), want.astype(np.uint16))
+    st.close()
+
+
+def test_wire_copy_is_refused_where_it_would_lose_counts():
+    dev = vd.Device(0)
+    st = dev.stream()
+    img = dev.empty((32, 64), np.uint32, L.IMAGE)
+    wire = dev.empty((32, 64), np.uint16, L.IMAGE)
+    p = ops.escape_params(L.MANDELBROT, 64, 32, -2.5, -1.0, 3.5 / 64, 2.0 / 32, max_iter=70000)
+    with pytest.raises(vd.VrhiError) as err:
+        ops.escape_time(st, img, p, wire=wire)
+    assert err.value.status == L.ERR_UNSUPPORTED
+    small = dev.empty((16, 64), np.uint16, L.IMAGE)
+    p.max_iter = 100
+    with pytest.raises(vd.VrhiError) as err:
+        ops.escape_time(st, img, p, wire=small)
+    assert err.value.status == L.ERR_SIZE
+    st.close()
+
+
+@pytest.mark.parametrize("W,world", [(512, 2), (512, 4), (100, 2)])   # 100: the scalar path of the widening kernel
+def test_gather_with_uint16_on_the_wire_rebuilds_the_whole_image(W, world):
+    dev = vd.Device(0)
+    st = dev.stream()
+    chunk_rows, slabs = 8, 3
+    H = chunk_rows * world * slabs
+    max_iter = 400
+    dx, dy, want = _julia(W, H, max_iter)
+    images = [dev.empty((H, W), np.uint32, L.IMAGE) for _ in range(world)]
+    wires = [dev.empty((H, W), np.uint16, L.IMAGE) for _ in range(world)]
+    for r in range(world):
+        images[r].fill(0xEE, stream=st)           # rows of other ranks start as garbage
+        wires[r].fill(0xDD, stream=st)
+        part = ops.partition_rows(H, world, r, L.PART_CYCLIC, chunk_rows)
+        p = ops.escape_params(L.JULIA, W, H, J["x0"], J["y0"], dx, dy, cr=J["cr"], ci=J["ci"], max_iter=max_iter, partition=part)
+        ops.escape_time(st, images[r], p, wire=wires[r])
+    # the push: rank r's chunks (every world-th chunk starting at r) into every peer's wire image
+    chunk_bytes = chunk_rows * W * 2
+    for r in range(world):
+        for q in range(world):
+            if q != r:
+                wires[r].copy_2d_to(wires[q], r * chunk_bytes, world * chunk_bytes, r * chunk_bytes, world * chunk_bytes, chunk_bytes, slabs, st)
+    # arrival, in two slab ranges as a pipelined step would do it
+    for r in range(world):
+        ops.widen_rows_u16(st, wires[r], images[r], W, H, chunk_rows, world, r, 0, 1)
+        ops.widen_rows_u16(st, wires[r], images[r], W, H, chunk_rows, world, r, 1, slabs - 1)
+    st.check()
+    for r in range(world):
+        assert np.array_equal(images[r].download(dtype=np.uint32, shape=(H, W)), want), r
+    # widening every chunk (no rank skipped) from a complete wire image gives the same picture
+    blank = dev.empty((H, W), np.uint32, L.IMAGE)
+    blank.fill(0, stream=st)
+    ops.widen_rows_u16(st, wires[0], blank, W, H, chunk_rows, world, world, 0, slabs)
+    st.check()
+    assert np.array_equal(blank.download(dtype=np.uint32, shape=(H, W)), want)
+    with pytest.raises(vd.VrhiError):
+        ops.widen_rows_u16(st, wires[0], blank, W, H, chunk_rows, world, 0, slabs, 1)   # beyond the last slab
+    st.close()

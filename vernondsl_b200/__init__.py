@@ -9,7 +9,7 @@ Nothing in the package computes on the CPU; without the built library it raises.
 from . import _lib
 from ._lib import (EXACT, FAST, IMAGE, INPUT, JULIA, MANDELBROT, OUTPUT, STORAGE_BUFFER, UNIFORM, UNIFORM_CONSTANT,
                    VARYING, VrhiError, build)
-from .rhi import Buffer, Device, Event, PinnedArray, Stream
+from .rhi import Buffer, Device, Event, PinnedArray, Sequence, Stream
 
-__all__ = ["Buffer", "Device", "Event", "PinnedArray", "Stream", "VrhiError", "build", "_lib", "INPUT", "OUTPUT",
+__all__ = ["Buffer", "Device", "Event", "PinnedArray", "Sequence", "Stream", "VrhiError", "build", "_lib", "INPUT", "OUTPUT",
            "UNIFORM", "UNIFORM_CONSTANT", "STORAGE_BUFFER", "IMAGE", "VARYING", "MANDELBROT", "JULIA", "EXACT", "FAST"]

@@ -68,6 +68,11 @@ class EscapeParams(C.Structure):
                 ("chunk_step", C.c_uint32), ("chunk_count", C.c_uint32), ("flags", C.c_uint32)]
 
 
+class WidenParams(C.Structure):
+    _fields_ = [("size", C.c_uint32), ("width", C.c_uint32), ("height", C.c_uint32), ("chunk_rows", C.c_uint32),
+                ("world", C.c_uint32), ("skip_rank", C.c_uint32), ("slab_first", C.c_uint32), ("slab_count", C.c_uint32)]
+
+
 class MapParams(C.Structure):
     _fields_ = [("size", C.c_uint32), ("reserved", C.c_uint32), ("n", C.c_uint64)]
 
@@ -146,6 +151,11 @@ PROTOTYPES = {
     "vrhi_event_synchronize": [_vp],
     "vrhi_event_elapsed_ms": [_vp, _vp, _P(C.c_float)],
     "vrhi_stream_wait_event": [_vp, _vp],
+    "vrhi_sequence_begin": [_vp],
+    "vrhi_sequence_end": [_vp, _P(_vp)],
+    "vrhi_sequence_launch": [_vp, _vp],
+    "vrhi_sequence_stats": [_vp, _P(C.c_uint64), _P(C.c_uint64), _P(C.c_uint64)],
+    "vrhi_sequence_destroy": [_vp],
     "vrhi_op_count": [_P(_i)],
     "vrhi_op_name": [_i, _P(C.c_char_p)],
     "vrhi_op_lookup": [C.c_char_p, _P(_i)],

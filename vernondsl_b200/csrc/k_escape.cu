@@ -78,6 +78,10 @@ __device__ __forceinline__ void store_count(void *image, size_t pix, uint32_t co
     static_cast<float *>(image)[pix] = __fsub_rn(1.0f, __fmul_rn((float)count, color_scale));
 }
 
+// Second copy of a count as uint16 at the same pixel index (the compact form a rank sends to its
+// peers when the image is gathered; counts up to 65535 lose nothing).
+__device__ __forceinline__ void store_wire(uint16_t *wire, size_t pix, uint32_t count) { wire[pix] = (uint16_t)count; }
+
 // Row of the image that owned row r maps to (rows are owned in chunks dealt round-robin).
 __device__ __forceinline__ uint32_t owned_row_to_image_row(const EscapeDev &p, uint32_t r) {
   uint32_t k = r / p.chunk_rows;
@@ -85,12 +89,19 @@ __device__ __forceinline__ uint32_t owned_row_to_image_row(const EscapeDev &p, u
 }
 
 template <int KIND, int MODE, int TEST, int OUT>
-__global__ void __launch_bounds__(256) escape_checked_kernel(EscapeDev p, void *image, uint32_t *work_counter) {
+__global__ void __launch_bounds__(256) escape_checked_kernel(EscapeDev p, void *image, uint32_t *work_counter, uint16_t *wire) {
   const uint32_t lane = threadIdx.x & 31u;
+  // work_counter == nullptr: batches are dealt to warps round-robin (small frames, where the
+  // counter's reset would cost as much as the frame); otherwise warps pull batches from the counter
+  uint32_t next = blockIdx.x * 8u + (threadIdx.x >> 5);
   for (;;) {
-    uint32_t batch = 0;
-    if (lane == 0) batch = atomicAdd(work_counter, 1u);
-    batch = __shfl_sync(0xffffffffu, batch, 0);
+    uint32_t batch = next;
+    if (work_counter) {
+      if (lane == 0) batch = atomicAdd(work_counter, 1u);
+      batch = __shfl_sync(0xffffffffu, batch, 0);
+    } else {
+      next += gridDim.x * 8u;
+    }
     if (batch >= p.n_batches) break;
     const uint32_t r = batch / p.batches_per_row;
     const uint32_t tile0 = (batch - r * p.batches_per_row) * p.batch_tiles;
@@ -117,6 +128,7 @@ __global__ void __launch_bounds__(256) escape_checked_kernel(EscapeDev p, void *
         ++count;
       }
       store_count<OUT>(image, row_base + i, count, p.color_scale);
+      if (wire) store_wire(wire, row_base + i, count);
     }
   }
 }
@@ -151,8 +163,8 @@ __global__ void __launch_bounds__(256) escape_checked_kernel(EscapeDev p, void *
 constexpr int kPoolCap = 64;
 
 // U = steps per block, T = waiting lanes that trigger a checked block, K = checked steps a fresh pixel gets before it is pooled
-template <int KIND, int OUT, int U, int T, int K = 8, int MODE = VRHI_ESCAPE_EXACT>
-__global__ void __launch_bounds__(256, 6) escape_regroup_kernel(EscapeDev p, void *image, uint32_t *work_counter) {
+template <int KIND, int OUT, int U, int T, int K = 8, int MODE = VRHI_ESCAPE_EXACT, bool WIRE = false>
+__global__ void __launch_bounds__(256, 6) escape_regroup_kernel(EscapeDev p, void *image, uint32_t *work_counter, uint16_t *wire = nullptr) {
   constexpr bool PER_PIXEL_C = (KIND == VRHI_ESCAPE_MANDELBROT);
   __shared__ float s_zr[8][kPoolCap], s_zi[8][kPoolCap];
   __shared__ uint32_t s_idx[8][kPoolCap], s_cnt[8][kPoolCap];
@@ -228,7 +240,10 @@ __global__ void __launch_bounds__(256, 6) escape_regroup_kernel(EscapeDev p, voi
         }
       }
     }
-    if (valid && !flive) store_count<OUT>(image, (size_t)(row_base + i), fcnt, color_scale);
+    if (valid && !flive) {
+      store_count<OUT>(image, (size_t)(row_base + i), fcnt, color_scale);
+      if (WIRE) store_wire(wire, (size_t)(row_base + i), fcnt);
+    }
     const uint32_t m = __ballot_sync(FULL, flive);
     if (m) {
       if (flive) {
@@ -262,7 +277,10 @@ __global__ void __launch_bounds__(256, 6) escape_regroup_kernel(EscapeDev p, voi
     // for lanes that pass)
     live = live && (z_norm2<MODE>(zr, zi, a, b) <= bound);
     if (CAP) live = live && (cnt < max_iter);
-    if (occ && !live) store_count<OUT>(image, (size_t)idx, cnt, color_scale);
+    if (occ && !live) {
+      store_count<OUT>(image, (size_t)idx, cnt, color_scale);
+      if (WIRE) store_wire(wire, (size_t)idx, cnt);
+    }
     occ = live;
     run = live;  // a finishing lane always ends inside the block
   };
@@ -310,27 +328,35 @@ __global__ void __launch_bounds__(256, 6) escape_regroup_kernel(EscapeDev p, voi
 }
 
 template <int KIND, int MODE, int TEST>
-static void launch_checked_out(int out, int grid, cudaStream_t s, const EscapeDev &p, void *image, uint32_t *ctr) {
+static void launch_checked_out(int out, int grid, cudaStream_t s, const EscapeDev &p, void *image, uint32_t *ctr, uint16_t *wire) {
   switch (out) {
-    case VRHI_OUT_COUNT_U32: escape_checked_kernel<KIND, MODE, TEST, VRHI_OUT_COUNT_U32><<<grid, 256, 0, s>>>(p, image, ctr); break;
-    case VRHI_OUT_COUNT_U16: escape_checked_kernel<KIND, MODE, TEST, VRHI_OUT_COUNT_U16><<<grid, 256, 0, s>>>(p, image, ctr); break;
-    default: escape_checked_kernel<KIND, MODE, TEST, VRHI_OUT_COLOR_F32><<<grid, 256, 0, s>>>(p, image, ctr); break;
+    case VRHI_OUT_COUNT_U32: escape_checked_kernel<KIND, MODE, TEST, VRHI_OUT_COUNT_U32><<<grid, 256, 0, s>>>(p, image, ctr, wire); break;
+    case VRHI_OUT_COUNT_U16: escape_checked_kernel<KIND, MODE, TEST, VRHI_OUT_COUNT_U16><<<grid, 256, 0, s>>>(p, image, ctr, nullptr); break;
+    default: escape_checked_kernel<KIND, MODE, TEST, VRHI_OUT_COLOR_F32><<<grid, 256, 0, s>>>(p, image, ctr, nullptr); break;
   }
 }
 
 template <int KIND, int MODE>
-static void launch_checked_test(int test, int out, int grid, cudaStream_t s, const EscapeDev &p, void *image, uint32_t *ctr) {
+static void launch_checked_test(int test, int out, int grid, cudaStream_t s, const EscapeDev &p, void *image, uint32_t *ctr, uint16_t *wire) {
   if (test == VRHI_TEST_NORM2_GT)
-    launch_checked_out<KIND, MODE, VRHI_TEST_NORM2_GT>(out, grid, s, p, image, ctr);
+    launch_checked_out<KIND, MODE, VRHI_TEST_NORM2_GT>(out, grid, s, p, image, ctr, wire);
   else
-    launch_checked_out<KIND, MODE, VRHI_TEST_NORM_GE>(out, grid, s, p, image, ctr);
+    launch_checked_out<KIND, MODE, VRHI_TEST_NORM_GE>(out, grid, s, p, image, ctr, wire);
 }
 
 int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const void *params, size_t params_size) {
   vrhi_escape_params q;
   VRHI_TRY(read_params(params, params_size, &q));
-  if (n_args != 1) return fail(VRHI_ERR_INVALID, "escape_time takes 1 argument (the image), got %d", n_args);
+  if (n_args != 1 && n_args != 2) return fail(VRHI_ERR_INVALID, "escape_time takes the image and, optionally, a uint16 wire copy; got %d arguments", n_args);
   if (!writable(args[0])) return fail(VRHI_ERR_INVALID, "escape_time: the image buffer is read-only (class %s)", vrhi_arg_class_name(args[0].buf_cls));
+  uint16_t *wire = nullptr;
+  if (n_args == 2) {
+    if (q.output != VRHI_OUT_COUNT_U32) return fail(VRHI_ERR_INVALID, "escape_time: the uint16 wire copy goes with uint32 counts only");
+    if (q.max_iter > 65535u) return fail(VRHI_ERR_UNSUPPORTED, "escape_time: a uint16 wire copy needs max_iter <= 65535");
+    if (!writable(args[1])) return fail(VRHI_ERR_INVALID, "escape_time: the wire buffer is read-only (class %s)", vrhi_arg_class_name(args[1].buf_cls));
+    if (args[1].bytes < (uint64_t)q.width * q.height * 2) return fail(VRHI_ERR_SIZE, "escape_time: the wire view holds %llu bytes, %llu needed", (unsigned long long)args[1].bytes, (unsigned long long)q.width * q.height * 2);
+    wire = reinterpret_cast<uint16_t *>(args[1].ptr);
+  }
   if (q.kind > VRHI_ESCAPE_JULIA || q.mode > VRHI_ESCAPE_FAST || q.test > VRHI_TEST_NORM_GE || q.output > VRHI_OUT_COLOR_F32)
     return fail(VRHI_ERR_INVALID, "escape_time: kind/mode/test/output out of range");
   if (q.width == 0 || q.height == 0) return fail(VRHI_ERR_SIZE, "escape_time: empty image");
@@ -379,10 +405,6 @@ int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const
   if (nb > 0xfffffff0ull) return fail(VRHI_ERR_UNSUPPORTED, "escape_time: image too large for 32-bit batch indices");
   p.n_batches = (uint32_t)nb;
 
-  uint32_t *ctrl = nullptr;
-  VRHI_TRY(stream_arena(st, 0, &ctrl, nullptr));
-  uint32_t *counter = ctrl + CTRL_WORK0;
-  VRHI_CUDA(cudaMemsetAsync(counter, 0, sizeof(uint32_t), st->s));
   const int sms = st->dev->prop.multiProcessorCount;
   uint64_t warps_needed = nb;
   int grid = (int)((warps_needed + 7) / 8 < (uint64_t)sms * 8 ? (warps_needed + 7) / 8 : (uint64_t)sms * 8);
@@ -392,6 +414,16 @@ int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const
   const bool regroup_ok = q.test == VRHI_TEST_NORM2_GT && q.bound >= 4.0f && q.bound < 3.0e38f &&
                           q.max_iter >= 64u && q.max_iter <= (1u << 30) && (uint64_t)q.width * q.height <= 0xffffffffull &&
                           (q.kind == VRHI_ESCAPE_MANDELBROT || c2 <= 2.25) && !(q.flags & VRHI_ESCAPE_FLAG_CHECKED_ONLY);
+  // A frame of a few batches per warp (the 640 x 320 frame of fractal.py:7-8 is one) is dealt out
+  // statically: resetting a work counter would be a second node per frame and cost as much as the frame.
+  const bool dealt = !regroup_ok && nb <= (uint64_t)grid * 8 * 4;
+  uint32_t *counter = nullptr;
+  if (!dealt) {
+    uint32_t *ctrl = nullptr;
+    VRHI_TRY(stream_arena(st, 0, &ctrl, nullptr));
+    counter = ctrl + CTRL_WORK0;
+    VRHI_CUDA(cudaMemsetAsync(counter, 0, sizeof(uint32_t), st->s));
+  }
   if (regroup_ok) {
     // Measured on B200: 3-4 CTAs of 256 threads per SM are as fast as the 6 that fit (the kernel is
     // issue-bound, not latency-bound); small images run faster still with 2, because each warp then
@@ -406,7 +438,7 @@ int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const
     if (const char *tune = getenv("VRHI_ESCAPE_TUNE")) {
       int tu = 0, tt = 0, tc = 0, tk = 8;
       int got = sscanf(tune, "%d,%d,%d,%d", &tu, &tt, &tc, &tk);
-      if (got >= 2 && q.output == VRHI_OUT_COUNT_U32 && q.mode == VRHI_ESCAPE_EXACT) {
+      if (got >= 2 && q.output == VRHI_OUT_COUNT_U32 && q.mode == VRHI_ESCAPE_EXACT && !wire) {
         if (got >= 3 && tc > 0) { cap = (uint64_t)sms * tc; grid = (int)(ctas < cap ? ctas : cap); }
         bool hit = true;
 #define TUNEK(UU, TT, KK)                                                                                              \
@@ -429,7 +461,15 @@ int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const
     if (q.mode == VRHI_ESCAPE_EXACT) escape_regroup_kernel<KIND, OUT, 12, 8, 8, VRHI_ESCAPE_EXACT><<<grid, 256, 0, st->s>>>(p, args[0].ptr, counter); \
     else escape_regroup_kernel<KIND, OUT, 12, 8, 8, VRHI_ESCAPE_FAST><<<grid, 256, 0, st->s>>>(p, args[0].ptr, counter);   \
   } while (0)
-    if (q.kind == VRHI_ESCAPE_MANDELBROT) {
+#define REGROUP_WIRE(KIND)                                                                                              \
+  do {                                                                                                                 \
+    if (q.mode == VRHI_ESCAPE_EXACT) escape_regroup_kernel<KIND, VRHI_OUT_COUNT_U32, 12, 8, 8, VRHI_ESCAPE_EXACT, true><<<grid, 256, 0, st->s>>>(p, args[0].ptr, counter, wire); \
+    else escape_regroup_kernel<KIND, VRHI_OUT_COUNT_U32, 12, 8, 8, VRHI_ESCAPE_FAST, true><<<grid, 256, 0, st->s>>>(p, args[0].ptr, counter, wire);   \
+  } while (0)
+    if (wire) {
+      if (q.kind == VRHI_ESCAPE_MANDELBROT) REGROUP_WIRE(VRHI_ESCAPE_MANDELBROT);
+      else REGROUP_WIRE(VRHI_ESCAPE_JULIA);
+    } else if (q.kind == VRHI_ESCAPE_MANDELBROT) {
       if (q.output == VRHI_OUT_COUNT_U32) REGROUP(VRHI_ESCAPE_MANDELBROT, VRHI_OUT_COUNT_U32);
       else if (q.output == VRHI_OUT_COUNT_U16) REGROUP(VRHI_ESCAPE_MANDELBROT, VRHI_OUT_COUNT_U16);
       else REGROUP(VRHI_ESCAPE_MANDELBROT, VRHI_OUT_COLOR_F32);
@@ -439,14 +479,15 @@ int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const
       else REGROUP(VRHI_ESCAPE_JULIA, VRHI_OUT_COLOR_F32);
     }
 #undef REGROUP
+#undef REGROUP_WIRE
     return post_launch(st, "escape_time (regrouping)");
   }
   if (q.kind == VRHI_ESCAPE_MANDELBROT) {
-    if (q.mode == VRHI_ESCAPE_EXACT) launch_checked_test<VRHI_ESCAPE_MANDELBROT, VRHI_ESCAPE_EXACT>(q.test, q.output, grid, st->s, p, args[0].ptr, counter);
-    else launch_checked_test<VRHI_ESCAPE_MANDELBROT, VRHI_ESCAPE_FAST>(q.test, q.output, grid, st->s, p, args[0].ptr, counter);
+    if (q.mode == VRHI_ESCAPE_EXACT) launch_checked_test<VRHI_ESCAPE_MANDELBROT, VRHI_ESCAPE_EXACT>(q.test, q.output, grid, st->s, p, args[0].ptr, counter, wire);
+    else launch_checked_test<VRHI_ESCAPE_MANDELBROT, VRHI_ESCAPE_FAST>(q.test, q.output, grid, st->s, p, args[0].ptr, counter, wire);
   } else {
-    if (q.mode == VRHI_ESCAPE_EXACT) launch_checked_test<VRHI_ESCAPE_JULIA, VRHI_ESCAPE_EXACT>(q.test, q.output, grid, st->s, p, args[0].ptr, counter);
-    else launch_checked_test<VRHI_ESCAPE_JULIA, VRHI_ESCAPE_FAST>(q.test, q.output, grid, st->s, p, args[0].ptr, counter);
+    if (q.mode == VRHI_ESCAPE_EXACT) launch_checked_test<VRHI_ESCAPE_JULIA, VRHI_ESCAPE_EXACT>(q.test, q.output, grid, st->s, p, args[0].ptr, counter, wire);
+    else launch_checked_test<VRHI_ESCAPE_JULIA, VRHI_ESCAPE_FAST>(q.test, q.output, grid, st->s, p, args[0].ptr, counter, wire);
   }
   return post_launch(st, "escape_time");
 }

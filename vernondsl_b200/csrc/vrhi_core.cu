@@ -30,6 +30,10 @@ static int set_device(vrhi_device_t *dev) {
 int stream_arena(vrhi_stream_t *st, size_t payload, uint32_t **ctrl, char **payload_ptr) {
   if (!st->arena || st->arena_payload < payload) {
     VRHI_TRY(set_device(st->dev));
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    VRHI_CUDA(cudaStreamIsCapturing(st->s, &cap));
+    if (cap != cudaStreamCaptureStatusNone)
+      return fail(VRHI_ERR_INVALID, "this launch needs %zu bytes of stream scratch that do not exist yet; run the operator once on the stream before recording it", payload);
     size_t want = payload < (size_t(4) << 20) ? (size_t(4) << 20) : payload;
     if (st->arena) {
       VRHI_CUDA(cudaStreamSynchronize(st->s));
@@ -49,7 +53,7 @@ int stream_arena(vrhi_stream_t *st, size_t payload, uint32_t **ctrl, char **payl
 }
 
 static const OpDef kOps[] = {
-    {"escape_time", "args: image(OUTPUT|IMAGE u32/u16/f32 [height][width]); params: vrhi_escape_params",
+    {"escape_time", "args: image(OUTPUT|IMAGE u32/u16/f32 [height][width])[, wire(OUTPUT|IMAGE u16 [height][width])]; params: vrhi_escape_params",
      launch_escape_time},
     {"fused_map", "args: a,x,y(INPUT f32[n]), out(OUTPUT f32[n]); params: vrhi_map_params", launch_fused_map},
     {"map_tape", "args: inputs..., outputs...; params: vrhi_tape_params", launch_map_tape},
@@ -71,6 +75,8 @@ static const OpDef kOps[] = {
      "varying(VARYING f32[n][3]); params: vrhi_map_params",
      launch_vertex_transform},
     {"flat_color", "args: color(UNIFORM f32[3]), fragments(IMAGE f32[n][4]); params: vrhi_map_params", launch_flat_color},
+    {"widen_rows_u16", "args: wire(u16 [height][width]), image(OUTPUT|IMAGE u32 [height][width]); params: vrhi_widen_params",
+     launch_widen_rows_u16},
 };
 static const int kNumOps = int(sizeof(kOps) / sizeof(kOps[0]));
 
@@ -505,6 +511,91 @@ int vrhi_event_synchronize(vrhi_event event) {
 int vrhi_event_elapsed_ms(vrhi_event start, vrhi_event stop, float *out_ms) {
   if (!start || !stop || !out_ms) return fail(VRHI_ERR_INVALID, "NULL argument");
   VRHI_CUDA(cudaEventElapsedTime(out_ms, start->e, stop->e));
+  return VRHI_OK;
+}
+
+/* ---------------------------------------------------------------- recorded sequences ---- */
+
+int vrhi_sequence_begin(vrhi_stream stream) {
+  if (!stream) return fail(VRHI_ERR_INVALID, "NULL stream");
+  if (stream->recording) return fail(VRHI_ERR_INVALID, "the stream is already recording");
+  VRHI_TRY(set_device(stream->dev));
+  // thread-local mode: an allocation or synchronisation attempted by THIS thread while recording
+  // fails loudly instead of corrupting the recording; other threads are unaffected
+  VRHI_CUDA(cudaStreamBeginCapture(stream->s, cudaStreamCaptureModeThreadLocal));
+  stream->recording = true;
+  stream->record_mark = stream->launches;
+  return VRHI_OK;
+}
+
+int vrhi_sequence_end(vrhi_stream stream, vrhi_sequence *inout_seq) {
+  if (!stream || !inout_seq) return fail(VRHI_ERR_INVALID, "NULL argument");
+  if (!stream->recording) return fail(VRHI_ERR_INVALID, "the stream is not recording");
+  VRHI_TRY(set_device(stream->dev));
+  stream->recording = false;
+  const uint64_t kernels = stream->launches - stream->record_mark;
+  stream->launches = stream->record_mark;  // nothing ran
+  cudaGraph_t g = nullptr;
+  cudaError_t e = cudaStreamEndCapture(stream->s, &g);
+  if (e != cudaSuccess || !g) {
+    if (g) cudaGraphDestroy(g);
+    return fail(VRHI_ERR_CUDA, "the recording was invalidated: %s", cudaGetErrorString(e));
+  }
+  vrhi_sequence_t *seq = *inout_seq;
+  if (seq) {
+    cudaGraphExecUpdateResultInfo info{};
+    e = cudaGraphExecUpdate(seq->exec, g, &info);
+    if (e == cudaSuccess) {
+      seq->kernels = kernels;
+      seq->retargets++;
+      cudaGraphDestroy(g);
+      return VRHI_OK;
+    }
+    (void)cudaGetLastError();  // a different shape of recording: rebuild below
+    cudaGraphExecDestroy(seq->exec);
+    seq->exec = nullptr;
+    seq->rebuilds++;
+  } else {
+    seq = new (std::nothrow) vrhi_sequence_t{stream->dev, nullptr, 0, 0, 0};
+    if (!seq) {
+      cudaGraphDestroy(g);
+      return fail(VRHI_ERR_OOM, "host allocation failed");
+    }
+  }
+  e = cudaGraphInstantiate(&seq->exec, g, 0);
+  cudaGraphDestroy(g);
+  if (e != cudaSuccess) {
+    if (!*inout_seq) delete seq; else seq->exec = nullptr;
+    return fail(VRHI_ERR_CUDA, "cudaGraphInstantiate failed: %s", cudaGetErrorString(e));
+  }
+  seq->kernels = kernels;
+  *inout_seq = seq;
+  return VRHI_OK;
+}
+
+int vrhi_sequence_launch(vrhi_sequence seq, vrhi_stream stream) {
+  if (!seq || !stream) return fail(VRHI_ERR_INVALID, "NULL argument");
+  if (!seq->exec) return fail(VRHI_ERR_INVALID, "the sequence holds no recording");
+  if (seq->dev != stream->dev) return fail(VRHI_ERR_INVALID, "the sequence was recorded on another device");
+  VRHI_TRY(set_device(stream->dev));
+  VRHI_CUDA(cudaGraphLaunch(seq->exec, stream->s));
+  stream->launches += seq->kernels;
+  return VRHI_OK;
+}
+
+int vrhi_sequence_stats(vrhi_sequence seq, uint64_t *out_kernels, uint64_t *out_retargets, uint64_t *out_rebuilds) {
+  if (!seq) return fail(VRHI_ERR_INVALID, "NULL sequence");
+  if (out_kernels) *out_kernels = seq->kernels;
+  if (out_retargets) *out_retargets = seq->retargets;
+  if (out_rebuilds) *out_rebuilds = seq->rebuilds;
+  return VRHI_OK;
+}
+
+int vrhi_sequence_destroy(vrhi_sequence seq) {
+  if (!seq) return VRHI_OK;
+  cudaSetDevice(seq->dev->ordinal);
+  if (seq->exec) cudaGraphExecDestroy(seq->exec);
+  delete seq;
   return VRHI_OK;
 }
 

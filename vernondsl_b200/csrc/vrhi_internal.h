@@ -36,6 +36,14 @@ struct vrhi_stream_t {
   char *arena;           // device memory, or nullptr until first use
   size_t arena_payload;  // payload bytes available behind the control block
   uint64_t launches;
+  uint64_t record_mark;  // value of `launches` when recording began
+  bool recording;
+};
+
+struct vrhi_sequence_t {
+  vrhi_device_t *dev;
+  cudaGraphExec_t exec;
+  uint64_t kernels, retargets, rebuilds;
 };
 
 struct vrhi_event_t {
@@ -103,6 +111,7 @@ int launch_mse_tanh_bwd(vrhi_stream_t *, const ArgView *, int, const void *, siz
 int launch_fp32_probe(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
 int launch_vertex_transform(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
 int launch_flat_color(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
+int launch_widen_rows_u16(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
 
 // Copies a caller's parameter block into a zero-initialised struct of the current layout,
 // honouring the leading size field (older, shorter callers leave new fields zero).

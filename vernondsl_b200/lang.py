@@ -631,3 +631,61 @@ class Kernel:
 
 def kernel(fn):
     return Kernel(fn)
+
+
+class FrameLoop:
+    """The frame loop of fractal.py:30-33 without its window: ``for i in range(...): paint(i * 0.03)``
+    followed by a blit becomes a recorded run of launches whose frames land in a ring of device
+    buffers (there is no graphics stack to show them; ``frame(k)`` downloads one).
+
+    ``record(uniforms)`` walks the kernel once per frame on the host (each frame's uniforms become
+    part of the recording) and records the launches; ``play()`` replays all of them with a single
+    submission, which is what matters for small frames whose cost is the launch.  Calling ``record``
+    again with other uniforms re-targets the existing recording in place.
+    """
+
+    def __init__(self, kern: "Kernel", target: Field, ring: int = 4):
+        if ring < 1:
+            raise ValueError("the ring needs at least one frame")
+        dev, st = _runtime()
+        self.kernel, self.target, self.stream = kern, target, st
+        self.ring: List[Buffer] = [target.buffer] + [dev.empty(target.shape, target.dtype, L.IMAGE) for _ in range(ring - 1)]
+        self.seq = None
+        self.frames = 0
+
+    def record(self, uniforms) -> None:
+        uniforms = [u if isinstance(u, (tuple, list)) else (u,) for u in uniforms]
+        if not uniforms:
+            raise ValueError("nothing to record")
+        home = self.target.buffer
+        try:
+            if self.seq is None:
+                self.kernel(*uniforms[0])  # sizes the operator's stream scratch: nothing may allocate while recording
+            with self.stream.record(self.seq) as seq:
+                for k, u in enumerate(uniforms):
+                    self.target.buffer = self.ring[k % len(self.ring)]
+                    self.kernel(*u)
+            self.seq = seq
+            self.frames = len(uniforms)
+        finally:
+            self.target.buffer = home
+
+    def play(self) -> None:
+        if self.seq is None:
+            raise LangError("record() a run of frames first")
+        self.seq.launch(self.stream)
+
+    def frame(self, k: int) -> np.ndarray:
+        """Frame ``k`` of the last replay (the ring keeps only the last ``ring`` frames)."""
+        if not (0 <= k < self.frames) or k < self.frames - len(self.ring):
+            raise IndexError("that frame is no longer in the ring")
+        self.stream.check()
+        return self.ring[k % len(self.ring)].download(dtype=self.target.dtype, shape=self.target.shape)
+
+    def close(self) -> None:
+        if self.seq is not None:
+            self.seq.close()
+            self.seq = None
+        for b in self.ring[1:]:
+            b.close()
+        self.ring = self.ring[:1]

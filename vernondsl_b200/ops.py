@@ -68,9 +68,23 @@ def escape_params(kind: int, width: int, height: int, x0: float, y0: float, dx: 
     return p
 
 
-def escape_time(stream: Stream, image: Buffer, params: L.EscapeParams) -> None:
-    """Launch the escape-time map (the per-pixel loop of fractal.py:18-25) into ``image``."""
-    launch(stream, "escape_time", [image.arg(L.IMAGE if image.arg_class == L.IMAGE else L.OUTPUT)], params)
+def escape_time(stream: Stream, image: Buffer, params: L.EscapeParams, wire: Optional[Buffer] = None) -> None:
+    """Launch the escape-time map (the per-pixel loop of fractal.py:18-25) into ``image``.  ``wire``,
+    a uint16 image of the same geometry, receives every count a second time (the form sent to peers)."""
+    args = [image.arg(L.IMAGE if image.arg_class == L.IMAGE else L.OUTPUT)]
+    if wire is not None:
+        args.append(wire.arg(L.IMAGE if wire.arg_class == L.IMAGE else L.OUTPUT))
+    launch(stream, "escape_time", args, params)
+
+
+def widen_rows_u16(stream: Stream, wire: Buffer, image: Buffer, width: int, height: int, chunk_rows: int, world: int,
+                   skip_rank: int, slab_first: int, slab_count: int) -> None:
+    """Copy uint16 counts of the given slabs into the uint32 image, leaving out ``skip_rank``'s chunks."""
+    p = L.WidenParams()
+    p.size = C.sizeof(L.WidenParams)
+    p.width, p.height, p.chunk_rows, p.world = int(width), int(height), int(chunk_rows), int(world)
+    p.skip_rank, p.slab_first, p.slab_count = int(skip_rank), int(slab_first), int(slab_count)
+    launch(stream, "widen_rows_u16", [wire.arg(), image.arg(L.IMAGE if image.arg_class == L.IMAGE else L.OUTPUT)], p)
 
 
 # ------------------------------------------------------------------------------ maps ----------

@@ -16,6 +16,8 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import List, Optional, Tuple
 
+import numpy as np
+
 from . import _lib as L
 from . import ops
 
@@ -173,3 +175,39 @@ class PeerImageExchange:
         for b in self.peers.values():
             b.close()
         self.peers = {}
+
+
+class WireImageExchange:
+    """The same gather with uint16 counts on the wire: half the bytes cross NVLink.
+
+    The escape-time kernel writes every count twice, as uint32 into the rank's image and as uint16
+    into a wire image of the same geometry (``ops.escape_time(..., wire=exchange.wire)``).  The wire
+    chunks are pushed into the peers' wire images by the copy engines (:class:`PeerImageExchange`);
+    ``finish`` orders the one-element all-reduce behind the pushes and then widens the peers' rows
+    from the local wire image into the uint32 image (``widen_rows_u16``, HBM-bound).  Needs
+    ``max_iter <= 65535``, so that nothing is lost.
+    """
+
+    def __init__(self, dev, image, plan: ImagePlan, width: int, group=None):
+        self.dev, self.image, self.plan, self.width = dev, image, plan, int(width)
+        self.wire = dev.empty((plan.height, self.width), np.uint16, L.IMAGE)
+        self.peer = PeerImageExchange(dev, self.wire, plan, self.width * 2, group)
+        self.n_slabs = self.peer.n_slabs
+
+    def push(self, stream, slab_range=None) -> None:
+        self.peer.push(stream, slab_range)
+
+    def finish(self, torch_stream, stream, slab_range=None) -> None:
+        """``torch_stream`` and ``stream`` are the same CUDA stream (torch's handle for the collective,
+        the library's for the kernel).  After this, stream-ordered, the uint32 image holds every rank's
+        rows of ``slab_range`` (default: all)."""
+        from . import ops
+
+        self.peer.finish(torch_stream)
+        lo, hi = slab_range if slab_range is not None else (0, self.n_slabs)
+        p = self.plan
+        ops.widen_rows_u16(stream, self.wire, self.image, self.width, p.height, p.part.chunk_rows, p.world, p.rank, lo, hi - lo)
+
+    def close(self) -> None:
+        self.peer.close()
+        self.wire.close()

@@ -218,6 +218,48 @@ class Stream:
     def wait(self, event: "Event") -> None:
         check(lib().vrhi_stream_wait_event(self._h, event._h))
 
+    def record(self, into: Optional["Sequence"] = None) -> "_Recording":
+        """``with stream.record() as seq:`` records the launches issued on this stream inside the
+        block (``vrhi_sequence_begin/end``) instead of running them; ``seq.launch()`` replays them as
+        one submission.  Passing an existing sequence re-targets it in place."""
+        return _Recording(self, into)
+
+
+class Sequence:
+    """A recorded run of launches (``vrhi_sequence``), replayed with one submission."""
+
+    def __init__(self, stream: Stream):
+        self.stream = stream
+        self._h = C.c_void_p()
+
+    def launch(self, stream: Optional[Stream] = None) -> None:
+        check(lib().vrhi_sequence_launch(self._h, (stream or self.stream)._h))
+
+    def stats(self) -> dict:
+        k, u, r = C.c_uint64(), C.c_uint64(), C.c_uint64()
+        check(lib().vrhi_sequence_stats(self._h, C.byref(k), C.byref(u), C.byref(r)))
+        return {"kernels": k.value, "retargets": u.value, "rebuilds": r.value}
+
+    def close(self) -> None:
+        if self._h:
+            lib().vrhi_sequence_destroy(self._h)
+            self._h = C.c_void_p()
+
+
+class _Recording:
+    def __init__(self, stream: Stream, into: Optional[Sequence]):
+        self.stream, self.seq = stream, into or Sequence(stream)
+
+    def __enter__(self) -> Sequence:
+        check(lib().vrhi_sequence_begin(self.stream._h))
+        return self.seq
+
+    def __exit__(self, exc_type, exc, tb) -> bool:
+        rc = lib().vrhi_sequence_end(self.stream._h, C.byref(self.seq._h))
+        if exc_type is None:
+            check(rc)
+        return False
+
 
 class Event:
     def __init__(self, dev: Device, handle):

@@ -347,9 +347,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workloads", default="all", choices=["all", "main"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--gather", default="p2p16", choices=["p2p16", "p2p", "nccl"],
-                    help="N > 1: exchange image chunks by peer copies of uint16 counts widened on arrival (p2p16), by peer "
-                         "copies of the uint32 rows (p2p), or by NCCL all-gather")
+    ap.add_argument("--gather", default="p2p16", choices=["pull16", "p2p16", "p2p", "nccl"],
+                    help="N > 1: how the image is gathered.  pull16: every rank reads its peers' uint16 counts over NVLink and "
+                         "widens them in the same kernel; p2p16: uint16 counts pushed by the copy engines, widened on arrival; "
+                         "p2p: uint32 rows pushed by the copy engines; nccl: NCCL all-gather")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
@@ -418,61 +419,111 @@ def main():
     # in-place all-gather of the slabs a launch completed runs on a second stream while the next
     # launch computes.  The step ends when the last gather has finished.
     GROUPS = int(os.environ.get("VRHI_BENCH_GROUPS", "4"))  # launches per step; finished slabs are exchanged while the next launch computes
+    # Group g takes slabs g, g+GROUPS, g+2*GROUPS, ...: every group is a thin comb over the whole image, so the
+    # groups cost the same although the rows near the set cost far more than the rows at the edges.
     exchange = None
     n_slabs = plan.part.chunk_count
     group_params, group_slabs = [], []
     if world > 1:
         import copy
         for gidx in range(GROUPS):
-            k0, k1 = n_slabs * gidx // GROUPS, n_slabs * (gidx + 1) // GROUPS
-            if k1 == k0:
+            count = (n_slabs - gidx + GROUPS - 1) // GROUPS if gidx < n_slabs else 0
+            if count <= 0:
                 continue
             gp = copy.copy(params)
-            gp.chunk_first = plan.part.chunk_first + k0 * plan.part.chunk_step
-            gp.chunk_count = k1 - k0
+            gp.chunk_first = plan.part.chunk_first + gidx * plan.part.chunk_step
+            gp.chunk_step = plan.part.chunk_step * GROUPS
+            gp.chunk_count = count
             group_params.append(gp)
-            group_slabs.append((k0, k1))
+            group_slabs.append((gidx, count, GROUPS))
         comm_stream = torch.cuda.Stream(device=local)
         comm_st = dev.wrap_stream(comm_stream.cuda_stream)
         exchange = None
-        if args.gather in ("p2p", "p2p16"):
+        if args.gather != "nccl":
             try:
-                exchange = (partition.WireImageExchange(dev, image, plan, W) if args.gather == "p2p16"
-                            else partition.PeerImageExchange(dev, image, plan, W * 4))
+                if args.gather == "pull16":
+                    exchange = partition.PullImageExchange(dev, image, plan, W, groups=len(group_params))
+                    sig_stream = torch.cuda.Stream(device=local)
+                    sig_st = dev.wrap_stream(sig_stream.cuda_stream)
+                elif args.gather == "p2p16":
+                    exchange = partition.WireImageExchange(dev, image, plan, W)
+                    arrive_stream = torch.cuda.Stream(device=local)
+                    arrive_st = dev.wrap_stream(arrive_stream.cuda_stream)
+                else:
+                    exchange = partition.PeerImageExchange(dev, image, plan, W * 4)
             except Exception as exc:  # no peer mapping on this box: fall back to the NCCL gather
                 print(f"peer exchange unavailable ({exc}); using the NCCL all-gather", file=sys.stderr)
 
-    wire = exchange.wire if isinstance(exchange, partition.WireImageExchange) else None
-    SYNC_PER_GROUP = os.environ.get("VRHI_BENCH_SYNC", "group") == "group"
+    pulling = isinstance(exchange, partition.PullImageExchange)
+    pushing16 = isinstance(exchange, partition.WireImageExchange)
+    trace = []   # (label, event) of one extra, untimed step when VRHI_BENCH_TRACE is set: where a step's time goes
+    TRACING = [False]
+
+    def mark(label, stream):
+        if TRACING[0]:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record(stream)
+            trace.append((label, e))
 
     def step():
         if world == 1:
             compute()
             return
         works = []
-        for gp, (k0, k1) in zip(group_params, group_slabs):
+        mark("start", tstream)
+        wire = exchange.wire if (pulling or pushing16) else None
+        for gi, (gp, slabs) in enumerate(zip(group_params, group_slabs)):
             ops.escape_time(st, image, gp, wire=wire)
+            mark(f"computed {gi}", tstream)
             ev = torch.cuda.Event()
             ev.record(tstream)
             comm_stream.wait_event(ev)
-            if exchange is not None:
+            if pulling:
+                # tell the peers this group is ready (own stream: the next group's kernel is not held up), then
+                # fetch their rows of the same group: remote uint16 loads over NVLink, widened into the image
+                sig_stream.wait_event(ev)
+                exchange.signal(sig_st, gi)
+                exchange.pull(comm_st, gi, slabs)
+                mark(f"pulled {gi}", comm_stream)
+            elif exchange is not None:
                 # one stream for all peers: pushes to several peers at once measured slower on this box
-                exchange.push(comm_st, (k0, k1))      # copy engines: overlaps the next group's kernel
-                if wire is not None and SYNC_PER_GROUP:
-                    exchange.finish(comm_stream, comm_st, (k0, k1))   # widen what has arrived while later groups compute
+                exchange.push(comm_st, slabs)      # copy engines: overlaps the next group's kernel
+                mark(f"pushed {gi}", comm_stream)
+                if pushing16:
+                    # arrival on a third stream, so that the next push does not queue behind it: the all-reduce and
+                    # the widening kernel get few issue slots while the escape-time kernel runs and catch up after it
+                    pev = torch.cuda.Event()
+                    pev.record(comm_stream)
+                    arrive_stream.wait_event(pev)
+                    exchange.finish(arrive_stream, arrive_st, slabs)
+                    mark(f"widened {gi}", arrive_stream)
             else:
                 with torch.cuda.stream(comm_stream):
-                    works += partition.all_gather_image(image_t, plan, async_op=True, slab_range=(k0, k1))
-        if exchange is not None:
-            if wire is None:
+                    works += partition.all_gather_image(image_t, plan, async_op=True, slabs=slabs)
+        if pulling:
+            tstream.wait_stream(sig_stream)
+            tstream.wait_stream(comm_stream)
+            exchange.next_step()
+        elif exchange is not None:
+            if pushing16:
+                tstream.wait_stream(arrive_stream)
+            else:
                 exchange.finish(comm_stream)
-            elif not SYNC_PER_GROUP:
-                exchange.finish(comm_stream, comm_st)
+            mark("exchange complete", comm_stream)
             tstream.wait_stream(comm_stream)
         else:
             with torch.cuda.stream(tstream):
                 for w in works:
                     w.wait()   # the compute stream waits for the gathers: the step is complete after this
+
+    EXCHANGE_NOTE = ("none" if world == 1 else
+                     "no collective: each rank reads its peers' rows as uint16 out of their memory over NVLink and widens them into "
+                     "its uint32 image in one kernel, group by group while later groups compute; readiness flags with bounded device waits" if pulling else
+                     "counts pushed as uint16 into every peer's wire image by strided peer copies (copy engines over NVLink), overlapped "
+                     "with compute, widened into the uint32 image after a 4-byte NCCL all-reduce" if pushing16 else
+                     "image chunks pushed into every peer's image by strided peer copies (copy engines over NVLink), overlapped with "
+                     "compute; one 4-byte NCCL all-reduce orders completion" if exchange is not None else
+                     "in-place NCCL all-gather of the image each step, overlapped with compute")
 
     def timed(fn, k):
         barrier()
@@ -499,6 +550,14 @@ def main():
     launches0 = st.launch_count()
     total_ms = timed(step, args.steps)
     launches = st.launch_count() - launches0
+    if world > 1 and os.environ.get("VRHI_BENCH_TRACE"):
+        barrier()
+        TRACING[0] = True
+        with torch.cuda.stream(tstream):
+            step()
+        TRACING[0] = False
+        torch.cuda.synchronize()
+        print(f"rank {rank} step timeline (ms after start): " + ", ".join(f"{lab} {trace[0][1].elapsed_time(e):.3f}" for lab, e in trace[1:]), file=sys.stderr)
     t_hold = time.perf_counter()
     while time.perf_counter() - t_hold < 0.3:
         step()
@@ -599,7 +658,7 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": WORKLOAD_NAME, "partition": f"cyclic 128-row chunks over {world} rank(s)",
-                       "collective": ("none" if world == 1 else "counts pushed as uint16 into every peer's wire image by strided peer copies (copy engines over NVLink) and widened into the uint32 image on arrival, overlapped with compute; 4-byte NCCL all-reduces order completion" if wire is not None else "image chunks pushed into every peer's image by strided peer copies (copy engines over NVLink), overlapped with compute; one 4-byte NCCL all-reduce orders completion" if exchange is not None else "in-place NCCL all-gather of the image each step, overlapped with compute"),
+                       "collective": EXCHANGE_NOTE,
                        "l2": "no inputs; the 1 GiB output image written each step exceeds L2 (126 MB)"},
             "verified_bit_exact": verified,
             "compute_only": {"value": compute_value, "ms_per_step": compute_ms},

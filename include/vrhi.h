@@ -257,7 +257,33 @@ typedef struct vrhi_widen_params {
   uint32_t width, height;
   uint32_t chunk_rows, world, skip_rank;
   uint32_t slab_first, slab_count;
+  uint32_t slab_stride; /* slabs slab_first + k*slab_stride, k < slab_count; 0 reads as 1 */
 } vrhi_widen_params;
+
+/* ops "gather_signal" and "gather_pull_u16" -- the gather in pull form, for ranks whose
+ * buffers are mapped into one another (vrhi_buffer_ipc_export/open): transfer over NVLink and
+ * widening are one kernel on the receiving side.
+ * gather_signal: args = the flag arrays (uint32[world], zero-initialised, one per rank) of the
+ *   world-1 peers, in any order; stores `seq` into slot `rank` of each.  Launch it on the stream
+ *   that computed the rows, after them.
+ * gather_pull_u16: args = [0] the caller's own flag array, [1] its uint32 image, [2..] the uint16
+ *   wire images of ranks 0..world-1 without the caller's own, in rank order.  Waits until every
+ *   peer's slot in the flag array has reached `seq` (a one-warp kernel; at most wait_ms
+ *   milliseconds, default 2000; on expiry nothing is copied and vrhi_stream_check returns
+ *   VRHI_ERR_TIMEOUT), then copies the peers' rows of the given slabs into the image.
+ * Sequence numbers must grow by less than 2^31 between a wait and the value it waits for.
+ * A rank must not overwrite rows a peer may still be pulling: alternate two wire images.
+ * Reference counterpart: none (the reference runs on one device). */
+#define VRHI_GATHER_MAX_WORLD 8
+typedef struct vrhi_gather_params {
+  uint32_t size;
+  uint32_t width, height;
+  uint32_t chunk_rows, world, rank;
+  uint32_t slab_first, slab_count;
+  uint32_t seq;
+  uint32_t wait_ms;
+  uint32_t slab_stride; /* as in vrhi_widen_params */
+} vrhi_gather_params;
 
 /* op "fused_map" -- the map chain  out = tanh(a*x + y) * exp(-0.5*x*x) + sqrt(|y| + 1e-3)
  * as one kernel.  args: [0] a, [1] x, [2] y (INPUT, n floats), [3] out (OUTPUT, n floats). */

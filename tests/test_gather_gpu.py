@@ -77,10 +77,10 @@ def test_gather_with_uint16_on_the_wire_rebuilds_the_whole_image(W, world):
         for q in range(world):
             if q != r:
                 wires[r].copy_2d_to(wires[q], r * chunk_bytes, world * chunk_bytes, r * chunk_bytes, world * chunk_bytes, chunk_bytes, slabs, st)
-    # arrival, in two slab ranges as a pipelined step would do it
+    # arrival, in two combs of slabs as a pipelined step does it: slabs 0 and 2, then slab 1
     for r in range(world):
-        ops.widen_rows_u16(st, wires[r], images[r], W, H, chunk_rows, world, r, 0, 1)
-        ops.widen_rows_u16(st, wires[r], images[r], W, H, chunk_rows, world, r, 1, slabs - 1)
+        ops.widen_rows_u16(st, wires[r], images[r], W, H, chunk_rows, world, r, 0, 2, 2)
+        ops.widen_rows_u16(st, wires[r], images[r], W, H, chunk_rows, world, r, 1, 1, 2)
     st.check()
     for r in range(world):
         assert np.array_equal(images[r].download(dtype=np.uint32, shape=(H, W)), want), r
@@ -92,4 +92,64 @@ def test_gather_with_uint16_on_the_wire_rebuilds_the_whole_image(W, world):
     assert np.array_equal(blank.download(dtype=np.uint32, shape=(H, W)), want)
     with pytest.raises(vd.VrhiError):
         ops.widen_rows_u16(st, wires[0], blank, W, H, chunk_rows, world, 0, slabs, 1)   # beyond the last slab
+    st.close()
+
+
+def test_pull_gather_reads_the_peers_rows_and_widens_them():
+    dev = vd.Device(0)
+    st = dev.stream()
+    W, world, chunk_rows, slabs = 256, 3, 4, 5
+    H = chunk_rows * world * slabs
+    max_iter = 500
+    dx, dy, want = _julia(W, H, max_iter)
+    images = [dev.empty((H, W), np.uint32, L.IMAGE) for _ in range(world)]
+    wires = [dev.empty((H, W), np.uint16, L.IMAGE) for _ in range(world)]
+    flags = [dev.empty((world,), np.uint32, L.STORAGE_BUFFER) for _ in range(world)]
+    for r in range(world):
+        images[r].fill(0xEE, stream=st)
+        wires[r].fill(0xDD, stream=st)
+        flags[r].fill(0, stream=st)
+        part = ops.partition_rows(H, world, r, L.PART_CYCLIC, chunk_rows)
+        p = ops.escape_params(L.JULIA, W, H, J["x0"], J["y0"], dx, dy, cr=J["cr"], ci=J["ci"], max_iter=max_iter, partition=part)
+        ops.escape_time(st, images[r], p, wire=wires[r])
+    seq = 7
+    for r in range(world):          # every rank marks its rows ready in its peers' flag arrays
+        ops.gather_signal(st, [flags[q] for q in range(world) if q != r], world, r, seq)
+    for r in range(world):          # the marks are already there (same stream): the wait returns at once
+        peers = [wires[q] for q in range(world) if q != r]
+        ops.gather_pull_u16(st, flags[r], images[r], peers, W, H, chunk_rows, world, r, 0, 3, seq, wait_ms=200, slab_stride=2)   # slabs 0, 2, 4
+        ops.gather_pull_u16(st, flags[r], images[r], peers, W, H, chunk_rows, world, r, 1, 2, seq - 3, wait_ms=200, slab_stride=2)  # slabs 1, 3; an older number is satisfied too
+    st.check()
+    for r in range(world):
+        got_flags = flags[r].download(dtype=np.uint32)
+        assert [int(v) for v in got_flags] == [0 if q == r else seq for q in range(world)]
+        assert np.array_equal(images[r].download(dtype=np.uint32, shape=(H, W)), want), r
+    st.close()
+
+
+def test_pull_gather_gives_up_after_its_time_limit_and_reports_it():
+    """A flag that nothing sets: the device-side wait runs out, the kernel copies nothing and returns,
+    the stream reports VRHI_ERR_TIMEOUT once and stays usable."""
+    dev = vd.Device(0)
+    st = dev.stream()
+    W, H, world, chunk_rows = 64, 16, 2, 4
+    image = dev.empty((H, W), np.uint32, L.IMAGE)
+    wire_peer = dev.empty((H, W), np.uint16, L.IMAGE)
+    flags = dev.empty((world,), np.uint32, L.STORAGE_BUFFER)
+    image.fill(0x11, stream=st)
+    wire_peer.fill(0x22, stream=st)
+    flags.fill(0, stream=st)
+    ops.gather_pull_u16(st, flags, image, [wire_peer], W, H, chunk_rows, world, 0, 0, 2, seq=1, wait_ms=20)
+    with pytest.raises(vd.VrhiError) as err:
+        st.check()
+    assert err.value.status == L.ERR_TIMEOUT
+    assert np.all(image.download(dtype=np.uint32, shape=(H, W)) == 0x11111111)      # untouched
+    st.check()                                                                       # reported once; the stream goes on
+    ops.gather_signal(st, [flags], world, 1, 1)                                      # the peer's mark arrives
+    ops.gather_pull_u16(st, flags, image, [wire_peer], W, H, chunk_rows, world, 0, 0, 2, seq=1, wait_ms=20)
+    st.check()
+    got = image.download(dtype=np.uint32, shape=(H, W))
+    rows_of_peer = [r for r in range(H) if (r // chunk_rows) % world == 1]
+    rows_own = [r for r in range(H) if (r // chunk_rows) % world == 0]
+    assert np.all(got[rows_of_peer] == 0x2222) and np.all(got[rows_own] == 0x11111111)
     st.close()

@@ -70,7 +70,17 @@ class EscapeParams(C.Structure):
 
 class WidenParams(C.Structure):
     _fields_ = [("size", C.c_uint32), ("width", C.c_uint32), ("height", C.c_uint32), ("chunk_rows", C.c_uint32),
-                ("world", C.c_uint32), ("skip_rank", C.c_uint32), ("slab_first", C.c_uint32), ("slab_count", C.c_uint32)]
+                ("world", C.c_uint32), ("skip_rank", C.c_uint32), ("slab_first", C.c_uint32), ("slab_count", C.c_uint32),
+                ("slab_stride", C.c_uint32)]
+
+
+class GatherParams(C.Structure):
+    _fields_ = [("size", C.c_uint32), ("width", C.c_uint32), ("height", C.c_uint32), ("chunk_rows", C.c_uint32),
+                ("world", C.c_uint32), ("rank", C.c_uint32), ("slab_first", C.c_uint32), ("slab_count", C.c_uint32),
+                ("seq", C.c_uint32), ("wait_ms", C.c_uint32), ("slab_stride", C.c_uint32)]
+
+
+GATHER_MAX_WORLD = 8
 
 
 class MapParams(C.Structure):

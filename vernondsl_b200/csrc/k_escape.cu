@@ -16,7 +16,9 @@
 // cannot take.
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <type_traits>
+#include <unordered_map>
 
 #include "vrhi_internal.h"
 
@@ -327,6 +329,42 @@ __global__ void __launch_bounds__(256, 6) escape_regroup_kernel(EscapeDev p, voi
   }
 }
 
+// Launch of the regrouping kernel with its residency pinned.  The kernel is a persistent grid of
+// `per_sm` blocks per SM that steal work; that only balances if the blocks really sit per_sm to an
+// SM.  On an idle GPU they do, but when blocks of another stream's kernel are resident at launch
+// time the hardware packs the grid onto whichever SMs have room (up to 6 blocks fit by registers),
+// and the SMs that got more than their share then finish late (measured: 3.7 ms instead of 2.5 ms
+// for the 16384^2 image).  Unused dynamic shared memory sized so that exactly per_sm blocks fit makes
+// the surplus blocks wait for their own SM instead.
+template <class Kern>
+static int launch_regroup_pinned(Kern kern, int grid, int per_sm, vrhi_stream_t *st, const EscapeDev &p, void *image,
+                                 uint32_t *counter, uint16_t *wire) {
+  static std::mutex mu;
+  static std::unordered_map<const void *, size_t> static_bytes;
+  size_t fixed = 0;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = static_bytes.find(reinterpret_cast<const void *>(kern));
+    if (it == static_bytes.end()) {
+      cudaFuncAttributes fa{};
+      VRHI_CUDA(cudaFuncGetAttributes(&fa, kern));
+      it = static_bytes.emplace(reinterpret_cast<const void *>(kern), fa.sharedSizeBytes).first;
+    }
+    fixed = it->second;
+  }
+  const size_t per_sm_bytes = st->dev->prop.sharedMemPerMultiprocessor;  // each resident block also reserves 1 KB
+  size_t total = ((size_t)((double)per_sm_bytes / (per_sm + 0.5)) - 1024) & ~size_t(127);
+  const size_t optin = st->dev->prop.sharedMemPerBlockOptin;
+  if (total > optin) total = optin;
+  size_t dyn = total > fixed ? total - fixed : 0;
+  if (const char *e = getenv("VRHI_ESCAPE_PIN")) {  // tuning aid: 0 launches without the padding
+    if (atoi(e) == 0) dyn = 0;
+  }
+  VRHI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+  kern<<<grid, 256, dyn, st->s>>>(p, image, counter, wire);
+  return VRHI_OK;
+}
+
 template <int KIND, int MODE, int TEST>
 static void launch_checked_out(int out, int grid, cudaStream_t s, const EscapeDev &p, void *image, uint32_t *ctr, uint16_t *wire) {
   switch (out) {
@@ -399,6 +437,10 @@ int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const
     const uint64_t tiles = (uint64_t)p.tiles_per_row * p.rows_owned;
     uint64_t bt = tiles / (resident_warps * 8);
     p.batch_tiles = (uint32_t)(bt < 2 ? 2 : bt > 16 ? 16 : bt);
+    if (const char *e = getenv("VRHI_ESCAPE_BATCH")) {  // tuning aid
+      const int b = atoi(e);
+      if (b >= 1 && b <= 64) p.batch_tiles = (uint32_t)b;
+    }
   }
   p.batches_per_row = (p.tiles_per_row + p.batch_tiles - 1) / p.batch_tiles;
   uint64_t nb = (uint64_t)p.batches_per_row * p.rows_owned;
@@ -430,41 +472,24 @@ int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const
     // owns enough tiles to keep its pool busy and the drain at the end is shorter.
     uint64_t ctas = (nb + 7) / 8;
     const uint64_t tiles_total = (uint64_t)p.tiles_per_row * p.rows_owned;
-    const uint64_t per_sm = tiles_total / ((uint64_t)sms * 4 * 8) < 32 ? 2 : 4;
+    uint64_t per_sm = tiles_total / ((uint64_t)sms * 4 * 8) < 32 ? 2 : 4;
     uint64_t cap = (uint64_t)sms * per_sm;
     grid = (int)(ctas < cap ? ctas : cap);
-    // Tuning aid: VRHI_ESCAPE_TUNE="U,T[,ctas_per_sm]" selects another block length / refill threshold for
-    // uint32 output (the shipped default is what measurements on B200 favoured).
-    if (const char *tune = getenv("VRHI_ESCAPE_TUNE")) {
-      int tu = 0, tt = 0, tc = 0, tk = 8;
-      int got = sscanf(tune, "%d,%d,%d,%d", &tu, &tt, &tc, &tk);
-      if (got >= 2 && q.output == VRHI_OUT_COUNT_U32 && q.mode == VRHI_ESCAPE_EXACT && !wire) {
-        if (got >= 3 && tc > 0) { cap = (uint64_t)sms * tc; grid = (int)(ctas < cap ? ctas : cap); }
-        bool hit = true;
-#define TUNEK(UU, TT, KK)                                                                                              \
-  else if (tu == UU && tt == TT && tk == KK) {                                                                         \
-    if (q.kind == VRHI_ESCAPE_MANDELBROT) escape_regroup_kernel<VRHI_ESCAPE_MANDELBROT, VRHI_OUT_COUNT_U32, UU, TT, KK><<<grid, 256, 0, st->s>>>(p, args[0].ptr, counter); \
-    else escape_regroup_kernel<VRHI_ESCAPE_JULIA, VRHI_OUT_COUNT_U32, UU, TT, KK><<<grid, 256, 0, st->s>>>(p, args[0].ptr, counter); \
-  }
-#define TUNE(UU, TT) TUNEK(UU, TT, 8)
-        if (false) {}
-        TUNE(8, 4) TUNE(8, 8) TUNE(8, 12) TUNE(12, 8) TUNE(12, 12) TUNE(16, 8) TUNE(16, 12) TUNEK(8, 8, 4) TUNEK(8, 8, 6) TUNEK(12, 8, 4) TUNEK(12, 8, 6) TUNEK(12, 8, 12) TUNEK(8, 8, 12) TUNEK(12, 6, 6) TUNEK(12, 10, 6)
-        else hit = false;
-#undef TUNE
-#undef TUNEK
-        if (hit) return post_launch(st, "escape_time (regrouping, tuned)");
-      }
+    // Tuning aid: VRHI_ESCAPE_CTAS_PER_SM overrides the residency chosen above.
+    if (const char *e = getenv("VRHI_ESCAPE_CTAS_PER_SM")) {
+      const int tc = atoi(e);
+      if (tc >= 1 && tc <= 6) { per_sm = (uint64_t)tc; cap = (uint64_t)sms * tc; grid = (int)(ctas < cap ? ctas : cap); }
     }
-    // U = 12, T = 8, K = 8: the sweep on B200 is flat within 2 % between U = 8..16 and T = 8..12
+    // U = 12, T = 8, K = 8: a sweep on B200 (U = 8..16, T = 4..12, K = 4..12) was flat within 2 % around this point
 #define REGROUP(KIND, OUT)                                                                                             \
   do {                                                                                                                 \
-    if (q.mode == VRHI_ESCAPE_EXACT) escape_regroup_kernel<KIND, OUT, 12, 8, 8, VRHI_ESCAPE_EXACT><<<grid, 256, 0, st->s>>>(p, args[0].ptr, counter); \
-    else escape_regroup_kernel<KIND, OUT, 12, 8, 8, VRHI_ESCAPE_FAST><<<grid, 256, 0, st->s>>>(p, args[0].ptr, counter);   \
+    if (q.mode == VRHI_ESCAPE_EXACT) VRHI_TRY(launch_regroup_pinned(escape_regroup_kernel<KIND, OUT, 12, 8, 8, VRHI_ESCAPE_EXACT>, grid, (int)per_sm, st, p, args[0].ptr, counter, nullptr)); \
+    else VRHI_TRY(launch_regroup_pinned(escape_regroup_kernel<KIND, OUT, 12, 8, 8, VRHI_ESCAPE_FAST>, grid, (int)per_sm, st, p, args[0].ptr, counter, nullptr));   \
   } while (0)
 #define REGROUP_WIRE(KIND)                                                                                              \
   do {                                                                                                                 \
-    if (q.mode == VRHI_ESCAPE_EXACT) escape_regroup_kernel<KIND, VRHI_OUT_COUNT_U32, 12, 8, 8, VRHI_ESCAPE_EXACT, true><<<grid, 256, 0, st->s>>>(p, args[0].ptr, counter, wire); \
-    else escape_regroup_kernel<KIND, VRHI_OUT_COUNT_U32, 12, 8, 8, VRHI_ESCAPE_FAST, true><<<grid, 256, 0, st->s>>>(p, args[0].ptr, counter, wire);   \
+    if (q.mode == VRHI_ESCAPE_EXACT) VRHI_TRY(launch_regroup_pinned(escape_regroup_kernel<KIND, VRHI_OUT_COUNT_U32, 12, 8, 8, VRHI_ESCAPE_EXACT, true>, grid, (int)per_sm, st, p, args[0].ptr, counter, wire)); \
+    else VRHI_TRY(launch_regroup_pinned(escape_regroup_kernel<KIND, VRHI_OUT_COUNT_U32, 12, 8, 8, VRHI_ESCAPE_FAST, true>, grid, (int)per_sm, st, p, args[0].ptr, counter, wire));   \
   } while (0)
     if (wire) {
       if (q.kind == VRHI_ESCAPE_MANDELBROT) REGROUP_WIRE(VRHI_ESCAPE_MANDELBROT);

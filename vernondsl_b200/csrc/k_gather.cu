@@ -10,14 +10,14 @@ namespace vrhi {
 template <bool VEC>
 __global__ void __launch_bounds__(256) widen_rows_u16_kernel(const uint16_t *__restrict__ wire, uint32_t *__restrict__ image,
                                                              uint32_t width, uint32_t height, uint32_t chunk_rows, uint32_t world,
-                                                             uint32_t skip_rank, uint32_t slab_first, uint32_t total_rows) {
+                                                             uint32_t skip_rank, uint32_t slab_first, uint32_t slab_stride, uint32_t total_rows) {
   const uint32_t nq = skip_rank < world ? world - 1 : world;
   const uint32_t rows_per_slab = nq * chunk_rows;
   for (uint32_t u = blockIdx.y; u < total_rows; u += gridDim.y) {
     const uint32_t slab = u / rows_per_slab, rem = u - slab * rows_per_slab;
     const uint32_t qq = rem / chunk_rows, rr = rem - qq * chunk_rows;
     const uint32_t q = qq + (qq >= skip_rank ? 1u : 0u);
-    const uint64_t row = ((uint64_t)(slab_first + slab) * world + q) * chunk_rows + rr;
+    const uint64_t row = ((uint64_t)(slab_first + slab * slab_stride) * world + q) * chunk_rows + rr;
     if (row >= height) continue;
     const size_t base = (size_t)row * width;
     if (VEC) {
@@ -49,7 +49,9 @@ int launch_widen_rows_u16(vrhi_stream_t *st, const ArgView *args, int n_args, co
   if (args[1].bytes < px * 4) return fail(VRHI_ERR_SIZE, "widen_rows_u16: the image view holds %llu bytes, %llu needed", (unsigned long long)args[1].bytes, (unsigned long long)(px * 4));
   const uint64_t n_chunks = ((uint64_t)q.height + q.chunk_rows - 1) / q.chunk_rows;
   const uint64_t n_slabs = (n_chunks + q.world - 1) / q.world;
-  if ((uint64_t)q.slab_first + q.slab_count > n_slabs) return fail(VRHI_ERR_SIZE, "widen_rows_u16: slabs %u..%llu lie beyond the image's %llu", q.slab_first, (unsigned long long)q.slab_first + q.slab_count, (unsigned long long)n_slabs);
+  const uint32_t stride = q.slab_stride ? q.slab_stride : 1u;
+  if (q.slab_count && (uint64_t)q.slab_first + (uint64_t)(q.slab_count - 1) * stride >= n_slabs)
+    return fail(VRHI_ERR_SIZE, "widen_rows_u16: slabs %u + k*%u, k < %u, reach beyond the image's %llu", q.slab_first, stride, q.slab_count, (unsigned long long)n_slabs);
   const uint32_t nq = q.skip_rank < q.world ? q.world - 1 : q.world;
   const uint64_t total_rows = (uint64_t)q.slab_count * nq * q.chunk_rows;
   if (total_rows == 0) return VRHI_OK;  // nothing to widen (one rank, or an empty slab range)
@@ -60,13 +62,171 @@ int launch_widen_rows_u16(vrhi_stream_t *st, const ArgView *args, int n_args, co
   if (vec) {
     grid.x = (q.width / 8 + 255) / 256;
     widen_rows_u16_kernel<true><<<grid, 256, 0, st->s>>>(reinterpret_cast<const uint16_t *>(args[0].ptr), reinterpret_cast<uint32_t *>(args[1].ptr),
-                                                         q.width, q.height, q.chunk_rows, q.world, q.skip_rank, q.slab_first, (uint32_t)total_rows);
+                                                         q.width, q.height, q.chunk_rows, q.world, q.skip_rank, q.slab_first, stride, (uint32_t)total_rows);
   } else {
     grid.x = (q.width + 255) / 256 < 64 ? (q.width + 255) / 256 : 64;
     widen_rows_u16_kernel<false><<<grid, 256, 0, st->s>>>(reinterpret_cast<const uint16_t *>(args[0].ptr), reinterpret_cast<uint32_t *>(args[1].ptr),
-                                                          q.width, q.height, q.chunk_rows, q.world, q.skip_rank, q.slab_first, (uint32_t)total_rows);
+                                                          q.width, q.height, q.chunk_rows, q.world, q.skip_rank, q.slab_first, stride, (uint32_t)total_rows);
   }
   return post_launch(st, "widen_rows_u16");
+}
+
+// ---------------------------------------------------------------------------------------------
+// Pull form of the gather: each rank reads its peers' uint16 rows straight out of their memory
+// over NVLink and writes them, widened, into its own image: transfer and widening are one kernel,
+// nothing is staged, and all peers are read at the same time.  Readiness travels as sequence
+// numbers: after computing a group of slabs a rank stores the group's number into its slot of
+// every peer's flag array (signal kernel); the pull kernel of that group first waits, with a time
+// limit, until every peer's slot has reached the number.  The waiting side only ever waits for a
+// kernel that runs on ANOTHER GPU and that depends on nothing of the waiter's later work.
+struct PeerPtrs {
+  const uint16_t *wire[VRHI_GATHER_MAX_WORLD];  // indexed by rank; the caller's own entry is unused
+};
+struct PeerFlags {
+  uint32_t *flags[VRHI_GATHER_MAX_WORLD];
+};
+
+__global__ void gather_signal_kernel(PeerFlags peers, uint32_t n_peers, uint32_t slot, uint32_t seq) {
+  if (threadIdx.x < n_peers) {
+    __threadfence_system();  // this rank's rows (written by earlier kernels of the stream) before the number
+    *reinterpret_cast<volatile uint32_t *>(peers.flags[threadIdx.x] + slot) = seq;
+    __threadfence_system();
+  }
+}
+
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// The wait is a kernel of its own, one warp: a waiting kernel that held many thread slots could keep
+// this rank's own signal kernel (which its peers are waiting for) off the SMs.  Lane q polls slot q
+// of this rank's flag array; the verdict goes to `ok` for the copy kernel that follows in the stream.
+__global__ void gather_wait_kernel(const uint32_t *flags, uint32_t world, uint32_t rank, uint32_t seq, uint64_t wait_ns,
+                                   int32_t *status, uint32_t *ok) {
+  bool mine = true;
+  if (threadIdx.x < world && threadIdx.x != rank) {
+    const volatile uint32_t *f = flags + threadIdx.x;
+    const uint64_t t0 = global_ns();
+    while ((int32_t)(*f - seq) < 0) {  // sequence numbers compare modulo 2^32
+      if (global_ns() - t0 > wait_ns) { mine = false; break; }
+      __nanosleep(500);
+    }
+  }
+  const bool all = __all_sync(0xffffffffu, mine);
+  if (threadIdx.x == 0) {
+    if (!all) atomicCAS(status, 0, VRHI_ERR_TIMEOUT);
+    *ok = all ? 1u : 0u;
+    __threadfence();
+  }
+}
+
+constexpr int kPullRows = 4;  // rows in flight per thread: 64 bytes of remote loads outstanding
+
+__global__ void __launch_bounds__(256) gather_pull_u16_kernel(PeerPtrs peers, const uint32_t *ok, uint32_t *__restrict__ image,
+                                                              uint32_t width, uint32_t height, uint32_t chunk_rows, uint32_t world,
+                                                              uint32_t rank, uint32_t slab_first, uint32_t slab_stride, uint32_t total_rows) {
+  if (*reinterpret_cast<const volatile uint32_t *>(ok) == 0u) return;  // the wait gave up: copy nothing; the host finds VRHI_ERR_TIMEOUT
+  const uint32_t rows_per_slab = (world - 1) * chunk_rows;
+  const uint32_t v = blockIdx.x * 256u + threadIdx.x;
+  const bool col_ok = v * 8u < width;
+  for (uint32_t u0 = blockIdx.y; u0 < total_rows; u0 += gridDim.y * kPullRows) {
+    uint4 in[kPullRows];
+    size_t base[kPullRows];
+    bool ok[kPullRows];
+#pragma unroll
+    for (int k = 0; k < kPullRows; ++k) {
+      const uint32_t u = u0 + (uint32_t)k * gridDim.y;
+      ok[k] = false;
+      if (u < total_rows && col_ok) {
+        const uint32_t slab = u / rows_per_slab, rem = u - slab * rows_per_slab;
+        const uint32_t qq = rem / chunk_rows, rr = rem - qq * chunk_rows;
+        const uint32_t q = qq + (qq >= rank ? 1u : 0u);
+        const uint64_t row = ((uint64_t)(slab_first + slab * slab_stride) * world + q) * chunk_rows + rr;
+        if (row < height) {
+          ok[k] = true;
+          base[k] = (size_t)row * width;
+          in[k] = __ldcg(reinterpret_cast<const uint4 *>(peers.wire[q] + base[k]) + v);  // L2 only: never a stale L1 line
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < kPullRows; ++k) {
+      if (ok[k]) {
+        uint4 lo, hi;
+        lo.x = in[k].x & 0xffffu; lo.y = in[k].x >> 16; lo.z = in[k].y & 0xffffu; lo.w = in[k].y >> 16;
+        hi.x = in[k].z & 0xffffu; hi.y = in[k].z >> 16; hi.z = in[k].w & 0xffffu; hi.w = in[k].w >> 16;
+        uint4 *out = reinterpret_cast<uint4 *>(image + base[k]) + 2 * (size_t)v;
+        __stcs(out, lo);
+        __stcs(out + 1, hi);
+      }
+    }
+  }
+}
+
+static int read_gather(const void *params, size_t params_size, vrhi_gather_params *q) {
+  VRHI_TRY(read_params(params, params_size, q));
+  if (q->world < 2 || q->world > VRHI_GATHER_MAX_WORLD) return fail(VRHI_ERR_INVALID, "gather: world must be 2..%d, got %u", VRHI_GATHER_MAX_WORLD, q->world);
+  if (q->rank >= q->world) return fail(VRHI_ERR_INVALID, "gather: rank %u outside world %u", q->rank, q->world);
+  return VRHI_OK;
+}
+
+int launch_gather_signal(vrhi_stream_t *st, const ArgView *args, int n_args, const void *params, size_t params_size) {
+  vrhi_gather_params q;
+  VRHI_TRY(read_gather(params, params_size, &q));
+  if (n_args != (int)q.world - 1) return fail(VRHI_ERR_INVALID, "gather_signal takes the flag arrays of the %u peers, got %d arguments", q.world - 1, n_args);
+  PeerFlags pf{};
+  for (int k = 0; k < n_args; ++k) {
+    if (args[k].bytes < (uint64_t)q.world * 4) return fail(VRHI_ERR_SIZE, "gather_signal: flag array %d holds %llu bytes, %u needed", k, (unsigned long long)args[k].bytes, q.world * 4);
+    if (!writable(args[k])) return fail(VRHI_ERR_INVALID, "gather_signal: flag array %d is read-only", k);
+    pf.flags[k] = reinterpret_cast<uint32_t *>(args[k].ptr);
+  }
+  gather_signal_kernel<<<1, 32, 0, st->s>>>(pf, (uint32_t)n_args, q.rank, q.seq);
+  return post_launch(st, "gather_signal");
+}
+
+int launch_gather_pull_u16(vrhi_stream_t *st, const ArgView *args, int n_args, const void *params, size_t params_size) {
+  vrhi_gather_params q;
+  VRHI_TRY(read_gather(params, params_size, &q));
+  if (n_args != (int)q.world + 1) return fail(VRHI_ERR_INVALID, "gather_pull_u16 takes flags, image and the %u peers' wire images (%u arguments), got %d", q.world - 1, q.world + 1, n_args);
+  if (q.width == 0 || q.height == 0 || q.chunk_rows == 0) return fail(VRHI_ERR_SIZE, "gather_pull_u16: empty image or chunk");
+  if (q.width % 8 != 0) return fail(VRHI_ERR_UNSUPPORTED, "gather_pull_u16: the width must be a multiple of 8 pixels (16-byte loads)");
+  const uint64_t px = (uint64_t)q.width * q.height;
+  if (args[0].bytes < (uint64_t)q.world * 4) return fail(VRHI_ERR_SIZE, "gather_pull_u16: the flag array is too small");
+  if (!writable(args[1])) return fail(VRHI_ERR_INVALID, "gather_pull_u16: the image buffer is read-only (class %s)", vrhi_arg_class_name(args[1].buf_cls));
+  if (args[1].bytes < px * 4) return fail(VRHI_ERR_SIZE, "gather_pull_u16: the image view holds %llu bytes, %llu needed", (unsigned long long)args[1].bytes, (unsigned long long)(px * 4));
+  PeerPtrs pp{};
+  int k = 2;
+  for (uint32_t r = 0; r < q.world; ++r) {
+    if (r == q.rank) continue;
+    if (args[k].bytes < px * 2) return fail(VRHI_ERR_SIZE, "gather_pull_u16: the wire image of rank %u holds %llu bytes, %llu needed", r, (unsigned long long)args[k].bytes, (unsigned long long)(px * 2));
+    if ((uintptr_t)args[k].ptr % 16) return fail(VRHI_ERR_INVALID, "gather_pull_u16: the wire image of rank %u is not 16-byte aligned", r);
+    pp.wire[r] = reinterpret_cast<const uint16_t *>(args[k].ptr);
+    ++k;
+  }
+  if ((uintptr_t)args[1].ptr % 16) return fail(VRHI_ERR_INVALID, "gather_pull_u16: the image is not 16-byte aligned");
+  const uint64_t n_chunks = ((uint64_t)q.height + q.chunk_rows - 1) / q.chunk_rows;
+  const uint64_t n_slabs = (n_chunks + q.world - 1) / q.world;
+  const uint32_t stride = q.slab_stride ? q.slab_stride : 1u;
+  if (q.slab_count && (uint64_t)q.slab_first + (uint64_t)(q.slab_count - 1) * stride >= n_slabs) return fail(VRHI_ERR_SIZE, "gather_pull_u16: slabs beyond the image");
+  const uint64_t total_rows = (uint64_t)q.slab_count * (q.world - 1) * q.chunk_rows;
+  if (total_rows == 0) return VRHI_OK;
+  if (total_rows > 0xffffffffull) return fail(VRHI_ERR_UNSUPPORTED, "gather_pull_u16: too many rows");
+  uint32_t *ctrl = nullptr;
+  VRHI_TRY(stream_arena(st, 0, &ctrl, nullptr));
+  dim3 grid;
+  grid.x = (q.width / 8 + 255) / 256;
+  // enough blocks to keep ~64 bytes x 256 threads x 4 blocks per SM of remote loads in flight, no more
+  const uint64_t want_y = ((uint64_t)st->dev->prop.multiProcessorCount * 4 + grid.x - 1) / grid.x;
+  const uint64_t max_y = (total_rows + kPullRows - 1) / kPullRows;
+  grid.y = (unsigned)(want_y < max_y ? want_y : max_y);
+  const uint64_t wait_ns = (uint64_t)(q.wait_ms ? q.wait_ms : 2000u) * 1000000ull;
+  gather_wait_kernel<<<1, 32, 0, st->s>>>(reinterpret_cast<const uint32_t *>(args[0].ptr), q.world, q.rank, q.seq, wait_ns,
+                                          reinterpret_cast<int32_t *>(ctrl + CTRL_STATUS), ctrl + CTRL_WAIT_OK);
+  gather_pull_u16_kernel<<<grid, 256, 0, st->s>>>(pp, ctrl + CTRL_WAIT_OK, reinterpret_cast<uint32_t *>(args[1].ptr),
+                                                  q.width, q.height, q.chunk_rows, q.world, q.rank, q.slab_first, stride, (uint32_t)total_rows);
+  return post_launch(st, "gather_pull_u16", 2);
 }
 
 }  // namespace vrhi

@@ -77,6 +77,9 @@ static const OpDef kOps[] = {
     {"flat_color", "args: color(UNIFORM f32[3]), fragments(IMAGE f32[n][4]); params: vrhi_map_params", launch_flat_color},
     {"widen_rows_u16", "args: wire(u16 [height][width]), image(OUTPUT|IMAGE u32 [height][width]); params: vrhi_widen_params",
      launch_widen_rows_u16},
+    {"gather_signal", "args: the peers' flag arrays (u32[world]); params: vrhi_gather_params", launch_gather_signal},
+    {"gather_pull_u16", "args: flags(u32[world]), image(u32 [height][width]), the peers' wire images (u16 [height][width]) in rank order; params: vrhi_gather_params",
+     launch_gather_pull_u16},
 };
 static const int kNumOps = int(sizeof(kOps) / sizeof(kOps[0]));
 

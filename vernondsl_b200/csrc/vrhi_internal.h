@@ -55,7 +55,7 @@ namespace vrhi {
 
 constexpr size_t kCtrlBytes = 256;
 // control-word indices (uint32) inside the arena's control block
-enum { CTRL_STATUS = 0, CTRL_WORK0 = 1, CTRL_WORK1 = 2, CTRL_DONE = 3 };
+enum { CTRL_STATUS = 0, CTRL_WORK0 = 1, CTRL_WORK1 = 2, CTRL_DONE = 3, CTRL_WAIT_OK = 4 };
 
 int fail(int code, const char *fmt, ...) __attribute__((format(printf, 2, 3)));
 void clear_error();
@@ -112,6 +112,8 @@ int launch_fp32_probe(vrhi_stream_t *, const ArgView *, int, const void *, size_
 int launch_vertex_transform(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
 int launch_flat_color(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
 int launch_widen_rows_u16(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
+int launch_gather_signal(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
+int launch_gather_pull_u16(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
 
 // Copies a caller's parameter block into a zero-initialised struct of the current layout,
 // honouring the leading size field (older, shorter callers leave new fields zero).

@@ -78,13 +78,35 @@ def escape_time(stream: Stream, image: Buffer, params: L.EscapeParams, wire: Opt
 
 
 def widen_rows_u16(stream: Stream, wire: Buffer, image: Buffer, width: int, height: int, chunk_rows: int, world: int,
-                   skip_rank: int, slab_first: int, slab_count: int) -> None:
-    """Copy uint16 counts of the given slabs into the uint32 image, leaving out ``skip_rank``'s chunks."""
+                   skip_rank: int, slab_first: int, slab_count: int, slab_stride: int = 1) -> None:
+    """Copy uint16 counts of slabs ``slab_first + k*slab_stride`` (k < slab_count) into the uint32 image, leaving out
+    ``skip_rank``'s chunks."""
     p = L.WidenParams()
     p.size = C.sizeof(L.WidenParams)
     p.width, p.height, p.chunk_rows, p.world = int(width), int(height), int(chunk_rows), int(world)
-    p.skip_rank, p.slab_first, p.slab_count = int(skip_rank), int(slab_first), int(slab_count)
+    p.skip_rank, p.slab_first, p.slab_count, p.slab_stride = int(skip_rank), int(slab_first), int(slab_count), int(slab_stride)
     launch(stream, "widen_rows_u16", [wire.arg(), image.arg(L.IMAGE if image.arg_class == L.IMAGE else L.OUTPUT)], p)
+
+
+def gather_signal(stream: Stream, peer_flags: Sequence[Buffer], world: int, rank: int, seq: int) -> None:
+    """Store ``seq`` into slot ``rank`` of every peer's flag array: this rank's rows up to that number are ready."""
+    p = L.GatherParams()
+    p.size, p.world, p.rank, p.seq = C.sizeof(L.GatherParams), int(world), int(rank), int(seq) & 0xFFFFFFFF
+    launch(stream, "gather_signal", [f.arg(L.STORAGE_BUFFER) for f in peer_flags], p)
+
+
+def gather_pull_u16(stream: Stream, flags: Buffer, image: Buffer, peer_wires: Sequence[Buffer], width: int, height: int,
+                    chunk_rows: int, world: int, rank: int, slab_first: int, slab_count: int, seq: int, wait_ms: int = 0,
+                    slab_stride: int = 1) -> None:
+    """Wait (bounded) for every peer's flag to reach ``seq``, then read the peers' uint16 rows of the given slabs out
+    of their wire images and write them, widened, into ``image``.  ``peer_wires``: ranks in order, without ``rank``."""
+    p = L.GatherParams()
+    p.size = C.sizeof(L.GatherParams)
+    p.width, p.height, p.chunk_rows, p.world, p.rank = int(width), int(height), int(chunk_rows), int(world), int(rank)
+    p.slab_first, p.slab_count, p.seq, p.wait_ms = int(slab_first), int(slab_count), int(seq) & 0xFFFFFFFF, int(wait_ms)
+    p.slab_stride = int(slab_stride)
+    args = [flags.arg(), image.arg(L.IMAGE if image.arg_class == L.IMAGE else L.OUTPUT)] + [w.arg() for w in peer_wires]
+    launch(stream, "gather_pull_u16", args, p)
 
 
 # ------------------------------------------------------------------------------ maps ----------

@@ -53,7 +53,7 @@ def owner_of_row(plan: ImagePlan, row: int) -> int:
     return c % plan.world if plan.scheme == L.PART_CYCLIC else c
 
 
-def all_gather_image(image, plan: ImagePlan, group=None, async_op: bool = False, slab_range=None):
+def all_gather_image(image, plan: ImagePlan, group=None, async_op: bool = False, slab_range=None, slabs=None):
     """All-gather the row chunks of ``image`` (a [height, width] tensor holding this rank's chunks
     at their true rows) so that every rank ends with the whole image.
 
@@ -61,8 +61,8 @@ def all_gather_image(image, plan: ImagePlan, group=None, async_op: bool = False,
     [slab, rank, chunk_rows*width] already has rank r's data at [:, r, :], which is exactly the
     output layout of an all-gather of each slab.  Anything else falls back to one broadcast per
     chunk from its owner.  ``slab_range=(lo, hi)`` restricts an even cyclic gather to slabs lo..hi-1
-    (slab k holds chunks k*world .. k*world+world-1), so that the gather of finished slabs can overlap
-    the computation of later ones.  Returns the list of work handles when ``async_op``.
+    (slab k holds chunks k*world .. k*world+world-1), ``slabs=(first, count, stride)`` to slabs
+    first + k*stride, so that the gather of finished slabs can overlap the computation of later ones.  Returns the list of work handles when ``async_op``.
     """
     import torch.distributed as dist
 
@@ -74,19 +74,24 @@ def all_gather_image(image, plan: ImagePlan, group=None, async_op: bool = False,
     n_chunks = -(-height // p.chunk_rows)
     even = plan.scheme == L.PART_CYCLIC and height % p.chunk_rows == 0 and n_chunks % world == 0
     if even:
-        slabs = image.view(n_chunks // world, world, p.chunk_rows * width)
-        lo, hi = slab_range if slab_range is not None else (0, slabs.shape[0])
-        if image.is_cuda and hasattr(dist, "_coalescing_manager") and hi - lo > 1:
+        slab_view = image.view(n_chunks // world, world, p.chunk_rows * width)
+        if slabs is not None:
+            which = range(slabs[0], slabs[0] + slabs[1] * slabs[2], slabs[2])
+        else:
+            lo, hi = slab_range if slab_range is not None else (0, slab_view.shape[0])
+            which = range(lo, hi)
+        slabs = slab_view
+        if image.is_cuda and hasattr(dist, "_coalescing_manager") and len(which) > 1:
             # one NCCL group for all slabs: a single launch instead of one per slab
             with dist._coalescing_manager(group=group, device=image.device, async_ops=True) as cm:
-                for k in range(lo, hi):
+                for k in which:
                     dist.all_gather_into_tensor(slabs[k].view(-1), slabs[k, plan.rank], group=group)
             if async_op:
                 works.append(cm)
             else:
                 cm.wait()
         else:
-            for k in range(lo, hi):
+            for k in which:
                 w = dist.all_gather_into_tensor(slabs[k].view(-1), slabs[k, plan.rank], group=group, async_op=async_op)
                 if async_op:
                     works.append(w)
@@ -147,24 +152,25 @@ class PeerImageExchange:
         self.peers = {r: dev.open_ipc(handles[r], image.nbytes, L.IMAGE) for r in range(plan.world) if r != plan.rank}
         self._flag = torch.zeros(1, device=f"cuda:{dev.ordinal}")
 
-    def push(self, stream, slab_range=None) -> None:
-        """Enqueue the copies of this rank's chunks of slabs lo..hi-1 into every peer.  ``stream`` is one
-        stream, or a list with one stream per peer so that the pushes to different peers run on
-        different copy engines at the same time."""
-        lo, hi = slab_range if slab_range is not None else (0, self.n_slabs)
-        if hi <= lo:
+    def push(self, stream, slabs=None) -> None:
+        """Enqueue the copies of this rank's chunks of slabs ``first + k*stride`` (k < count) into every peer;
+        ``slabs`` = (first, count, stride), default all.  ``stream`` is one stream, or a list with one stream per
+        peer so that the pushes to different peers run on different copy engines at the same time."""
+        first, count, stride = slabs if slabs is not None else (0, self.n_slabs, 1)
+        if count <= 0:
             return
         world, rank = self.plan.world, self.plan.rank
-        offset = (lo * world + rank) * self.chunk_bytes
-        pitch = world * self.chunk_bytes
+        offset = (first * world + rank) * self.chunk_bytes
+        pitch = world * stride * self.chunk_bytes
         # start with the next rank so that, at any moment, the ranks write to different peers
         streams = stream if isinstance(stream, (list, tuple)) else [stream] * (world - 1)
         for step in range(1, world):
             peer = self.peers[(rank + step) % world]
-            self.image.copy_2d_to(peer, offset, pitch, offset, pitch, self.chunk_bytes, hi - lo, streams[step - 1])
+            self.image.copy_2d_to(peer, offset, pitch, offset, pitch, self.chunk_bytes, count, streams[step - 1])
 
     def finish(self, torch_stream) -> None:
-        """Stream-ordered completion: after this, all ranks' pushes are visible in this rank's image."""
+        """Stream-ordered completion: after this, every rank's pushes enqueued before its matching call
+        are visible in this rank's image."""
         import torch
         import torch.distributed as dist
 
@@ -194,20 +200,88 @@ class WireImageExchange:
         self.peer = PeerImageExchange(dev, self.wire, plan, self.width * 2, group)
         self.n_slabs = self.peer.n_slabs
 
-    def push(self, stream, slab_range=None) -> None:
-        self.peer.push(stream, slab_range)
+    def push(self, stream, slabs=None) -> None:
+        self.peer.push(stream, slabs)
 
-    def finish(self, torch_stream, stream, slab_range=None) -> None:
+    def finish(self, torch_stream, stream, slabs=None) -> None:
         """``torch_stream`` and ``stream`` are the same CUDA stream (torch's handle for the collective,
-        the library's for the kernel).  After this, stream-ordered, the uint32 image holds every rank's
-        rows of ``slab_range`` (default: all)."""
-        from . import ops
-
+        the library's for the kernel), ordered behind this rank's pushes of ``slabs`` = (first, count,
+        stride), default all.  After this, stream-ordered, the uint32 image holds every rank's rows of
+        those slabs."""
         self.peer.finish(torch_stream)
-        lo, hi = slab_range if slab_range is not None else (0, self.n_slabs)
+        first, count, stride = slabs if slabs is not None else (0, self.n_slabs, 1)
         p = self.plan
-        ops.widen_rows_u16(stream, self.wire, self.image, self.width, p.height, p.part.chunk_rows, p.world, p.rank, lo, hi - lo)
+        ops.widen_rows_u16(stream, self.wire, self.image, self.width, p.height, p.part.chunk_rows, p.world, p.rank, first, count, stride)
 
     def close(self) -> None:
         self.peer.close()
         self.wire.close()
+
+
+class PullImageExchange:
+    """The gather in pull form: every rank reads its peers' uint16 rows out of their memory over
+    NVLink and widens them into its own uint32 image in the same kernel (``gather_pull_u16``).
+
+    Nothing is pushed and no collective runs: after computing a group of slabs (with
+    ``ops.escape_time(..., wire=exchange.wire)``) a rank calls ``signal``, which stores the group's
+    sequence number into its slot of every peer's flag array; ``pull`` waits (bounded, on the
+    device) until every peer's slot has reached that number and then copies.  Two wire images
+    alternate from step to step so that a rank never overwrites rows a slower peer is still reading.
+
+    ``groups`` is the number of signal/pull pairs per step and must be the same on every rank.
+    """
+
+    def __init__(self, dev, image, plan: ImagePlan, width: int, groups: int, group=None, wait_ms: int = 2000):
+        import torch.distributed as dist
+
+        p = plan.part
+        n_chunks = -(-plan.height // p.chunk_rows)
+        if not (plan.scheme == L.PART_CYCLIC and plan.height % p.chunk_rows == 0 and n_chunks % plan.world == 0):
+            raise ValueError("the pull exchange needs a cyclic plan whose chunk count divides evenly")
+        if not 2 <= plan.world <= L.GATHER_MAX_WORLD:
+            raise ValueError(f"the pull exchange serves 2..{L.GATHER_MAX_WORLD} ranks")
+        if width % 8:
+            raise ValueError("the pull exchange needs a width that is a multiple of 8 pixels")
+        self.dev, self.image, self.plan, self.width = dev, image, plan, int(width)
+        self.groups, self.wait_ms = int(groups), int(wait_ms)
+        self.n_slabs = n_chunks // plan.world
+        self.wires = [dev.empty((plan.height, self.width), np.uint16, L.IMAGE) for _ in range(2)]
+        self.flags = dev.empty((1 << 19,), np.uint32, L.STORAGE_BUFFER)   # its own 2 MiB allocation; world slots are used
+        self.flags.fill(0)
+        dev.synchronize()
+        mine = (self.wires[0].ipc_handle(), self.wires[1].ipc_handle(), self.flags.ipc_handle())
+        handles = [None] * plan.world
+        dist.all_gather_object(handles, mine, group=group)
+        self.peer_wires = [[dev.open_ipc(handles[r][b], self.wires[b].nbytes, L.STORAGE_BUFFER) for r in range(plan.world) if r != plan.rank]
+                           for b in range(2)]
+        self.peer_flags = [dev.open_ipc(handles[r][2], self.flags.nbytes, L.STORAGE_BUFFER) for r in range(plan.world) if r != plan.rank]
+        self.step = 0
+        dist.barrier(group=group)   # every rank has zeroed its flags before anyone signals
+
+    @property
+    def wire(self):
+        """The wire image this step's kernels write into."""
+        return self.wires[self.step & 1]
+
+    def next_step(self) -> None:
+        self.step += 1
+
+    def _seq(self, g: int) -> int:
+        return self.step * self.groups + g + 1
+
+    def signal(self, stream, g: int) -> None:
+        """Enqueue on ``stream`` (behind the kernels that computed group ``g``) the ready mark for the peers."""
+        ops.gather_signal(stream, self.peer_flags, self.plan.world, self.plan.rank, self._seq(g))
+
+    def pull(self, stream, g: int, slabs) -> None:
+        first, count, stride = slabs
+        p = self.plan
+        ops.gather_pull_u16(stream, self.flags, self.image, self.peer_wires[self.step & 1], self.width, p.height, p.part.chunk_rows,
+                            p.world, p.rank, first, count, self._seq(g), self.wait_ms, stride)
+
+    def close(self) -> None:
+        for b in self.peer_flags + self.peer_wires[0] + self.peer_wires[1]:
+            b.close()
+        self.peer_flags, self.peer_wires = [], [[], []]
+        for b in self.wires + [self.flags]:
+            b.close()

@@ -418,7 +418,10 @@ def main():
     # With N > 1 a step is pipelined: the rank's chunks are computed in GROUPS launches, and the
     # in-place all-gather of the slabs a launch completed runs on a second stream while the next
     # launch computes.  The step ends when the last gather has finished.
-    GROUPS = int(os.environ.get("VRHI_BENCH_GROUPS", "4"))  # launches per step; finished slabs are exchanged while the next launch computes
+    # launches per step; finished slabs are exchanged while the next launch computes.  Every extra launch costs
+    # about 60 us of ramp-up and drain, every group fewer lengthens the last, exposed push: 2 groups measured
+    # best on 2 GPUs, 4 on 4 and 8.
+    GROUPS = int(os.environ.get("VRHI_BENCH_GROUPS", "2" if world == 2 else "4"))
     # Group g takes slabs g, g+GROUPS, g+2*GROUPS, ...: every group is a thin comb over the whole image, so the
     # groups cost the same although the rows near the set cost far more than the rows at the edges.
     exchange = None

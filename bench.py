@@ -24,6 +24,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import copy
 import os
 import subprocess
 import sys
@@ -428,7 +429,6 @@ def main():
     n_slabs = plan.part.chunk_count
     group_params, group_slabs = [], []
     if world > 1:
-        import copy
         for gidx in range(GROUPS):
             count = (n_slabs - gidx + GROUPS - 1) // GROUPS if gidx < n_slabs else 0
             if count <= 0:
@@ -550,9 +550,20 @@ def main():
         sampler.start()
     for _ in range(args.warmup):
         step()
-    launches0 = st.launch_count()
+    def count_launches():
+        # kernels of this library on every stream a step uses (compute, and the arrival or pull streams)
+        n = st.launch_count()
+        if world > 1:
+            n += comm_st.launch_count()
+            if pushing16:
+                n += arrive_st.launch_count()
+            if pulling:
+                n += sig_st.launch_count()
+        return n
+
+    launches0 = count_launches()
     total_ms = timed(step, args.steps)
-    launches = st.launch_count() - launches0
+    launches = count_launches() - launches0
     if world > 1 and os.environ.get("VRHI_BENCH_TRACE"):
         barrier()
         TRACING[0] = True
@@ -654,6 +665,40 @@ def main():
     d2h = sum(n for _, n in chunks) * W * 4
     host.close()
 
+    # The same end-to-end step with the counts delivered as uint16 (VRHI_OUT_COUNT_U16; max_iter = 4096 fits): the
+    # step is bound by the device-to-host link, so half the bytes is close to twice the rate.  Extra line, N = 1 only.
+    e2e_u16 = None
+    if world == 1:
+        image16 = dev.empty((H, W), np.uint16, L.IMAGE)
+        host16 = vd.PinnedArray((H, W), np.uint16)
+        groups16 = []
+        for gp, spans in e2e_groups:
+            gp16 = copy.copy(gp)
+            gp16.output = L.OUT_COUNT_U16
+            groups16.append((gp16, spans))
+
+        def e2e16_step():
+            for gp16, spans in groups16:
+                ops.escape_time(st, image16, gp16)
+                ev = torch.cuda.Event()
+                ev.record(tstream)
+                copy_tstream.wait_event(ev)
+                for r0, n, dst_row in spans:
+                    image16.download(host16.array[dst_row:dst_row + n], offset=r0 * W * 2, stream=copy_st)
+            copy_st.synchronize()
+
+        for _ in range(2):
+            e2e16_step()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e16_step()
+        secs = time.perf_counter() - t0
+        ok16 = bool(int(host16.array.astype(np.uint64).sum()) == total_iters)
+        e2e_u16 = {"value": total_iters * e2e_steps / secs / 1e9, "unit": "Gpixel-iters/s", "d2h_bytes_per_step": H * W * 2,
+                   "sum_of_counts_matches": ok16, "note": "counts delivered as uint16 instead of uint32; otherwise the e2e step"}
+        host16.close()
+        image16.close()
+
     if rank == 0:
         achieved = OPS_PER_ITER * total_iters / (compute_ms * 1e-3) / 1e9 / world  # per GPU
         line = {
@@ -675,6 +720,8 @@ def main():
                     "note": "kernel + download of this rank's rows into pinned host memory; uniforms travel as kernel parameters"},
             "gpu_launches": int(launches), "clocks": clocks, "fast_mode": fast_mode,
         }
+        if e2e_u16 is not None:
+            line["e2e_uint16_result"] = e2e_u16
         if world == 1 and not args.no_cpu_baseline:
             import oracle
 

@@ -1,0 +1,114 @@
+"""One rank of the multi-GPU gather test (launched by test_multi_gpu.py through torch.distributed.run).
+
+Every rank computes its comb of chunks of a small Julia image, the image is gathered with each
+exchange in turn, and every rank compares its whole image with the CPU oracle."""
+import os
+import sys
+
+import numpy as np
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def main() -> int:
+    import torch
+    import torch.distributed as dist
+
+    import oracle
+    import vernondsl_b200 as vd
+    from vernondsl_b200 import _lib as L
+    from vernondsl_b200 import ops, partition
+
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+    dev = vd.Device(local)
+    W, chunk_rows, slabs, G = 512, 16, 6, 3
+    H = chunk_rows * world * slabs
+    max_iter = 600
+    dx, dy = ops.grid_steps(-1.6, 1.6, -1.6, 1.6, W, H)
+    want, _ = oracle.escape_time(oracle.JULIA, W, H, -1.6, -1.6, dx, dy, -0.8, 0.156, max_iter)
+    plan = partition.plan_image(H, world, rank, L.PART_CYCLIC, chunk_rows)
+    tstream, cstream = torch.cuda.Stream(device=local), torch.cuda.Stream(device=local)
+    st, cst = dev.wrap_stream(tstream.cuda_stream), dev.wrap_stream(cstream.cuda_stream)
+    image = dev.empty((H, W), np.uint32, L.IMAGE)
+    image_t = image.as_tensor(np.uint32, (H, W))
+    base = ops.escape_params(L.JULIA, W, H, -1.6, -1.6, dx, dy, cr=-0.8, ci=0.156, max_iter=max_iter, partition=plan.part)
+    failures = []
+
+    def groups():
+        import copy
+        for g in range(G):
+            p = copy.copy(base)
+            p.chunk_first = plan.part.chunk_first + g * plan.part.chunk_step
+            p.chunk_step = plan.part.chunk_step * G
+            p.chunk_count = (slabs - g + G - 1) // G
+            yield g, p, (g, p.chunk_count, G)
+
+    def check(name):
+        torch.cuda.synchronize()
+        st.check()
+        cst.check()
+        got = image.download(dtype=np.uint32, shape=(H, W))
+        if not np.array_equal(got, want):
+            failures.append(f"{name}: {int((got != want).sum())} pixels differ on rank {rank}")
+        image.fill(0xEE)
+        dev.synchronize()
+        dist.barrier()
+
+    # NCCL all-gather, comb by comb
+    for g, p, comb in groups():
+        ops.escape_time(st, image, p)
+        cstream.wait_stream(tstream)
+        with torch.cuda.stream(cstream):
+            partition.all_gather_image(image_t, plan, slabs=comb)
+    check("nccl")
+
+    # uint32 rows pushed by the copy engines
+    ex = partition.PeerImageExchange(dev, image, plan, W * 4)
+    for g, p, comb in groups():
+        ops.escape_time(st, image, p)
+        cstream.wait_stream(tstream)
+        ex.push(cst, comb)
+    ex.finish(cstream)
+    check("p2p")
+    ex.close()
+
+    # uint16 on the wire, widened on arrival; two steps, so that stale wire rows would show
+    ex = partition.WireImageExchange(dev, image, plan, W)
+    for step in range(2):
+        ex.wire.fill(0xDD)
+        dev.synchronize()
+        dist.barrier()
+        for g, p, comb in groups():
+            ops.escape_time(st, image, p, wire=ex.wire)
+            cstream.wait_stream(tstream)
+            ex.push(cst, comb)
+            ex.finish(cstream, cst, comb)
+        check(f"p2p16 step {step}")
+    ex.close()
+
+    # pull form: signals and bounded waits, two wire images alternating
+    ex = partition.PullImageExchange(dev, image, plan, W, groups=G, wait_ms=5000)
+    for step in range(3):
+        for g, p, comb in groups():
+            ops.escape_time(st, image, p, wire=ex.wire)
+            ex.signal(st, g)
+            ex.pull(cst, g, comb)
+        torch.cuda.synchronize()
+        ex.next_step()
+        check(f"pull16 step {step}")
+    ex.close()
+
+    dist.barrier()
+    dist.destroy_process_group()
+    if failures:
+        print("\n".join(failures), file=sys.stderr)
+        return 1
+    if rank == 0:
+        print("EXCHANGES_OK")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,31 @@
+"""GPU, two or more devices: every form of the image gather (NCCL all-gather, peer pushes of uint32
+rows, uint16 on the wire with widening, the pull form with signals and bounded waits) must leave the
+whole image, bit-exact against the CPU oracle, on every rank.  Skipped on a single-GPU box."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _gpu_count() -> int:
+    import torch
+
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_every_exchange_rebuilds_the_image_on_every_rank(world):
+    if _gpu_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    port = 29600 + (os.getpid() % 300) + world
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(HERE, "exchange_worker.py")]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
+    assert out.returncode == 0, out.stderr[-3000:]
+    assert "EXCHANGES_OK" in out.stdout

@@ -189,7 +189,28 @@ def other_workloads(dev, st, torch, hbm_peak, peak_kind, fp32_peak):
                 "gpixel_iters_per_s": rate / 1e9,
                 "roofline": {"bound": "fp32", "achieved": OPS_PER_ITER * rate / 1e9, "peak": fp32_peak, "unit": "Gop/s",
                              "frac": OPS_PER_ITER * rate / 1e9 / fp32_peak}})
-    img.close()
+    # The same frames into a ring of 4 images from two streams in turn, recorded once: the first blocks of a
+    # frame start while the last blocks of the frame before drain (a frame is far too short to fill the GPU to its end).
+    side = dev.stream()
+    ring = [img] + [dev.empty((H, W), np.uint32, L.IMAGE) for _ in range(3)]
+    for s_ in (st, side):
+        ops.escape_time(s_, ring[1], p)
+        s_.check()
+    with st.record() as seq:
+        st.fork_recording(side)
+        for k in range(48):
+            ops.escape_time(st if k % 2 == 0 else side, ring[k % 4], p)
+    ms2 = time_launches(dev, st, lambda: seq.launch(), 5) / 48
+    st.check()
+    ok = all(int(r.as_tensor(np.uint32, (H, W)).sum(dtype=torch.int64).item()) == total for r in ring)
+    rate2 = total / (ms2 * 1e-3)
+    out.append({"workload": "mandelbrot 1920x1080 max_iter=256 u32 exact, 48 frames as one recorded sequence on two alternating streams, ring of 4 images",
+                "kernel": "escape_time", "ms": ms2, "gpixel_iters_per_s": rate2 / 1e9, "sum_of_counts_matches_every_frame": ok,
+                "roofline": {"bound": "fp32", "achieved": OPS_PER_ITER * rate2 / 1e9, "peak": fp32_peak, "unit": "Gop/s",
+                             "frac": OPS_PER_ITER * rate2 / 1e9 / fp32_peak}})
+    seq.close()
+    for b in ring:
+        b.close()
 
     # The reference program's own frame (fractal.py:7-25): 640 x 320 binary32 colour, |z| < 20, at most 50
     # steps, a new uniform every frame (fractal.py:30-31).  Such a frame costs a few microseconds of
@@ -202,19 +223,26 @@ def other_workloads(dev, st, torch, hbm_peak, peak_kind, fp32_peak):
                                  test=L.TEST_NORM_GE, bound=20.0, output=L.OUT_COLOR_F32, color_scale=0.02)
                for k in range(frames)]
 
-    def run_frames():
+    def run_frames(streams):
         for k, fp in enumerate(fparams):
-            ops.escape_time(st, ring[k % 4], fp)
+            ops.escape_time(streams[k % len(streams)], ring[k % 4], fp)
 
-    ms_plain = time_launches(dev, st, run_frames, 5) / frames
+    ms_plain = time_launches(dev, st, lambda: run_frames([st]), 5) / frames
     with st.record() as seq:
-        run_frames()
+        run_frames([st])
     ms_seq = time_launches(dev, st, lambda: seq.launch(), 5) / frames
+    with st.record() as seq2:
+        st.fork_recording(side)
+        run_frames([st, side])
+    ms_seq2 = time_launches(dev, st, lambda: seq2.launch(), 5) / frames
     out.append({"workload": f"fractal.py frame 640x320 f32 colour, max_iter=50, {frames} frames with a new uniform each, ring of 4 device frames",
                 "kernel": "escape_time", "ms_per_frame_plain_launches": ms_plain, "ms_per_frame_recorded_sequence": ms_seq,
-                "frames_per_s_recorded_sequence": 1e3 / ms_seq,
-                "note": "launch-bound: one CUDA graph submission for all frames against one launch call per frame"})
+                "ms_per_frame_recorded_two_streams": ms_seq2, "frames_per_s_recorded_two_streams": 1e3 / ms_seq2,
+                "note": "launch-bound: one CUDA graph submission for all frames against one launch call per frame; with two "
+                        "alternating streams consecutive frames overlap"})
     seq.close()
+    seq2.close()
+    side.close()
     for b in ring:
         b.close()
 
@@ -419,10 +447,9 @@ def main():
     # With N > 1 a step is pipelined: the rank's chunks are computed in GROUPS launches, and the
     # in-place all-gather of the slabs a launch completed runs on a second stream while the next
     # launch computes.  The step ends when the last gather has finished.
-    # launches per step; finished slabs are exchanged while the next launch computes.  Every extra launch costs
-    # about 60 us of ramp-up and drain, every group fewer lengthens the last, exposed push: 2 groups measured
-    # best on 2 GPUs, 4 on 4 and 8.
-    GROUPS = int(os.environ.get("VRHI_BENCH_GROUPS", "2" if world == 2 else "4"))
+    # launches per step; finished slabs are exchanged while the next launch computes.  More groups shorten the last,
+    # exposed push; every launch adds ramp-up and drain, most of which the two alternating compute streams hide.
+    GROUPS = int(os.environ.get("VRHI_BENCH_GROUPS", "4"))
     # Group g takes slabs g, g+GROUPS, g+2*GROUPS, ...: every group is a thin comb over the whole image, so the
     # groups cost the same although the rows near the set cost far more than the rows at the edges.
     exchange = None
@@ -457,6 +484,10 @@ def main():
             except Exception as exc:  # no peer mapping on this box: fall back to the NCCL gather
                 print(f"peer exchange unavailable ({exc}); using the NCCL all-gather", file=sys.stderr)
 
+    TWO_COMPUTE_STREAMS = world > 1 and os.environ.get("VRHI_BENCH_COMPUTE_STREAMS", "2") == "2"
+    if TWO_COMPUTE_STREAMS:
+        tstream2 = torch.cuda.Stream(device=local)
+        st2 = dev.wrap_stream(tstream2.cuda_stream)
     pulling = isinstance(exchange, partition.PullImageExchange)
     pushing16 = isinstance(exchange, partition.WireImageExchange)
     trace = []   # (label, event) of one extra, untimed step when VRHI_BENCH_TRACE is set: where a step's time goes
@@ -475,11 +506,16 @@ def main():
         works = []
         mark("start", tstream)
         wire = exchange.wire if (pulling or pushing16) else None
+        if TWO_COMPUTE_STREAMS:
+            tstream2.wait_stream(tstream)
         for gi, (gp, slabs) in enumerate(zip(group_params, group_slabs)):
-            ops.escape_time(st, image, gp, wire=wire)
-            mark(f"computed {gi}", tstream)
+            # launches alternate between two streams: the first blocks of a group start while the last blocks of
+            # the group before drain (each launch otherwise pays ~60 us of ramp-up and drain by itself)
+            cs_t, cs = (tstream2, st2) if (TWO_COMPUTE_STREAMS and gi % 2) else (tstream, st)
+            ops.escape_time(cs, image, gp, wire=wire)
+            mark(f"computed {gi}", cs_t)
             ev = torch.cuda.Event()
-            ev.record(tstream)
+            ev.record(cs_t)
             comm_stream.wait_event(ev)
             if pulling:
                 # tell the peers this group is ready (own stream: the next group's kernel is not held up), then
@@ -503,6 +539,8 @@ def main():
             else:
                 with torch.cuda.stream(comm_stream):
                     works += partition.all_gather_image(image_t, plan, async_op=True, slabs=slabs)
+        if TWO_COMPUTE_STREAMS:
+            tstream.wait_stream(tstream2)
         if pulling:
             tstream.wait_stream(sig_stream)
             tstream.wait_stream(comm_stream)
@@ -555,6 +593,8 @@ def main():
         n = st.launch_count()
         if world > 1:
             n += comm_st.launch_count()
+            if TWO_COMPUTE_STREAMS:
+                n += st2.launch_count()
             if pushing16:
                 n += arrive_st.launch_count()
             if pulling:

@@ -176,6 +176,12 @@ VRHI_API int vrhi_stream_wait_event(vrhi_stream stream, vrhi_event event);
  * synchronisation are not recordable.
  * Reference counterpart: none; fractal.py leaves launching to its runtime. */
 VRHI_API int vrhi_sequence_begin(vrhi_stream stream);
+/* Draw a second stream into the recording of `stream`: what is launched on `side` from here on is
+ * recorded too, ordered behind everything recorded on `stream` so far and otherwise free to run
+ * beside it (frames k and k+1 of a frame loop on alternating streams overlap: the last blocks of
+ * one frame drain while the first of the next start).  At most 4 side streams; they rejoin at
+ * vrhi_sequence_end, which must be called on `stream`. */
+VRHI_API int vrhi_sequence_fork(vrhi_stream stream, vrhi_stream side);
 VRHI_API int vrhi_sequence_end(vrhi_stream stream, vrhi_sequence *inout_seq);
 VRHI_API int vrhi_sequence_launch(vrhi_sequence seq, vrhi_stream stream);
 /* kernels per replay, times the sequence was re-targeted in place, times it was rebuilt */

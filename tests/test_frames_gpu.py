@@ -123,3 +123,40 @@ def test_recording_refuses_an_operator_whose_scratch_does_not_exist_yet():
     want, _ = oracle.escape_time(oracle.MANDELBROT, 64, 64, -2.5, -1.0, np.float32(3.5 / 64), np.float32(2.0 / 64), max_iter=128)
     assert np.array_equal(img.download(dtype=np.uint32, shape=(64, 64)), want)
     st.close()
+
+
+def test_a_recording_can_span_two_streams():
+    """Frames of a loop go to two streams in turn inside one recording; every frame must still be right,
+    and launching on a side stream that was not drawn into the recording must fail loudly."""
+    dev = vd.Device(0)
+    st, side, stray = dev.stream(), dev.stream(), dev.stream()
+    W, H, N = 640, 360, 200
+    dx, dy = ops.grid_steps(-2.5, 1.0, -1.0, 1.0, W, H)
+    want, _ = oracle.escape_time(oracle.MANDELBROT, W, H, -2.5, -1.0, dx, dy, max_iter=N)
+    ring = [dev.empty((H, W), np.uint32, L.IMAGE) for _ in range(4)]
+    p = ops.escape_params(L.MANDELBROT, W, H, -2.5, -1.0, dx, dy, max_iter=N)
+    for s in (st, side):
+        ops.escape_time(s, ring[0], p)       # sizes each stream's scratch
+        s.check()
+    for b in ring:
+        b.fill(0, stream=st)
+    st.check()
+    with st.record() as seq:
+        st.fork_recording(side)
+        with pytest.raises(vd.VrhiError):
+            st.fork_recording(side)           # already part of the recording
+        for k in range(8):
+            ops.escape_time(st if k % 2 == 0 else side, ring[k % 4], p)
+    assert seq.stats()["kernels"] == 8
+    assert not np.any(ring[1].download(dtype=np.uint32, shape=(H, W))), "recording must not execute"
+    before = st.launch_count(), side.launch_count()
+    seq.launch()
+    st.check()
+    assert (st.launch_count() - before[0], side.launch_count() - before[1]) == (8, 0)
+    for b in ring:
+        assert np.array_equal(b.download(dtype=np.uint32, shape=(H, W)), want)
+    with pytest.raises(vd.VrhiError):
+        stray.fork_recording(side)            # `stray` is not recording
+    seq.close()
+    for s in (st, side, stray):
+        s.close()

@@ -162,6 +162,7 @@ PROTOTYPES = {
     "vrhi_event_elapsed_ms": [_vp, _vp, _P(C.c_float)],
     "vrhi_stream_wait_event": [_vp, _vp],
     "vrhi_sequence_begin": [_vp],
+    "vrhi_sequence_fork": [_vp, _vp],
     "vrhi_sequence_end": [_vp, _P(_vp)],
     "vrhi_sequence_launch": [_vp, _vp],
     "vrhi_sequence_stats": [_vp, _P(C.c_uint64), _P(C.c_uint64), _P(C.c_uint64)],

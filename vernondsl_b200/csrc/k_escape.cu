@@ -357,6 +357,10 @@ static int launch_regroup_pinned(Kern kern, int grid, int per_sm, vrhi_stream_t 
   const size_t optin = st->dev->prop.sharedMemPerBlockOptin;
   if (total > optin) total = optin;
   size_t dyn = total > fixed ? total - fixed : 0;
+  // Small images (2 blocks per SM) are short launches, usually frames of a sequence: there the next
+  // frame's blocks should move in while this frame's last ones drain (65 -> 41 us per 1080p frame
+  // with two alternating streams), and a few tens of microseconds cannot go far out of balance.
+  if (per_sm < 4) dyn = 0;
   if (const char *e = getenv("VRHI_ESCAPE_PIN")) {  // tuning aid: 0 launches without the padding
     if (atoi(e) == 0) dyn = 0;
   }

@@ -441,6 +441,7 @@ int vrhi_stream_destroy(vrhi_stream stream) {
     cudaStreamSynchronize(stream->s);
     cudaFree(stream->arena);
   }
+  if (stream->fork_event) cudaEventDestroy(stream->fork_event);
   if (stream->owned) {
     cudaError_t e = cudaStreamDestroy(stream->s);
     if (e != cudaSuccess) rc = fail(VRHI_ERR_CUDA, "cudaStreamDestroy failed: %s", cudaGetErrorString(e));
@@ -531,13 +532,45 @@ int vrhi_sequence_begin(vrhi_stream stream) {
   return VRHI_OK;
 }
 
+int vrhi_sequence_fork(vrhi_stream stream, vrhi_stream side) {
+  if (!stream || !side) return fail(VRHI_ERR_INVALID, "NULL argument");
+  if (!stream->recording || stream->record_main) return fail(VRHI_ERR_INVALID, "fork needs the stream on which the recording began");
+  if (side == stream || side->dev != stream->dev) return fail(VRHI_ERR_INVALID, "the side stream must be another stream of the same device");
+  if (side->recording) return fail(VRHI_ERR_INVALID, "the side stream is already recording");
+  if (stream->n_record_sides >= 4) return fail(VRHI_ERR_UNSUPPORTED, "at most 4 side streams per recording");
+  VRHI_TRY(set_device(stream->dev));
+  if (!stream->fork_event) VRHI_CUDA(cudaEventCreateWithFlags(&stream->fork_event, cudaEventDisableTiming));
+  VRHI_CUDA(cudaEventRecord(stream->fork_event, stream->s));
+  VRHI_CUDA(cudaStreamWaitEvent(side->s, stream->fork_event, 0));  // the side stream joins the capture here
+  side->recording = true;
+  side->record_main = stream;
+  side->record_mark = side->launches;
+  stream->record_sides[stream->n_record_sides++] = side;
+  return VRHI_OK;
+}
+
 int vrhi_sequence_end(vrhi_stream stream, vrhi_sequence *inout_seq) {
   if (!stream || !inout_seq) return fail(VRHI_ERR_INVALID, "NULL argument");
   if (!stream->recording) return fail(VRHI_ERR_INVALID, "the stream is not recording");
+  if (stream->record_main) return fail(VRHI_ERR_INVALID, "end the recording on the stream it began on");
   VRHI_TRY(set_device(stream->dev));
   stream->recording = false;
-  const uint64_t kernels = stream->launches - stream->record_mark;
+  uint64_t kernels = stream->launches - stream->record_mark;
   stream->launches = stream->record_mark;  // nothing ran
+  for (int k = 0; k < stream->n_record_sides; ++k) {
+    vrhi_stream_t *side = stream->record_sides[k];
+    // rejoin: the recording ends only after everything recorded on the side stream
+    if (!side->fork_event) cudaEventCreateWithFlags(&side->fork_event, cudaEventDisableTiming);
+    if (side->fork_event) {
+      cudaEventRecord(side->fork_event, side->s);
+      cudaStreamWaitEvent(stream->s, side->fork_event, 0);
+    }
+    kernels += side->launches - side->record_mark;
+    side->launches = side->record_mark;
+    side->recording = false;
+    side->record_main = nullptr;
+  }
+  stream->n_record_sides = 0;
   cudaGraph_t g = nullptr;
   cudaError_t e = cudaStreamEndCapture(stream->s, &g);
   if (e != cudaSuccess || !g) {

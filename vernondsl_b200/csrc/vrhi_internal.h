@@ -8,6 +8,8 @@
 #include <cstdio>
 #include <string>
 
+struct vrhi_stream_t;
+
 #include "vrhi.h"
 
 struct vrhi_device_t {
@@ -38,6 +40,10 @@ struct vrhi_stream_t {
   uint64_t launches;
   uint64_t record_mark;  // value of `launches` when recording began
   bool recording;
+  vrhi_stream_t *record_main;  // side stream of a recording: the stream that owns it
+  vrhi_stream_t *record_sides[4];
+  int n_record_sides;
+  cudaEvent_t fork_event;      // created on first use, reused
 };
 
 struct vrhi_sequence_t {

@@ -644,11 +644,18 @@ class FrameLoop:
     again with other uniforms re-targets the existing recording in place.
     """
 
-    def __init__(self, kern: "Kernel", target: Field, ring: int = 4):
+    def __init__(self, kern: "Kernel", target: Field, ring: int = 4, streams: int = 2):
         if ring < 1:
             raise ValueError("the ring needs at least one frame")
+        if not 1 <= streams <= 4:
+            raise ValueError("1..4 streams")
+        while ring % streams:       # frames that share a ring slot must share a stream, or their order is lost
+            streams -= 1
         dev, st = _runtime()
         self.kernel, self.target, self.stream = kern, target, st
+        # frames go to the streams in turn: consecutive frames write different ring slots, so the next
+        # frame's first blocks may start while the last blocks of this one drain
+        self.streams: List[Stream] = [st] + [dev.stream() for _ in range(streams - 1)]
         self.ring: List[Buffer] = [target.buffer] + [dev.empty(target.shape, target.dtype, L.IMAGE) for _ in range(ring - 1)]
         self.seq = None
         self.frames = 0
@@ -660,15 +667,23 @@ class FrameLoop:
         home = self.target.buffer
         try:
             if self.seq is None:
-                self.kernel(*uniforms[0])  # sizes the operator's stream scratch: nothing may allocate while recording
+                for s in self.streams:      # sizes the operator's scratch on every stream: nothing may allocate while recording
+                    _state["stream"] = s
+                    self.kernel(*uniforms[0])
+                    s.check()
+            n_streams = min(len(self.streams), len(uniforms))
             with self.stream.record(self.seq) as seq:
+                for s in self.streams[1:n_streams]:
+                    self.stream.fork_recording(s)
                 for k, u in enumerate(uniforms):
                     self.target.buffer = self.ring[k % len(self.ring)]
+                    _state["stream"] = self.streams[k % n_streams]
                     self.kernel(*u)
             self.seq = seq
             self.frames = len(uniforms)
         finally:
             self.target.buffer = home
+            _state["stream"] = self.stream
 
     def play(self) -> None:
         if self.seq is None:
@@ -689,3 +704,6 @@ class FrameLoop:
         for b in self.ring[1:]:
             b.close()
         self.ring = self.ring[:1]
+        for s in self.streams[1:]:
+            s.close()
+        self.streams = self.streams[:1]

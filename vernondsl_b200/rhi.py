@@ -224,6 +224,11 @@ class Stream:
         one submission.  Passing an existing sequence re-targets it in place."""
         return _Recording(self, into)
 
+    def fork_recording(self, side: "Stream") -> None:
+        """While this stream records: draw ``side`` into the recording (``vrhi_sequence_fork``).  Launches on
+        ``side`` are recorded from here on and may run beside this stream's; they rejoin when the recording ends."""
+        check(lib().vrhi_sequence_fork(self._h, side._h))
+
 
 class Sequence:
     """A recorded run of launches (``vrhi_sequence``), replayed with one submission."""

@@ -456,16 +456,11 @@ def main():
     n_slabs = plan.part.chunk_count
     group_params, group_slabs = [], []
     if world > 1:
-        for gidx in range(GROUPS):
-            count = (n_slabs - gidx + GROUPS - 1) // GROUPS if gidx < n_slabs else 0
-            if count <= 0:
-                continue
+        for (first, step_, count), slabs in partition.comb_groups(plan, GROUPS):
             gp = copy.copy(params)
-            gp.chunk_first = plan.part.chunk_first + gidx * plan.part.chunk_step
-            gp.chunk_step = plan.part.chunk_step * GROUPS
-            gp.chunk_count = count
+            gp.chunk_first, gp.chunk_step, gp.chunk_count = first, step_, count
             group_params.append(gp)
-            group_slabs.append((gidx, count, GROUPS))
+            group_slabs.append(slabs)
         comm_stream = torch.cuda.Stream(device=local)
         comm_st = dev.wrap_stream(comm_stream.cuda_stream)
         exchange = None

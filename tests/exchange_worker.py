@@ -38,12 +38,10 @@ def main() -> int:
 
     def groups():
         import copy
-        for g in range(G):
+        for g, ((first, step, count), comb) in enumerate(partition.comb_groups(plan, G)):
             p = copy.copy(base)
-            p.chunk_first = plan.part.chunk_first + g * plan.part.chunk_step
-            p.chunk_step = plan.part.chunk_step * G
-            p.chunk_count = (slabs - g + G - 1) // G
-            yield g, p, (g, p.chunk_count, G)
+            p.chunk_first, p.chunk_step, p.chunk_count = first, step, count
+            yield g, p, comb
 
     def check(name):
         torch.cuda.synchronize()

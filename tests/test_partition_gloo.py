@@ -62,3 +62,54 @@ def test_image_gather_and_partial_sums(tmp_path, world, height, width, scheme, c
         assert ok_image and ok_sum
         spans.append((b, c))
     assert spans[0][0] == 0 and sum(c for _, c in spans) == 1000003
+
+
+@pytest.mark.parametrize("world,slabs,groups", [(2, 6, 3), (4, 8, 4), (3, 5, 2), (2, 3, 8), (1, 7, 4)])
+def test_combs_cover_every_owned_chunk_exactly_once(world, slabs, groups):
+    chunk, height = 4, 4 * world * slabs
+    for rank in range(world):
+        plan = partition.plan_image(height, world, rank, L.PART_CYCLIC, chunk)
+        owned = [r0 // chunk for r0, _ in plan.chunks()]
+        seen, slabs_seen = [], []
+        for (first, step, count), (s0, n, stride) in partition.comb_groups(plan, groups):
+            assert count == n and stride == groups
+            seen += [first + k * step for k in range(count)]
+            slabs_seen += [s0 + k * stride for k in range(n)]
+        assert sorted(seen) == owned
+        assert sorted(slabs_seen) == list(range(slabs))
+        # chunk ids and slab ids name the same rows: chunk = slab * world + rank
+        assert sorted(seen) == sorted(s * world + rank for s in slabs_seen)
+    with pytest.raises(ValueError):
+        partition.comb_groups(partition.plan_image(height, world, 0, L.PART_CONTIGUOUS, 0), 2)
+
+
+def _comb_worker(rank, world, port, height, width, chunk, groups, result_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        plan = partition.plan_image(height, world, rank, L.PART_CYCLIC, chunk)
+        image = torch.full((height, width), -1, dtype=torch.int32)
+        want = torch.arange(width, dtype=torch.int32)[None, :] + 1000 * torch.arange(height, dtype=torch.int32)[:, None]
+        ok_partial = True
+        done_slabs = set()
+        for (first, step, count), comb in partition.comb_groups(plan, groups):
+            for k in range(count):                      # "compute" this comb's chunks
+                r0 = (first + k * step) * chunk
+                image[r0:r0 + chunk] = want[r0:r0 + chunk]
+            partition.all_gather_image(image, plan, slabs=comb)
+            done_slabs |= {comb[0] + k * comb[2] for k in range(comb[1])}
+            for s in range(height // (chunk * world)):  # gathered combs are whole, the others still hold only own rows
+                rows = slice(s * world * chunk, (s + 1) * world * chunk)
+                if s in done_slabs:
+                    ok_partial &= bool(torch.equal(image[rows], want[rows]))
+        np.save(os.path.join(result_dir, f"c{rank}.npy"), np.array([ok_partial, bool(torch.equal(image, want))], dtype=np.int64))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_gather_comb_by_comb_over_gloo(tmp_path):
+    world, height, width, chunk, groups = 2, 96, 5, 8, 3
+    mp.spawn(_comb_worker, args=(world, _free_port(), height, width, chunk, groups, str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        ok_partial, ok_all = np.load(tmp_path / f"c{r}.npy")
+        assert ok_partial and ok_all

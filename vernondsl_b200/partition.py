@@ -4,7 +4,10 @@ Work is split by the planner inside ``libvrhi.so`` (``vrhi_partition_rows`` /
 ``vrhi_partition_leading``); this module adds the only exchange steps the path has:
 
 * escape-time images: every rank computes its own row chunks into a full-size image at their
-  true position, then the chunks are all-gathered in place (no staging copy, no permutation);
+  true position, then the chunks are gathered in place (no staging copy, no permutation), by one of
+  :class:`WireImageExchange` (uint16 counts pushed by the copy engines, widened on arrival),
+  :class:`PullImageExchange` (each rank reads its peers' uint16 rows over NVLink and widens them in
+  the same kernel), :class:`PeerImageExchange` (uint32 rows pushed) or :func:`all_gather_image` (NCCL);
 * the tanh-MSE backward: ``db`` and the loss are all-reduced (sum); ``dW`` and ``dx`` stay sharded.
 
 Map and row operators need no exchange: each rank owns a slice of the leading axis.
@@ -45,6 +48,24 @@ def plan_image(height: int, world: int, rank: int, scheme: int = L.PART_CYCLIC, 
     """Cyclic chunks by default: escape-time cost varies smoothly over the image, so dealing
     128-row chunks round-robin balances ranks where equal contiguous bands do not."""
     return ImagePlan(height, world, rank, scheme, ops.partition_rows(height, world, rank, scheme, chunk_rows))
+
+
+def comb_groups(plan: ImagePlan, groups: int) -> List[Tuple[Tuple[int, int, int], Tuple[int, int, int]]]:
+    """Split a cyclic plan's slabs into ``groups`` combs for a pipelined step: comb g takes slabs g, g+groups,
+    g+2*groups, ...  Every comb reaches over the whole image, so the combs cost about the same although rows
+    near the set cost many times the rows at the edges.  Returns, per non-empty comb,
+    ``((chunk_first, chunk_step, chunk_count), (slab_first, slab_count, slab_stride))``: the first triple goes
+    into the escape-time parameters of the comb's launch, the second names the comb to the exchange."""
+    if plan.scheme != L.PART_CYCLIC:
+        raise ValueError("combs are defined for cyclic plans")
+    if groups < 1:
+        raise ValueError("at least one group")
+    p, out = plan.part, []
+    for g in range(groups):
+        count = (p.chunk_count - g + groups - 1) // groups if g < p.chunk_count else 0
+        if count > 0:
+            out.append(((p.chunk_first + g * p.chunk_step, p.chunk_step * groups, count), (g, count, groups)))
+    return out
 
 
 def owner_of_row(plan: ImagePlan, row: int) -> int:

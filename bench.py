@@ -325,6 +325,72 @@ def run_only(args):
         img = dev.empty((H, W), np.uint32, L.IMAGE)
         res["ms"] = time_launches(dev, st, lambda: ops.escape_time(st, img, p), it, warmup=1)
         res["shape"] = [H, W]
+    elif name in ("escape_split", "escape_beside"):
+        from vernondsl_b200 import partition
+
+        W = H = max(2048, int(16384 * args.scale) // 2048 * 2048)
+        dx, dy = ops.grid_steps(-1.6, 1.6, -1.6, 1.6, W, H)
+        img = dev.empty((H, W), np.uint32, L.IMAGE)
+        world = max(1, args.world)
+        plan = partition.plan_image(H, world, 0, L.PART_CYCLIC, 128)        # rank 0's share of a world of that size
+        base = ops.escape_params(L.JULIA, W, H, -1.6, -1.6, dx, dy, cr=-0.8, ci=0.156, max_iter=4096, partition=plan.part)
+        st2 = dev.stream()
+        res["shape"], res["world"] = [H, W], world
+        if name == "escape_split":
+            # what a step costs when the rank's rows go out in G launches (combs of slabs), on one stream and on two in turn
+            def launches(groups, streams):
+                def fn():
+                    e = dev.event()
+                    e.record(st)
+                    st2.wait(e)
+                    for k, ((first, step_, count), _) in enumerate(partition.comb_groups(plan, groups)):
+                        gp = copy.copy(base)
+                        gp.chunk_first, gp.chunk_step, gp.chunk_count = first, step_, count
+                        ops.escape_time(streams[k % len(streams)], img, gp)
+                    e2 = dev.event()
+                    e2.record(st2)
+                    st.wait(e2)
+                    e.close(); e2.close()   # destruction is deferred until the recorded work has passed
+                return fn
+            res["ms_one_launch"] = time_launches(dev, st, launches(1, [st]), it, warmup=2)
+            for g in (2, 4, 8):
+                res[f"ms_{g}_launches_one_stream"] = time_launches(dev, st, launches(g, [st]), it, warmup=2)
+                res[f"ms_{g}_launches_two_streams"] = time_launches(dev, st, launches(g, [st, st2]), it, warmup=2)
+        else:
+            # does a small memory-bound kernel on another stream run while the escape-time kernel runs?
+            wire = dev.empty((H, W), np.uint16, L.IMAGE)
+            img2 = dev.empty((H, W), np.uint32, L.IMAGE)
+            flags = dev.empty((8,), np.uint32, L.STORAGE_BUFFER)
+            ops.escape_time(st, img, base, wire=wire)
+            ops.widen_rows_u16(st2, wire, img2, W, H, 128, 2, 0, 0, 8)
+            dev.synchronize()
+            for order in ("escape_first", "helpers_first"):
+                e0, e_esc, e_sig, e_wid = (dev.event() for _ in range(4))
+                dev.synchronize()
+                e0.record(st)
+                st2.wait(e0)
+
+                def helpers():
+                    ops.gather_signal(st2, [flags], 2, 1, 1)
+                    e_sig.record(st2)
+                    ops.widen_rows_u16(st2, wire, img2, W, H, 128, 2, 0, 0, 8)
+                    e_wid.record(st2)
+
+                def escape():
+                    ops.escape_time(st, img, base)
+                    e_esc.record(st)
+
+                (escape(), helpers()) if order == "escape_first" else (helpers(), escape())
+                dev.synchronize()
+                res[order] = {"escape_done_ms": e0.elapsed_ms(e_esc), "one_warp_kernel_done_ms": e0.elapsed_ms(e_sig),
+                              "widen_done_ms": e0.elapsed_ms(e_wid)}
+            e0, e1 = dev.event(), dev.event()
+            e0.record(st2)
+            ops.widen_rows_u16(st2, wire, img2, W, H, 128, 2, 0, 0, 8)
+            e1.record(st2)
+            e1.synchronize()
+            res["widen_alone_ms"] = e0.elapsed_ms(e1)
+        st2.check()
     elif name in ("fused_map", "map_tape"):
         n = int((1 << 28) * args.scale) // 4096 * 4096
         a, x, y, o = rn(n), rn(n), rn(n), torch.empty(n, device=device)
@@ -370,6 +436,7 @@ def main():
     ap.add_argument("--only", default=None, help="run one kernel family at reduced size (for profiling) and exit")
     ap.add_argument("--scale", type=float, default=0.25, help="with --only: fraction of the full workload size")
     ap.add_argument("--iters", type=int, default=3, help="with --only: timed launches")
+    ap.add_argument("--world", type=int, default=1, help="with --only escape_split/escape_beside: time rank 0's share of a world of this size")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)

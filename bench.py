@@ -261,8 +261,15 @@ def other_workloads(dev, st, torch, hbm_peak, peak_kind, fp32_peak):
     e = t.op("exp", t.op("mul", t.op("mul", t.const(-0.5), t.input(1)), t.input(1)))
     q = t.op("sqrt", t.op("add", t.op("abs", t.input(2)), t.const(1e-3)))
     t.output(t.op("fma", t.op("tanh", u), e, q))
+    before = ops.tape_jit_stats()["launches"]
     ms = time_launches(dev, st, lambda: ops.map_tape(st, t, [A, X, Y], [O], n // 4096, 4096), 10)
-    line("the same chain through the generic fused tape, 2^28 f32", "map_tape", ms, 16 * n)
+    compiled = ops.tape_jit_stats()["launches"] > before
+    line("the same chain as a generic tape, 2^28 f32 (kernel compiled for the tape at first use)" if compiled else
+         "the same chain as a generic tape, 2^28 f32 (interpreting kernel: no run-time compiler on this box)", "map_tape", ms, 16 * n)
+    if compiled:
+        ms = time_launches(dev, st, lambda: ops.map_tape(st, t, [A, X, Y], [O], n // 4096, 4096, interpret=True), 10)
+        line("the same tape through the interpreting kernel, 2^28 f32", "map_tape (interpreted)", ms, 16 * n,
+             note="bound by instruction issue and shared-memory traffic, not by HBM")
     del a, x, y, o
 
     # row reductions and softmax, [65536, 4096], N(0,4) read as sigma = 2

@@ -330,7 +330,18 @@ typedef struct vrhi_tape_params {
   uint32_t row_vector_mask, col_vector_mask, scalar_mask;
   uint32_t out_value[VRHI_TAPE_MAX_OUTPUTS]; /* value index stored to output k */
   vrhi_tape_instr instr[VRHI_TAPE_MAX_INSTR];
+  uint32_t flags; /* VRHI_TAPE_FLAG_* */
 } vrhi_tape_params;
+/* A tape normally runs as a kernel compiled for it at first use (NVRTC, cached; values in
+ * registers, HBM-bound).  This flag, or VRHI_TAPE_JIT=0 in the environment, selects the
+ * interpreting kernel instead, which is also what runs where NVRTC is not installed, for column
+ * counts that are not a multiple of 4 and for unaligned arrays.  Both give the same bits. */
+#define VRHI_TAPE_FLAG_INTERPRET 1u
+/* Tapes compiled so far in this process, and launches of compiled tapes. */
+VRHI_API int vrhi_tape_jit_stats(uint64_t *out_compiled, uint64_t *out_launches);
+/* The CUDA source generated for a tape (NUL-terminated, truncated to `capacity`); *out_needed
+ * receives the full length including the terminator.  Needs no device. */
+VRHI_API int vrhi_tape_source(const vrhi_tape_params *params, char *buffer, uint64_t capacity, uint64_t *out_needed);
 
 /* ops "row_sum", "row_max": args [0] INPUT [rows][cols] floats, [1] OUTPUT [rows] floats.
  * op "row_softmax": args [0] INPUT [rows][cols], [1] OUTPUT [rows][cols]; max is subtracted.

@@ -87,15 +87,31 @@ def chain_tape():
     return t
 
 
-@pytest.mark.parametrize("rows,cols", [(1, 4096), (64, 1024), (7, 36), (5, 13), (1, 1)])
+def run_tape_both_ways(dev, stream, tape, inputs, out_shapes, rows, cols):
+    """Runs the tape as a kernel compiled for it and through the interpreting kernel; the two must agree bit for
+    bit.  Where the compiled path applies (columns a multiple of 4) it must really have run."""
+    outs_c = [dev.empty(s, np.float32) for s in out_shapes]
+    outs_i = [dev.empty(s, np.float32) for s in out_shapes]
+    before = ops.tape_jit_stats()["launches"]
+    ops.map_tape(stream, tape, inputs, outs_c, rows, cols)
+    compiled_ran = ops.tape_jit_stats()["launches"] - before
+    ops.map_tape(stream, tape, inputs, outs_i, rows, cols, interpret=True)
+    assert ops.tape_jit_stats()["launches"] - before == compiled_ran      # the flag really selects the interpreter
+    stream.check()
+    assert compiled_ran == (1 if cols % 4 == 0 else 0)
+    got_c, got_i = [o.download() for o in outs_c], [o.download() for o in outs_i]
+    for c, i in zip(got_c, got_i):
+        assert np.array_equal(c.view(np.uint32), i.view(np.uint32)), "compiled and interpreted tape differ"
+    return got_c
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 4096), (64, 1024), (7, 36), (5, 13), (1, 1), (3, 4), (1000, 1028), (1, (1 << 20) + 4)])
 def test_tape_runs_the_same_chain(dev, stream, rows, cols):
     n = rows * cols
     a, x, y = chain_inputs(n, seed=7)
     A, X, Y = (dev.from_numpy(v) for v in (a, x, y))
-    out = dev.empty(n, np.float32)
-    ops.map_tape(stream, chain_tape(), [A, X, Y], [out], rows, cols)
-    stream.check()
-    check_chain(out.download(), a, x, y)
+    got, = run_tape_both_ways(dev, stream, chain_tape(), [A, X, Y], [n], rows, cols)
+    check_chain(got, a, x, y)
 
 
 UNARY_RANGES = {"tanh": (-12, 12), "exp": (-80, 80), "sqrt": (0, 1e6), "abs": (-5, 5), "neg": (-5, 5), "square": (-1e3, 1e3),
@@ -111,12 +127,10 @@ def test_tape_primitives_within_2_ulp(dev, stream, op):
     if op in ("tanh", "sigmoid", "exp"):
         x[:4096] = rng.uniform(-1e-3, 1e-3, 4096).astype(np.float32)  # near zero, where relative accuracy is hardest
     X = dev.from_numpy(x)
-    out = dev.empty(x.size, np.float32)
     t = ops.Tape(1)
     t.output(t.op(op, t.input(0)))
-    ops.map_tape(stream, t, [X], [out], 1, x.size)
-    stream.check()
-    got, want = out.download(), oracle.unary(op, x)
+    got, = run_tape_both_ways(dev, stream, t, [X], [x.size], 1, x.size)
+    want = oracle.unary(op, x)
     ok = np.isfinite(want) & (np.abs(want) > 1e-37)
     # cos/sin: error measured against the function's scale near its zeros, as libm accuracy tables do
     err = oracle.ulp_diff(got[ok], want[ok]) if op not in ("cos", "sin") else \
@@ -135,16 +149,14 @@ def test_tape_broadcasts_and_multiple_outputs(dev, stream):
         mm = np.ascontiguousarray(m[:, :cols_used])
         rr = np.ascontiguousarray(rv[:cols_used])
         M, RV, CV, SC = dev.from_numpy(mm), dev.from_numpy(rr), dev.from_numpy(cv), dev.from_numpy(sc)
-        o1, o2 = dev.empty(mm.shape, np.float32), dev.empty(mm.shape, np.float32)
         t = ops.Tape(4, row_vectors=[1], col_vectors=[2], scalars=[3])
         s = t.op("add", t.op("mul", t.input(0), t.input(1)), t.input(2))
         t.output(s)
         t.output(t.op("mul", t.op("max", s, t.const(0.0)), t.input(3)))
-        ops.map_tape(stream, t, [M, RV, CV, SC], [o1, o2], rows, cols_used)
-        stream.check()
+        o1, o2 = run_tape_both_ways(dev, stream, t, [M, RV, CV, SC], [mm.shape, mm.shape], rows, cols_used)
         want1 = (mm * rr[None, :]).astype(np.float32) + cv[:, None]
-        assert np.array_equal(o1.download(), want1)
-        assert np.array_equal(o2.download(), np.maximum(want1, 0) * sc[0])
+        assert np.array_equal(o1, want1)
+        assert np.array_equal(o2, np.maximum(want1, 0) * sc[0])
 
 
 def test_tape_errors(dev, stream):
@@ -160,3 +172,39 @@ def test_tape_errors(dev, stream):
     with pytest.raises(L.VrhiError) as e:
         ops.map_tape(stream, t, [X], [out], 2, 64)  # 128 elements do not fit
     assert e.value.status == L.ERR_SIZE
+
+
+def test_compiled_tape_covers_every_operation_and_is_cached(dev, stream):
+    """One tape through every opcode: compiled and interpreted kernels must agree bit for bit, a second
+    launch must reuse the compiled kernel, and a compiled tape can be recorded into a sequence."""
+    rows, cols = 33, 512
+    rng = np.random.default_rng(21)
+    a = rng.uniform(0.1, 3.0, (rows, cols)).astype(np.float32)
+    b = rng.uniform(-2.0, 2.0, (rows, cols)).astype(np.float32)
+    A, B = dev.from_numpy(a), dev.from_numpy(b)
+    t = ops.Tape(2)
+    x, y = t.input(0), t.input(1)
+    acc = t.op("add", x, y)
+    for name in ("sub", "mul", "div", "max", "min", "eq"):
+        acc = t.op("add", acc, t.op(name, x, y))
+    for name in ("neg", "abs", "square", "relu", "sign", "step", "sqrt", "rsqrt", "recip", "exp", "log", "tanh", "sigmoid", "cos", "sin"):
+        acc = t.op("add", acc, t.op(name, x))
+    acc = t.op("fma", acc, t.const(0.5), y)
+    t.output(acc)
+    t.output(t.op("sigmoid", y))
+    before = ops.tape_jit_stats()
+    o1, o2 = run_tape_both_ways(dev, stream, t, [A, B], [(rows, cols), (rows, cols)], rows, cols)
+    mid = ops.tape_jit_stats()
+    assert mid["compiled"] - before["compiled"] == 1
+    assert np.all(np.isfinite(o1)) and np.all((o2 > 0) & (o2 < 1))
+    again = [dev.empty((rows, cols), np.float32) for _ in range(2)]
+    ops.map_tape(stream, t, [A, B], again, rows, cols)
+    assert ops.tape_jit_stats()["compiled"] == mid["compiled"]          # cached
+    with stream.record() as seq:                                       # compiled before: recordable
+        ops.map_tape(stream, t, [A, B], again, rows, cols)
+    for o in again:
+        o.fill(0, stream=stream)
+    seq.launch()
+    stream.check()
+    assert np.array_equal(again[0].download(), o1) and np.array_equal(again[1].download(), o2)
+    seq.close()

@@ -97,7 +97,10 @@ class TapeParams(C.Structure):
                 ("n_instr", C.c_uint32), ("rows", C.c_uint64), ("cols", C.c_uint64),
                 ("row_vector_mask", C.c_uint32), ("col_vector_mask", C.c_uint32),
                 ("scalar_mask", C.c_uint32), ("out_value", C.c_uint32 * TAPE_MAX_OUTPUTS),
-                ("instr", TapeInstr * TAPE_MAX_INSTR)]
+                ("instr", TapeInstr * TAPE_MAX_INSTR), ("flags", C.c_uint32)]
+
+
+TAPE_FLAG_INTERPRET = 1
 
 
 class RowsParams(C.Structure):
@@ -161,6 +164,8 @@ PROTOTYPES = {
     "vrhi_event_synchronize": [_vp],
     "vrhi_event_elapsed_ms": [_vp, _vp, _P(C.c_float)],
     "vrhi_stream_wait_event": [_vp, _vp],
+    "vrhi_tape_jit_stats": [_P(C.c_uint64), _P(C.c_uint64)],
+    "vrhi_tape_source": [_P(TapeParams), C.c_char_p, C.c_uint64, _P(C.c_uint64)],
     "vrhi_sequence_begin": [_vp],
     "vrhi_sequence_fork": [_vp, _vp],
     "vrhi_sequence_end": [_vp, _P(_vp)],

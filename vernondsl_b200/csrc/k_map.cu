@@ -7,41 +7,10 @@
 //     out = tanh(a*x + y) * exp(-0.5*x*x) + sqrt(|y| + 1e-3).
 #include <cstring>
 
+#include "tape_math.cuh"
 #include "vrhi_internal.h"
 
 namespace vrhi {
-
-// exp(x) to well under one ulp in the normal range: n = round(x*log2e), r = x - n*ln2 with a
-// two-constant split (both steps exact or fused), exp(r) = 1 + (r + r*r*q(r)) with the Taylor
-// polynomial through r^7 (|r| <= 0.3466, next term < 2^-27), scaled by 2^n in two exact factors.
-__device__ __forceinline__ float exp_sub_ulp(float x) {
-  x = fminf(fmaxf(x, -104.0f), 88.72f);
-  const float t = fmaf(x, 1.442695041f, 12582912.0f);
-  const float n = t - 12582912.0f;
-  float r = fmaf(n, -0.693145752f, x);
-  r = fmaf(n, -1.42860677e-06f, r);
-  float q = 1.98412698e-4f;
-  q = fmaf(q, r, 1.38888889e-3f);
-  q = fmaf(q, r, 8.33333333e-3f);
-  q = fmaf(q, r, 4.16666667e-2f);
-  q = fmaf(q, r, 1.66666667e-1f);
-  q = fmaf(q, r, 0.5f);
-  const float p = fmaf(r * r, q, r);
-  const float res = 1.0f + p;
-  const int ni = (int)n, h = ni / 2;
-  return res * __int_as_float((h + 127) << 23) * __int_as_float((ni - h + 127) << 23);
-}
-
-// 1 / (1 + exp(-x)): the rounding of 1 + E is recovered (two-sum) and folded into one Newton
-// step on the reciprocal, so that the result carries little more than the error of E itself.
-__device__ __forceinline__ float sigmoid_accurate(float x) {
-  const float e = exp_sub_ulp(-x);
-  const float d = 1.0f + e;
-  const float dl = (e > 1.0f) ? (e - d) + 1.0f : (1.0f - d) + e;
-  const float r = 1.0f / d;
-  const float err = fmaf(-d, r, 1.0f);
-  return fmaf(r, err - dl * r, r);
-}
 
 __device__ __forceinline__ float4 ld_stream(const float4 *p) { return __ldcs(p); }
 __device__ __forceinline__ void st_stream(float4 *p, float4 v) { __stcs(p, v); }
@@ -373,6 +342,22 @@ static int tape_arity(int op) {
   }
 }
 
+// What both execution paths require of a tape: known opcodes, operands defined before use, outputs that exist.
+static int validate_tape(const vrhi_tape_params &q) {
+  const int NI = (int)q.n_inputs, NT = (int)q.n_instr;
+  for (int t = 0; t < NT; ++t) {
+    const vrhi_tape_instr &I = q.instr[t];
+    if (I.op >= VRHI_T_OPCOUNT) return fail(VRHI_ERR_INVALID, "map_tape: instruction %d has unknown opcode %u", t, I.op);
+    const int ar = tape_arity(I.op);
+    const uint16_t src[3] = {I.a, I.b, I.c};
+    for (int s = 0; s < ar; ++s)
+      if (src[s] >= NI + t) return fail(VRHI_ERR_INVALID, "map_tape: instruction %d reads value %u before it is defined", t, src[s]);
+  }
+  for (uint32_t k = 0; k < q.n_outputs; ++k)
+    if ((int)q.out_value[k] >= NI + NT) return fail(VRHI_ERR_INVALID, "map_tape: output %u names value %u, which does not exist", k, q.out_value[k]);
+  return VRHI_OK;
+}
+
 // SSA tape -> physical program (see the comment at the top of this section).
 static int plan_tape(const vrhi_tape_params &q, TapeDev *T, int max_slots) {
   const int NI = (int)q.n_inputs, NT = (int)q.n_instr, NV = NI + NT;
@@ -474,12 +459,11 @@ int launch_map_tape(vrhi_stream_t *st, const ArgView *args, int n_args, const vo
   if (n == 0) return VRHI_OK;
   if ((q.row_vector_mask & q.col_vector_mask) | (q.row_vector_mask & q.scalar_mask) | (q.col_vector_mask & q.scalar_mask))
     return fail(VRHI_ERR_INVALID, "map_tape: an input is marked with more than one broadcast shape");
+  VRHI_TRY(validate_tape(q));
   TapeDev T{};
   T.n_inputs = q.n_inputs; T.n_outputs = q.n_outputs;
   T.row_vector_mask = q.row_vector_mask; T.col_vector_mask = q.col_vector_mask; T.scalar_mask = q.scalar_mask;
   T.rows = q.rows; T.cols = q.cols;
-  const int slot_capacity = kTapeSlotBytes / (kTapeThreads * (int)sizeof(float4));  // 24 slots of one group
-  VRHI_TRY(plan_tape(q, &T, slot_capacity));
   for (uint32_t k = 0; k < q.n_inputs; ++k) {
     uint64_t need = ((q.row_vector_mask >> k) & 1u) ? q.cols * 4 : ((q.col_vector_mask >> k) & 1u) ? q.rows * 4 : ((q.scalar_mask >> k) & 1u) ? 4 : n * 4;
     if (args[k].bytes < need) return fail(VRHI_ERR_SIZE, "map_tape: input %u holds %llu bytes, %llu needed", k, (unsigned long long)args[k].bytes, (unsigned long long)need);
@@ -491,6 +475,15 @@ int launch_map_tape(vrhi_stream_t *st, const ArgView *args, int n_args, const vo
     if (!writable(o)) return fail(VRHI_ERR_INVALID, "map_tape: output %u is read-only (class %s)", k, vrhi_arg_class_name(o.buf_cls));
     T.out[k] = (float *)o.ptr;
   }
+  // The tape compiled to a kernel of its own where that is possible (values in registers, HBM-bound);
+  // the interpreter below otherwise.  Both compute the same bits.
+  {
+    const int rc = tape_jit_launch(st, q, T.in, T.out);
+    if (rc == VRHI_OK) return post_launch(st, "map_tape (compiled)");
+    if (rc != 1) return rc;
+  }
+  const int slot_capacity = kTapeSlotBytes / (kTapeThreads * (int)sizeof(float4));  // 24 slots of one group
+  VRHI_TRY(plan_tape(q, &T, slot_capacity));
   const int sms = st->dev->prop.multiProcessorCount;
   const uint32_t ns = T.n_slots ? T.n_slots : 1;
   if (q.cols % 4 == 0) {

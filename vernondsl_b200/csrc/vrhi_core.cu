@@ -518,6 +518,29 @@ int vrhi_event_elapsed_ms(vrhi_event start, vrhi_event stop, float *out_ms) {
   return VRHI_OK;
 }
 
+int vrhi_tape_jit_stats(uint64_t *out_compiled, uint64_t *out_launches) {
+  tape_jit_counters(out_compiled, out_launches);
+  return VRHI_OK;
+}
+
+int vrhi_tape_source(const vrhi_tape_params *params, char *buffer, uint64_t capacity, uint64_t *out_needed) {
+  if (!params) return fail(VRHI_ERR_INVALID, "NULL argument");
+  vrhi_tape_params q;
+  VRHI_TRY(read_params(params, params->size, &q));
+  if (q.n_inputs > VRHI_TAPE_MAX_INPUTS || q.n_outputs == 0 || q.n_outputs > VRHI_TAPE_MAX_OUTPUTS || q.n_instr > VRHI_TAPE_MAX_INSTR)
+    return fail(VRHI_ERR_INVALID, "tape outside the limits");
+  for (uint32_t t = 0; t < q.n_instr; ++t)
+    if (q.instr[t].op >= VRHI_T_OPCOUNT) return fail(VRHI_ERR_INVALID, "instruction %u has unknown opcode %u", t, q.instr[t].op);
+  const std::string src = tape_jit_source(q);
+  if (out_needed) *out_needed = src.size() + 1;
+  if (buffer && capacity) {
+    const size_t n = src.size() < capacity - 1 ? src.size() : (size_t)capacity - 1;
+    memcpy(buffer, src.data(), n);
+    buffer[n] = 0;
+  }
+  return VRHI_OK;
+}
+
 /* ---------------------------------------------------------------- recorded sequences ---- */
 
 int vrhi_sequence_begin(vrhi_stream stream) {

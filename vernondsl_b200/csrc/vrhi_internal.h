@@ -121,6 +121,12 @@ int launch_widen_rows_u16(vrhi_stream_t *, const ArgView *, int, const void *, s
 int launch_gather_signal(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
 int launch_gather_pull_u16(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
 
+// Run-time compiled tapes (tape_jit.cpp).  tape_jit_launch returns VRHI_OK (launched), 1 (leave it to
+// the interpreter) or an error code.
+int tape_jit_launch(vrhi_stream_t *st, const vrhi_tape_params &q, const float *const *in, float *const *out);
+void tape_jit_counters(uint64_t *compiled, uint64_t *launches);
+std::string tape_jit_source(const vrhi_tape_params &q);
+
 // Copies a caller's parameter block into a zero-initialised struct of the current layout,
 // honouring the leading size field (older, shorter callers leave new fields zero).
 template <class P>

@@ -165,9 +165,32 @@ class Tape:
         return p
 
 
-def map_tape(stream: Stream, tape: Tape, inputs: Sequence[Buffer], outputs: Sequence[Buffer], rows: int, cols: int) -> None:
+def map_tape(stream: Stream, tape: Tape, inputs: Sequence[Buffer], outputs: Sequence[Buffer], rows: int, cols: int,
+             interpret: bool = False) -> None:
+    """Run the tape over [rows][cols] arrays as one kernel: compiled for this tape at first use, or, with
+    ``interpret`` (and where no run-time compiler is installed), by the interpreting kernel.  Same bits either way."""
     args = [b.arg(L.INPUT) for b in inputs] + [b.arg(L.OUTPUT) for b in outputs]
-    launch(stream, "map_tape", args, tape.params(rows, cols))
+    p = tape.params(rows, cols)
+    if interpret:
+        p.flags |= L.TAPE_FLAG_INTERPRET
+    launch(stream, "map_tape", args, p)
+
+
+def tape_jit_stats() -> dict:
+    """Tapes compiled so far in this process and launches of compiled tapes."""
+    a, b = C.c_uint64(), C.c_uint64()
+    check(lib().vrhi_tape_jit_stats(C.byref(a), C.byref(b)))
+    return {"compiled": a.value, "launches": b.value}
+
+
+def tape_source(tape: Tape, rows: int = 4, cols: int = 4) -> str:
+    """The CUDA source the library generates for this tape (no device needed)."""
+    p = tape.params(rows, cols)
+    need = C.c_uint64()
+    check(lib().vrhi_tape_source(C.byref(p), None, 0, C.byref(need)))
+    buf = C.create_string_buffer(need.value)
+    check(lib().vrhi_tape_source(C.byref(p), buf, need.value, C.byref(need)))
+    return buf.value.decode()
 
 
 # ------------------------------------------------------------------------------ rows ----------

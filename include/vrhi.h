@@ -337,8 +337,12 @@ typedef struct vrhi_tape_params {
  * interpreting kernel instead, which is also what runs where NVRTC is not installed, for column
  * counts that are not a multiple of 4 and for unaligned arrays.  Both give the same bits. */
 #define VRHI_TAPE_FLAG_INTERPRET 1u
-/* Tapes compiled so far in this process, and launches of compiled tapes. */
-VRHI_API int vrhi_tape_jit_stats(uint64_t *out_compiled, uint64_t *out_launches);
+/* Tapes compiled so far in this process, launches of compiled tapes, the version of the run-time
+ * compiler in use (major*1000 + minor*10; 0 before the first tape, or when there is none) and the
+ * CUDA version the library was built with, counted the same way.  When the two versions are equal
+ * the compiled and the interpreting kernel give the same bits; with another compiler version the
+ * transcendental functions may round differently in the last place.  Any pointer may be NULL. */
+VRHI_API int vrhi_tape_jit_stats(uint64_t *out_compiled, uint64_t *out_launches, int *out_compiler_version, int *out_built_version);
 /* The CUDA source generated for a tape (NUL-terminated, truncated to `capacity`); *out_needed
  * receives the full length including the terminator.  Needs no device. */
 VRHI_API int vrhi_tape_source(const vrhi_tape_params *params, char *buffer, uint64_t capacity, uint64_t *out_needed);

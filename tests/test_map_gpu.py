@@ -100,8 +100,12 @@ def run_tape_both_ways(dev, stream, tape, inputs, out_shapes, rows, cols):
     stream.check()
     assert compiled_ran == (1 if cols % 4 == 0 else 0)
     got_c, got_i = [o.download() for o in outs_c], [o.download() for o in outs_i]
+    info = ops.tape_jit_stats()
     for c, i in zip(got_c, got_i):
-        assert np.array_equal(c.view(np.uint32), i.view(np.uint32)), "compiled and interpreted tape differ"
+        if info["compiler_version"] == info["built_version"] or not compiled_ran:
+            assert np.array_equal(c.view(np.uint32), i.view(np.uint32)), "compiled and interpreted tape differ"
+        else:   # another compiler version: its math library may round the last place differently
+            assert np.allclose(c, i, rtol=3e-7, atol=1e-37, equal_nan=True)
     return got_c
 
 

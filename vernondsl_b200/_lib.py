@@ -164,7 +164,7 @@ PROTOTYPES = {
     "vrhi_event_synchronize": [_vp],
     "vrhi_event_elapsed_ms": [_vp, _vp, _P(C.c_float)],
     "vrhi_stream_wait_event": [_vp, _vp],
-    "vrhi_tape_jit_stats": [_P(C.c_uint64), _P(C.c_uint64)],
+    "vrhi_tape_jit_stats": [_P(C.c_uint64), _P(C.c_uint64), _P(C.c_int), _P(C.c_int)],
     "vrhi_tape_source": [_P(TapeParams), C.c_char_p, C.c_uint64, _P(C.c_uint64)],
     "vrhi_sequence_begin": [_vp],
     "vrhi_sequence_fork": [_vp, _vp],

@@ -46,6 +46,8 @@ struct Nvrtc {
   decltype(&nvrtcGetProgramLog) log = nullptr;
   decltype(&nvrtcDestroyProgram) destroy = nullptr;
   decltype(&nvrtcGetErrorString) error_string = nullptr;
+  decltype(&nvrtcVersion) version = nullptr;
+  int version_number = 0;  // major * 1000 + minor * 10, as CUDART_VERSION counts
   bool ok = false;
 };
 
@@ -87,20 +89,38 @@ bool drv(const char *name, F *out) {
   return true;
 }
 
+bool bind(void *lib, Nvrtc *out) {
+  Nvrtc n;
+  n.ok = sym(lib, "nvrtcCreateProgram", &n.create) && sym(lib, "nvrtcCompileProgram", &n.compile) &&
+         sym(lib, "nvrtcGetCUBINSize", &n.cubin_size) && sym(lib, "nvrtcGetCUBIN", &n.cubin) &&
+         sym(lib, "nvrtcGetProgramLogSize", &n.log_size) && sym(lib, "nvrtcGetProgramLog", &n.log) &&
+         sym(lib, "nvrtcDestroyProgram", &n.destroy) && sym(lib, "nvrtcGetErrorString", &n.error_string) &&
+         sym(lib, "nvrtcVersion", &n.version);
+  if (!n.ok) return false;
+  int major = 0, minor = 0;
+  if (n.version(&major, &minor) != NVRTC_SUCCESS) return false;
+  n.version_number = major * 1000 + minor * 10;
+  *out = n;
+  return true;
+}
+
 void load_once() {
   if (g_loaded) return;
   g_loaded = true;
-  const char *names[] = {"libnvrtc.so.12", "libnvrtc.so", "/usr/local/cuda/lib64/libnvrtc.so.12", "/usr/local/cuda/lib64/libnvrtc.so"};
-  void *lib = nullptr;
-  for (const char *n : names)
-    if ((lib = dlopen(n, RTLD_NOW | RTLD_LOCAL))) break;
-  if (lib) {
-    Nvrtc &n = g_nvrtc;
-    n.ok = sym(lib, "nvrtcCreateProgram", &n.create) && sym(lib, "nvrtcCompileProgram", &n.compile) &&
-           sym(lib, "nvrtcGetCUBINSize", &n.cubin_size) && sym(lib, "nvrtcGetCUBIN", &n.cubin) &&
-           sym(lib, "nvrtcGetProgramLogSize", &n.log_size) && sym(lib, "nvrtcGetProgramLog", &n.log) &&
-           sym(lib, "nvrtcDestroyProgram", &n.destroy) && sym(lib, "nvrtcGetErrorString", &n.error_string);
+  // The compiler whose version is the one this library was built with is preferred: its math
+  // library is then the one the interpreting kernel was compiled against, which is what makes the
+  // two paths agree bit for bit.  Any other NVRTC 12 still gives a correct kernel.
+  const char *names[] = {getenv("VRHI_NVRTC"), "/usr/local/cuda/lib64/libnvrtc.so.12", "libnvrtc.so.12", "libnvrtc.so"};
+  Nvrtc fallback;
+  for (const char *name : names) {
+    if (!name || !*name) continue;
+    void *lib = dlopen(name, RTLD_NOW | RTLD_LOCAL);
+    Nvrtc n;
+    if (!lib || !bind(lib, &n)) continue;
+    if (n.version_number / 10 == CUDART_VERSION / 10) { g_nvrtc = n; break; }
+    if (!fallback.ok) fallback = n;
   }
+  if (!g_nvrtc.ok && fallback.ok) g_nvrtc = fallback;
   Driver &d = g_driver;
   d.ok = drv("cuModuleLoadData", &d.module_load_data) && drv("cuModuleGetFunction", &d.module_get_function) &&
          drv("cuLaunchKernel", &d.launch_kernel) && drv("cuGetErrorString", &d.get_error_string);
@@ -335,10 +355,12 @@ int tape_jit_launch(vrhi_stream_t *st, const vrhi_tape_params &q, const float *c
   return VRHI_OK;
 }
 
-void tape_jit_counters(uint64_t *compiled, uint64_t *launches) {
+void tape_jit_counters(uint64_t *compiled, uint64_t *launches, int *compiler_version, int *built_version) {
   std::lock_guard<std::mutex> lock(g_mu);
   if (compiled) *compiled = g_compiled;
   if (launches) *launches = g_launches;
+  if (compiler_version) *compiler_version = g_nvrtc.ok ? g_nvrtc.version_number : 0;
+  if (built_version) *built_version = CUDART_VERSION / 10 * 10;
 }
 
 // The generated source of a tape, for inspection and for tests that run without a GPU.

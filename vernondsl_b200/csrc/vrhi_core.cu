@@ -518,8 +518,8 @@ int vrhi_event_elapsed_ms(vrhi_event start, vrhi_event stop, float *out_ms) {
   return VRHI_OK;
 }
 
-int vrhi_tape_jit_stats(uint64_t *out_compiled, uint64_t *out_launches) {
-  tape_jit_counters(out_compiled, out_launches);
+int vrhi_tape_jit_stats(uint64_t *out_compiled, uint64_t *out_launches, int *out_compiler_version, int *out_built_version) {
+  tape_jit_counters(out_compiled, out_launches, out_compiler_version, out_built_version);
   return VRHI_OK;
 }
 

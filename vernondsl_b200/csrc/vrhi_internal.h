@@ -124,7 +124,7 @@ int launch_gather_pull_u16(vrhi_stream_t *, const ArgView *, int, const void *, 
 // Run-time compiled tapes (tape_jit.cpp).  tape_jit_launch returns VRHI_OK (launched), 1 (leave it to
 // the interpreter) or an error code.
 int tape_jit_launch(vrhi_stream_t *st, const vrhi_tape_params &q, const float *const *in, float *const *out);
-void tape_jit_counters(uint64_t *compiled, uint64_t *launches);
+void tape_jit_counters(uint64_t *compiled, uint64_t *launches, int *compiler_version, int *built_version);
 std::string tape_jit_source(const vrhi_tape_params &q);
 
 // Copies a caller's parameter block into a zero-initialised struct of the current layout,

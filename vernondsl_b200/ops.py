@@ -178,9 +178,9 @@ def map_tape(stream: Stream, tape: Tape, inputs: Sequence[Buffer], outputs: Sequ
 
 def tape_jit_stats() -> dict:
     """Tapes compiled so far in this process and launches of compiled tapes."""
-    a, b = C.c_uint64(), C.c_uint64()
-    check(lib().vrhi_tape_jit_stats(C.byref(a), C.byref(b)))
-    return {"compiled": a.value, "launches": b.value}
+    a, b, cv, bv = C.c_uint64(), C.c_uint64(), C.c_int(), C.c_int()
+    check(lib().vrhi_tape_jit_stats(C.byref(a), C.byref(b), C.byref(cv), C.byref(bv)))
+    return {"compiled": a.value, "launches": b.value, "compiler_version": cv.value, "built_version": bv.value}
 
 
 def tape_source(tape: Tape, rows: int = 4, cols: int = 4) -> str:

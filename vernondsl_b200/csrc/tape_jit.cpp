@@ -69,7 +69,7 @@ struct Compiled {
   CUfunction fn;
   bool flat;  // no row or column vectors: the kernel indexes the data as one long array
 };
-std::unordered_map<std::string, Compiled> g_cache;  // key: device ordinal + generated source
+std::unordered_map<std::string, Compiled> g_cache;  // key: device ordinal + the tape's description
 
 template <class F>
 bool sym(void *lib, const char *name, F *out) {
@@ -174,11 +174,11 @@ std::string expression(const vrhi_tape_instr &I) {
   }
 }
 
-// The kernel: 256 threads, each owning one float4 column group; blockIdx.y strides over rows, two
-// rows per trip so that the loads of both are in flight before either is used.  Row vectors are
+// The kernel: 256 threads, each owning one float4 column group; blockIdx.y strides over rows, `unroll`
+// rows per trip with the loads of all of them issued before any is used.  Row vectors are
 // loaded once per thread, column vectors once per row, scalars once per thread.  Without row or
 // column vectors the data is one long array (`flat`): the host picks a convenient row length.
-std::string generate(const vrhi_tape_params &q, bool *flat_out) {
+std::string generate(const vrhi_tape_params &q, bool *flat_out, int unroll = 2) {
   const unsigned NI = q.n_inputs, NO = q.n_outputs, NT = q.n_instr;
   const bool flat = (q.row_vector_mask | q.col_vector_mask) == 0;
   *flat_out = flat;
@@ -201,7 +201,7 @@ std::string generate(const vrhi_tape_params &q, bool *flat_out) {
   s += "}\n\nextern \"C\" __global__ void __launch_bounds__(256) vrhi_tape_kernel(";
   for (unsigned k = 0; k < NI; ++k) s += "const float *__restrict__ in" + std::to_string(k) + ", ";
   for (unsigned k = 0; k < NO; ++k) s += "float *__restrict__ out" + std::to_string(k) + ", ";
-  s += "const unsigned long long n4, const unsigned long long rows, const unsigned int cols4) {\n";
+  s += "const unsigned long long n4, const unsigned long long rows, const unsigned long long rows_full, const unsigned int cols4) {\n";
   s += "  const unsigned int c4 = blockIdx.x * 256u + threadIdx.x;\n  if (c4 >= cols4) return;\n";
   for (unsigned k = 0; k < NI; ++k) {
     if (!used[k]) continue;
@@ -209,44 +209,47 @@ std::string generate(const vrhi_tape_params &q, bool *flat_out) {
     if (shape(k) == 'r') s += "  const float4 x" + K + " = __ldg(reinterpret_cast<const float4 *>(in" + K + ") + c4);\n";
     if (shape(k) == 's') s += "  const float s" + K + " = __ldg(in" + K + ");\n  const float4 x" + K + " = make_float4(s" + K + ", s" + K + ", s" + K + ", s" + K + ");\n";
   }
-  s += "  for (unsigned long long row = blockIdx.y; row < rows; row += 2ull * gridDim.y) {\n";
-  s += "    const unsigned long long row1 = row + gridDim.y;\n";
-  s += "    const unsigned long long i0 = row * cols4 + c4, i1 = row1 * cols4 + c4;\n";
-  s += flat ? "    const bool has0 = i0 < n4, has1 = row1 < rows && i1 < n4;\n    if (!has0) break;\n"
-            : "    const bool has1 = row1 < rows;\n";
-  for (int g = 0; g < 2; ++g) {
-    const std::string G = std::to_string(g), idx = g ? "i1" : "i0", row = g ? "row1" : "row";
+  // loads of one row group, and its arithmetic and stores
+  auto loads = [&](const std::string &G, const std::string &idx, const std::string &row) {
+    std::string t;
     for (unsigned k = 0; k < NI; ++k) {
       if (!used[k]) continue;
       const std::string K = std::to_string(k), name = "x" + K + "_" + G;
-      if (shape(k) == 'f') {
-        if (g == 0) s += "    const float4 " + name + " = __ldcs(reinterpret_cast<const float4 *>(in" + K + ") + i0);\n";
-        else s += "    float4 " + name + " = x" + K + "_0;\n    if (has1) " + name + " = __ldcs(reinterpret_cast<const float4 *>(in" + K + ") + i1);\n";
-      } else if (shape(k) == 'c') {
-        if (g == 0) s += "    const float c" + K + "_0 = __ldg(in" + K + " + row);\n";
-        else s += "    const float c" + K + "_1 = has1 ? __ldg(in" + K + " + row1) : c" + K + "_0;\n";
-        s += "    const float4 " + name + " = make_float4(c" + K + "_" + G + ", c" + K + "_" + G + ", c" + K + "_" + G + ", c" + K + "_" + G + ");\n";
-      }
+      if (shape(k) == 'f') t += "      const float4 " + name + " = __ldcs(reinterpret_cast<const float4 *>(in" + K + ") + " + idx + ");\n";
+      if (shape(k) == 'c') t += "      const float c" + K + "_" + G + " = __ldg(in" + K + " + " + row + ");\n      const float4 " + name + " = make_float4(c" + K + "_" + G + ", c" + K + "_" + G + ", c" + K + "_" + G + ", c" + K + "_" + G + ");\n";
     }
-  }
-  for (int g = 0; g < 2; ++g) {
-    const std::string G = std::to_string(g), idx = g ? "i1" : "i0";
-    s += g ? "    if (has1) {\n" : "    {\n";
-    for (unsigned k = 0; k < NO; ++k) s += "      float4 o" + std::to_string(k) + ";\n";
+    return t;
+  };
+  auto work = [&](const std::string &G, const std::string &idx) {
+    std::string t = "      {\n";
+    for (unsigned k = 0; k < NO; ++k) t += "        float4 o" + std::to_string(k) + ";\n";
     for (const char *comp : {"x", "y", "z", "w"}) {
-      s += "      tape_body(";
+      t += "        tape_body(";
       for (unsigned k = 0; k < NI; ++k) {
         const std::string K = std::to_string(k);
-        if (!used[k]) s += "0.0f, ";
-        else if (shape(k) == 'r' || shape(k) == 's') s += "x" + K + "." + comp + ", ";
-        else s += "x" + K + "_" + G + "." + comp + ", ";
+        if (!used[k]) t += "0.0f, ";
+        else if (shape(k) == 'r' || shape(k) == 's') t += "x" + K + "." + comp + ", ";
+        else t += "x" + K + "_" + G + "." + comp + ", ";
       }
-      for (unsigned k = 0; k < NO; ++k) s += "o" + std::to_string(k) + "." + comp + (k + 1 < NO ? ", " : "");
-      s += ");\n";
+      for (unsigned k = 0; k < NO; ++k) t += "o" + std::to_string(k) + "." + comp + (k + 1 < NO ? ", " : "");
+      t += ");\n";
     }
-    for (unsigned k = 0; k < NO; ++k) s += "      __stcs(reinterpret_cast<float4 *>(out" + std::to_string(k) + ") + " + idx + ", o" + std::to_string(k) + ");\n";
-    s += "    }\n";
+    for (unsigned k = 0; k < NO; ++k) t += "        __stcs(reinterpret_cast<float4 *>(out" + std::to_string(k) + ") + " + idx + ", o" + std::to_string(k) + ");\n";
+    return t + "      }\n";
+  };
+  s += "  unsigned long long row = blockIdx.y;\n";
+  const std::string U = std::to_string(unroll);
+  s += "  for (; row + " + std::to_string(unroll - 1) + "ull * gridDim.y < rows_full; row += " + U + "ull * gridDim.y) {  // " + U + " complete rows per trip: all loads first\n";
+  for (int g = 0; g < unroll; ++g) {
+    const std::string G = std::to_string(g);
+    s += "      const unsigned long long row_" + G + " = row + " + G + "ull * gridDim.y, i" + G + " = row_" + G + " * cols4 + c4;\n";
   }
+  for (int g = 0; g < unroll; ++g) s += loads(std::to_string(g), "i" + std::to_string(g), "row_" + std::to_string(g));
+  for (int g = 0; g < unroll; ++g) s += work(std::to_string(g), "i" + std::to_string(g));
+  s += "  }\n";
+  s += "  for (; row < rows; row += gridDim.y) {  // rows left over; the last one may be ragged\n";
+  s += "      const unsigned long long i0 = row * cols4 + c4;\n      if (i0 >= n4) break;\n";
+  s += loads("0", "i0", "row") + work("0", "i0");
   s += "  }\n}\n";
   return s;
 }
@@ -308,10 +311,38 @@ int tape_jit_launch(vrhi_stream_t *st, const vrhi_tape_params &q, const float *c
   load_once();
   if (!g_nvrtc.ok || !g_driver.ok) return 1;
   bool flat = false;
-  const std::string src = generate(q, &flat);
-  const std::string key = std::to_string(st->dev->ordinal) + "\n" + src;
+  // About three 16-byte loads in flight per thread and six blocks per SM, all resident at once (one wave):
+  // measured on B200 with the three-input chain, 6.8 TB/s; eight blocks per SM spill into a second, partly
+  // filled wave and two rows per trip then cost 15 %.
+  int full_inputs = 0;
+  for (uint32_t k = 0; k < q.n_inputs; ++k)
+    if (!(((q.row_vector_mask | q.col_vector_mask | q.scalar_mask) >> k) & 1u)) ++full_inputs;
+  int unroll = full_inputs >= 3 ? 1 : full_inputs == 2 ? 2 : 3, blocks_per_sm = 6;
+  if (const char *e = getenv("VRHI_TAPE_UNROLL")) {  // tuning aids
+    const int u = atoi(e);
+    if (u >= 1 && u <= 8) unroll = u;
+  }
+  if (const char *e = getenv("VRHI_TAPE_BLOCKS_PER_SM")) {
+    const int b = atoi(e);
+    if (b >= 1 && b <= 32) blocks_per_sm = b;
+  }
+  // cache key: everything the generated text depends on, as raw bytes (the text itself is only built on a miss)
+  std::string key;
+  {
+    const uint32_t head[8] = {(uint32_t)st->dev->ordinal, (uint32_t)unroll, q.n_inputs, q.n_outputs, q.n_instr,
+                              q.row_vector_mask, q.col_vector_mask, q.scalar_mask};
+    key.append(reinterpret_cast<const char *>(head), sizeof head);
+    key.append(reinterpret_cast<const char *>(q.out_value), sizeof(uint32_t) * q.n_outputs);
+    for (uint32_t t = 0; t < q.n_instr; ++t) {  // field by field: padding bytes of the struct are not defined
+      const vrhi_tape_instr &I = q.instr[t];
+      const uint16_t f[4] = {I.op, I.a, I.b, I.c};
+      key.append(reinterpret_cast<const char *>(f), sizeof f);
+      key.append(reinterpret_cast<const char *>(&I.imm), sizeof I.imm);
+    }
+  }
   auto it = g_cache.find(key);
   if (it == g_cache.end()) {
+    const std::string src = generate(q, &flat, unroll);
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
     VRHI_CUDA(cudaStreamIsCapturing(st->s, &cap));
     if (cap != cudaStreamCaptureStatusNone)
@@ -326,25 +357,26 @@ int tape_jit_launch(vrhi_stream_t *st, const vrhi_tape_params &q, const float *c
   uint64_t rows = q.rows;
   uint32_t cols4 = (uint32_t)(q.cols / 4);
   if (q.cols / 4 > 0xffffffffull) return 1;
+  flat = it->second.flat;
   if (flat) {  // one long array: rows of 1024 float4 groups, the last one ragged (guarded by n4)
     cols4 = n4 < 1024 ? (uint32_t)n4 : 1024u;
     rows = (n4 + cols4 - 1) / cols4;
   }
   const unsigned gx = (cols4 + 255u) / 256u;
-  const uint64_t target = (uint64_t)st->dev->prop.multiProcessorCount * 8;
+  const uint64_t target = (uint64_t)st->dev->prop.multiProcessorCount * blocks_per_sm;
   uint64_t gy = (target + gx - 1) / gx;
-  const uint64_t row_pairs = (rows + 1) / 2;
+  const uint64_t row_pairs = (rows + unroll - 1) / unroll;
   if (gy > row_pairs) gy = row_pairs;
   if (gy > 65535) gy = 65535;
   if (gy == 0) gy = 1;
-  void *args[VRHI_TAPE_MAX_INPUTS + VRHI_TAPE_MAX_OUTPUTS + 3];
+  void *args[VRHI_TAPE_MAX_INPUTS + VRHI_TAPE_MAX_OUTPUTS + 4];
   const float *in_copy[VRHI_TAPE_MAX_INPUTS];
   float *out_copy[VRHI_TAPE_MAX_OUTPUTS];
   int n = 0;
   for (uint32_t k = 0; k < q.n_inputs; ++k) { in_copy[k] = in[k]; args[n++] = &in_copy[k]; }
   for (uint32_t k = 0; k < q.n_outputs; ++k) { out_copy[k] = out[k]; args[n++] = &out_copy[k]; }
-  uint64_t n4_arg = n4, rows_arg = rows;
-  args[n++] = &n4_arg; args[n++] = &rows_arg; args[n++] = &cols4;
+  uint64_t n4_arg = n4, rows_arg = rows, rows_full = n4 / cols4;  // rows_full: rows that hold all cols4 groups
+  args[n++] = &n4_arg; args[n++] = &rows_arg; args[n++] = &rows_full; args[n++] = &cols4;
   CUresult cr = g_driver.launch_kernel(it->second.fn, gx, (unsigned)gy, 1, 256, 1, 1, 0, reinterpret_cast<CUstream>(st->s), args, nullptr);
   if (cr != CUDA_SUCCESS) {
     const char *msg = "?";

@@ -73,7 +73,19 @@ int launch_fused_map(vrhi_stream_t *st, const ArgView *args, int n_args, const v
   const uint64_t n4 = q.n / 4;
   const int sms = st->dev->prop.multiProcessorCount;
   uint64_t want = (n4 + 255) / 256;
-  uint64_t cap = (uint64_t)sms * 8;
+  // One wave: as many blocks as are resident at once.  A grid that spills into a second, partly filled
+  // wave costs up to 20 % (measured: 5 blocks per SM 0.62 ms, 6 blocks 0.76 ms, 8 blocks 0.66 ms, 10 blocks 0.62 ms).
+  static int resident = 0;
+  if (resident == 0) {
+    int nb = 0;
+    VRHI_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, fused_map_kernel<2>, 256, 0));
+    resident = nb > 0 ? nb : 1;
+  }
+  uint64_t cap = (uint64_t)sms * resident;
+  if (const char *e = getenv("VRHI_MAP_BLOCKS_PER_SM")) {  // tuning aid
+    const int b = atoi(e);
+    if (b >= 1 && b <= 32) cap = (uint64_t)sms * b;
+  }
   unsigned grid = (unsigned)(want < cap ? (want ? want : 1) : cap);
   fused_map_kernel<2><<<grid, 256, 0, st->s>>>(
       (const float4 *)args[0].ptr, (const float4 *)args[1].ptr, (const float4 *)args[2].ptr, (float4 *)args[3].ptr, n4, q.n,

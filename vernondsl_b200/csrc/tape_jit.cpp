@@ -57,6 +57,7 @@ struct Driver {
   CUresult (*launch_kernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream, void **,
                             void **) = nullptr;
   CUresult (*get_error_string)(CUresult, const char **) = nullptr;
+  CUresult (*occupancy)(int *, CUfunction, int, size_t) = nullptr;
   bool ok = false;
 };
 
@@ -67,7 +68,8 @@ bool g_loaded = false;
 uint64_t g_compiled = 0, g_launches = 0;
 struct Compiled {
   CUfunction fn;
-  bool flat;  // no row or column vectors: the kernel indexes the data as one long array
+  bool flat;     // no row or column vectors: the kernel indexes the data as one long array
+  int resident;  // blocks of 256 threads that fit on one SM at a time
 };
 std::unordered_map<std::string, Compiled> g_cache;  // key: device ordinal + the tape's description
 
@@ -123,7 +125,8 @@ void load_once() {
   if (!g_nvrtc.ok && fallback.ok) g_nvrtc = fallback;
   Driver &d = g_driver;
   d.ok = drv("cuModuleLoadData", &d.module_load_data) && drv("cuModuleGetFunction", &d.module_get_function) &&
-         drv("cuLaunchKernel", &d.launch_kernel) && drv("cuGetErrorString", &d.get_error_string);
+         drv("cuLaunchKernel", &d.launch_kernel) && drv("cuGetErrorString", &d.get_error_string) &&
+         drv("cuOccupancyMaxActiveBlocksPerMultiprocessor", &d.occupancy);
 }
 
 int tape_arity(int op) {
@@ -317,7 +320,7 @@ int tape_jit_launch(vrhi_stream_t *st, const vrhi_tape_params &q, const float *c
   int full_inputs = 0;
   for (uint32_t k = 0; k < q.n_inputs; ++k)
     if (!(((q.row_vector_mask | q.col_vector_mask | q.scalar_mask) >> k) & 1u)) ++full_inputs;
-  int unroll = full_inputs >= 3 ? 1 : full_inputs == 2 ? 2 : 3, blocks_per_sm = 6;
+  int unroll = full_inputs >= 3 ? 1 : full_inputs == 2 ? 2 : 3, blocks_per_sm = 0;  // 0: what is resident at once, at most 6
   if (const char *e = getenv("VRHI_TAPE_UNROLL")) {  // tuning aids
     const int u = atoi(e);
     if (u >= 1 && u <= 8) unroll = u;
@@ -350,7 +353,9 @@ int tape_jit_launch(vrhi_stream_t *st, const vrhi_tape_params &q, const float *c
     VRHI_CUDA(cudaFree(nullptr));  // makes the device's primary context current for the driver calls below
     CUfunction fn = nullptr;
     VRHI_TRY(compile(st->dev, src, &fn));
-    it = g_cache.emplace(key, Compiled{fn, flat}).first;
+    int resident = 0;
+    if (g_driver.occupancy(&resident, fn, 256, 0) != CUDA_SUCCESS || resident < 1) resident = 4;
+    it = g_cache.emplace(key, Compiled{fn, flat, resident}).first;
     ++g_compiled;
   }
   const uint64_t n4 = q.rows * q.cols / 4;
@@ -363,6 +368,7 @@ int tape_jit_launch(vrhi_stream_t *st, const vrhi_tape_params &q, const float *c
     rows = (n4 + cols4 - 1) / cols4;
   }
   const unsigned gx = (cols4 + 255u) / 256u;
+  if (blocks_per_sm == 0) blocks_per_sm = it->second.resident < 6 ? it->second.resident : 6;
   const uint64_t target = (uint64_t)st->dev->prop.multiProcessorCount * blocks_per_sm;
   uint64_t gy = (target + gx - 1) / gx;
   const uint64_t row_pairs = (rows + unroll - 1) / unroll;

@@ -345,15 +345,6 @@ __global__ void __launch_bounds__(kTapeThreads) map_tape_scalar_kernel(const __g
   }
 }
 
-static int tape_arity(int op) {
-  switch (op) {
-    case VRHI_T_CONST: return 0;
-    case VRHI_T_ADD: case VRHI_T_SUB: case VRHI_T_MUL: case VRHI_T_DIV: case VRHI_T_MAX: case VRHI_T_MIN: case VRHI_T_EQ: return 2;
-    case VRHI_T_FMA: return 3;
-    default: return 1;
-  }
-}
-
 // What both execution paths require of a tape: known opcodes, operands defined before use, outputs that exist.
 static int validate_tape(const vrhi_tape_params &q) {
   const int NI = (int)q.n_inputs, NT = (int)q.n_instr;

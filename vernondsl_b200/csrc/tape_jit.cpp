@@ -129,15 +129,6 @@ void load_once() {
          drv("cuOccupancyMaxActiveBlocksPerMultiprocessor", &d.occupancy);
 }
 
-int tape_arity(int op) {
-  switch (op) {
-    case VRHI_T_CONST: return 0;
-    case VRHI_T_ADD: case VRHI_T_SUB: case VRHI_T_MUL: case VRHI_T_DIV: case VRHI_T_MAX: case VRHI_T_MIN: case VRHI_T_EQ: return 2;
-    case VRHI_T_FMA: return 3;
-    default: return 1;
-  }
-}
-
 std::string v(unsigned k) { return "v" + std::to_string(k); }
 
 // One SSA instruction as a C expression over the values v<k>.

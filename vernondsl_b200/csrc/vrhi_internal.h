@@ -121,6 +121,16 @@ int launch_widen_rows_u16(vrhi_stream_t *, const ArgView *, int, const void *, s
 int launch_gather_signal(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
 int launch_gather_pull_u16(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
 
+// Operand count of a tape operation (vrhi_tape_op).
+inline int tape_arity(int op) {
+  switch (op) {
+    case VRHI_T_CONST: return 0;
+    case VRHI_T_ADD: case VRHI_T_SUB: case VRHI_T_MUL: case VRHI_T_DIV: case VRHI_T_MAX: case VRHI_T_MIN: case VRHI_T_EQ: return 2;
+    case VRHI_T_FMA: return 3;
+    default: return 1;
+  }
+}
+
 // Run-time compiled tapes (tape_jit.cpp).  tape_jit_launch returns VRHI_OK (launched), 1 (leave it to
 // the interpreter) or an error code.
 int tape_jit_launch(vrhi_stream_t *st, const vrhi_tape_params &q, const float *const *in, float *const *out);

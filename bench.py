@@ -524,6 +524,7 @@ def main():
     # launches per step; finished slabs are exchanged while the next launch computes.  More groups shorten the last,
     # exposed push; every launch adds ramp-up and drain, most of which the two alternating compute streams hide.
     GROUPS = int(os.environ.get("VRHI_BENCH_GROUPS", "4"))
+    COMM_STREAMS = 2 if (os.environ.get("VRHI_BENCH_COMM_STREAMS", "1") == "2" and world > 2) else 1   # pushes to odd and even peers on two streams
     # Group g takes slabs g, g+GROUPS, g+2*GROUPS, ...: every group is a thin comb over the whole image, so the
     # groups cost the same although the rows near the set cost far more than the rows at the edges.
     exchange = None
@@ -537,6 +538,9 @@ def main():
             group_slabs.append(slabs)
         comm_stream = torch.cuda.Stream(device=local)
         comm_st = dev.wrap_stream(comm_stream.cuda_stream)
+        if COMM_STREAMS == 2:
+            comm_stream2 = torch.cuda.Stream(device=local)
+            comm_st2 = dev.wrap_stream(comm_stream2.cuda_stream)
         exchange = None
         if args.gather != "nccl":
             try:
@@ -594,8 +598,12 @@ def main():
                 exchange.pull(comm_st, gi, slabs)
                 mark(f"pulled {gi}", comm_stream)
             elif exchange is not None:
-                # one stream for all peers: pushes to several peers at once measured slower on this box
-                exchange.push(comm_st, slabs)      # copy engines: overlaps the next group's kernel
+                # copy engines: the pushes overlap the next group's kernel
+                if COMM_STREAMS == 2:
+                    comm_stream2.wait_event(ev)
+                    exchange.push([comm_st if k % 2 == 0 else comm_st2 for k in range(world - 1)], slabs)
+                else:
+                    exchange.push(comm_st, slabs)
                 mark(f"pushed {gi}", comm_stream)
                 if pushing16:
                     # arrival on a third stream, so that the next push does not queue behind it: the all-reduce and
@@ -603,6 +611,10 @@ def main():
                     pev = torch.cuda.Event()
                     pev.record(comm_stream)
                     arrive_stream.wait_event(pev)
+                    if COMM_STREAMS == 2:
+                        pev2 = torch.cuda.Event()
+                        pev2.record(comm_stream2)
+                        arrive_stream.wait_event(pev2)
                     exchange.finish(arrive_stream, arrive_st, slabs)
                     mark(f"widened {gi}", arrive_stream)
             else:
@@ -618,9 +630,13 @@ def main():
             if pushing16:
                 tstream.wait_stream(arrive_stream)
             else:
+                if COMM_STREAMS == 2:
+                    comm_stream.wait_stream(comm_stream2)
                 exchange.finish(comm_stream)
             mark("exchange complete", comm_stream)
             tstream.wait_stream(comm_stream)
+            if COMM_STREAMS == 2:
+                tstream.wait_stream(comm_stream2)
         else:
             with torch.cuda.stream(tstream):
                 for w in works:

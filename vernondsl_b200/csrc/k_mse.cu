@@ -13,8 +13,6 @@
 // saturates (1 - y*y evaluated from a rounded y loses it).
 #include <cstring>
 
-#include <cstdlib>
-
 #include "vrhi_internal.h"
 
 namespace vrhi {
@@ -127,72 +125,6 @@ __global__ void __launch_bounds__(256) mse_bwd_kernel(const float *__restrict__ 
       for (int k = 0; k < nc; ++k) db_partial[(uint64_t)blockIdx.y * cols + c0 + k] = gg[k];
     }
   }
-  const float bl = block_sum_256(lsum, smem);
-  if (threadIdx.x == 0) loss_partial[(uint64_t)blockIdx.y * gridDim.x + blockIdx.x] = bl;
-}
-
-// The backward with its loads staged through shared memory: every thread keeps a private ring of
-// STAGES rows (three 16-byte cp.async copies per row) ahead of the row it is working on.  The ring
-// is used like extra registers: a thread only ever reads what it copied itself, so no block-wide
-// synchronisation is needed, and the loads in flight no longer depend on where the thread is in
-// its arithmetic (43 instructions per element).  Same order of operations as mse_bwd_kernel: same bits.
-__device__ __forceinline__ void mse_cp_async_16(void *smem_dst, const void *gmem_src) {
-  const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
-}
-
-template <int STAGES>
-__global__ void __launch_bounds__(256) mse_bwd_pipe_kernel(const float *__restrict__ W, const float *__restrict__ X,
-                                                           const float *__restrict__ B, const float *__restrict__ Tt,
-                                                           float *__restrict__ dW, float *__restrict__ dX,
-                                                           float *__restrict__ db_partial, float *__restrict__ loss_partial,
-                                                           uint64_t rows, uint64_t cols, float inv) {
-  extern __shared__ float4 ring[];  // [STAGES][3][256]
-  __shared__ float smem[8];
-  const uint64_t c0 = ((uint64_t)blockIdx.x * 256 + threadIdx.x) * 4;
-  float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
-  float lsum = 0.f;
-  if (c0 < cols) {
-    const uint64_t cols4 = cols / 4, cg = c0 / 4;
-    const float4 b = *reinterpret_cast<const float4 *>(B + c0);
-    const float4 *w4 = reinterpret_cast<const float4 *>(W) + cg;
-    const float4 *x4 = reinterpret_cast<const float4 *>(X) + cg;
-    const float4 *t4 = reinterpret_cast<const float4 *>(Tt) + cg;
-    float4 *dw4 = reinterpret_cast<float4 *>(dW) + cg;
-    float4 *dx4 = reinterpret_cast<float4 *>(dX) + cg;
-    const uint64_t step = gridDim.y;
-    float4 *mine = ring + threadIdx.x;
-    uint64_t ahead = blockIdx.y;
-    auto issue = [&](int stage) {
-      if (ahead < rows) {
-        const uint64_t o = ahead * cols4;
-        mse_cp_async_16(mine + (stage * 3 + 0) * 256, w4 + o);
-        mse_cp_async_16(mine + (stage * 3 + 1) * 256, x4 + o);
-        mse_cp_async_16(mine + (stage * 3 + 2) * 256, t4 + o);
-      }
-      asm volatile("cp.async.commit_group;" ::: "memory");  // one group per row, empty past the end: the count stays uniform
-      ahead += step;
-    };
-#pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) issue(s);
-    int stage = 0;
-    for (uint64_t r = blockIdx.y; r < rows; r += step) {
-      issue(stage == 0 ? STAGES - 1 : stage - 1);  // the slot freed by the previous row
-      asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 1) : "memory");
-      const float4 wa = mine[(stage * 3 + 0) * 256], xa = mine[(stage * 3 + 1) * 256], ta = mine[(stage * 3 + 2) * 256];
-      const uint64_t o0 = r * cols4;
-      float4 ow, ox;
-      bwd_one(wa.x, xa.x, b.x, ta.x, inv, ow.x, ox.x, g.x, lsum);
-      bwd_one(wa.y, xa.y, b.y, ta.y, inv, ow.y, ox.y, g.y, lsum);
-      bwd_one(wa.z, xa.z, b.z, ta.z, inv, ow.z, ox.z, g.z, lsum);
-      bwd_one(wa.w, xa.w, b.w, ta.w, inv, ow.w, ox.w, g.w, lsum);
-      __stcs(dw4 + o0, ow);
-      __stcs(dx4 + o0, ox);
-      stage = stage + 1 == STAGES ? 0 : stage + 1;
-    }
-    *reinterpret_cast<float4 *>(db_partial + (uint64_t)blockIdx.y * cols + c0) = g;
-  }
-  asm volatile("cp.async.wait_group 0;" ::: "memory");
   const float bl = block_sum_256(lsum, smem);
   if (threadIdx.x == 0) loss_partial[(uint64_t)blockIdx.y * gridDim.x + blockIdx.x] = bl;
 }
@@ -327,19 +259,7 @@ int launch_mse_tanh_bwd(vrhi_stream_t *st, const ArgView *args, int n_args, cons
   dim3 grid(pl.gx, pl.gy);
   const float *W = (const float *)args[0].ptr, *X = (const float *)args[1].ptr, *B = (const float *)args[2].ptr, *T = (const float *)args[3].ptr;
   const float inv = (float)(2.0 / pl.denom);
-  int stages = 0;
-  if (const char *e = getenv("VRHI_MSE_STAGES")) stages = atoi(e);  // 0: loads straight into registers; 3 or 4: staged through shared memory
-  const bool aligned = ((uintptr_t)W % 16 == 0) && ((uintptr_t)X % 16 == 0) && ((uintptr_t)T % 16 == 0);
-  if (pl.vec && aligned && (stages == 3 || stages == 4)) {
-    const size_t smem = (size_t)stages * 3 * 256 * sizeof(float4);
-    if (stages == 3) {
-      VRHI_CUDA(cudaFuncSetAttribute(mse_bwd_pipe_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      mse_bwd_pipe_kernel<3><<<grid, 256, smem, st->s>>>(W, X, B, T, (float *)args[4].ptr, (float *)args[5].ptr, db_partial, loss_partial, pl.rows, pl.cols, inv);
-    } else {
-      VRHI_CUDA(cudaFuncSetAttribute(mse_bwd_pipe_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      mse_bwd_pipe_kernel<4><<<grid, 256, smem, st->s>>>(W, X, B, T, (float *)args[4].ptr, (float *)args[5].ptr, db_partial, loss_partial, pl.rows, pl.cols, inv);
-    }
-  } else if (pl.vec) mse_bwd_kernel<true><<<grid, 256, 0, st->s>>>(W, X, B, T, (float *)args[4].ptr, (float *)args[5].ptr, db_partial, loss_partial, pl.rows, pl.cols, inv);
+  if (pl.vec) mse_bwd_kernel<true><<<grid, 256, 0, st->s>>>(W, X, B, T, (float *)args[4].ptr, (float *)args[5].ptr, db_partial, loss_partial, pl.rows, pl.cols, inv);
   else mse_bwd_kernel<false><<<grid, 256, 0, st->s>>>(W, X, B, T, (float *)args[4].ptr, (float *)args[5].ptr, db_partial, loss_partial, pl.rows, pl.cols, inv);
   VRHI_TRY(post_launch(st, "mse_tanh_bwd"));
   VRHI_TRY(col_finalize(st, db_partial, (float *)args[6].ptr, pl.gy, pl.cols, 1.0f));

@@ -331,6 +331,8 @@ typedef struct vrhi_tape_params {
   uint32_t out_value[VRHI_TAPE_MAX_OUTPUTS]; /* value index stored to output k */
   vrhi_tape_instr instr[VRHI_TAPE_MAX_INSTR];
   uint32_t flags; /* VRHI_TAPE_FLAG_* */
+  uint32_t colsum_mask; /* bit k: output k is not stored; its column sums are: the argument is a [cols] array.
+                           Needs the compiled path (VRHI_ERR_UNSUPPORTED otherwise). Deterministic: fixed order. */
 } vrhi_tape_params;
 /* A tape normally runs as a kernel compiled for it at first use (NVRTC, cached; values in
  * registers, HBM-bound).  This flag, or VRHI_TAPE_JIT=0 in the environment, selects the

@@ -212,3 +212,33 @@ def test_compiled_tape_covers_every_operation_and_is_cached(dev, stream):
     stream.check()
     assert np.array_equal(again[0].download(), o1) and np.array_equal(again[1].download(), o2)
     seq.close()
+
+
+def test_tape_output_summed_over_columns_inside_the_kernel(dev, stream):
+    """An output flagged col_sum is never stored in full: the compiled kernel adds it up column by column
+    (fixed order: the same bits on every run) and a [cols] vector comes out."""
+    rows, cols = 301, 1024
+    rng = np.random.default_rng(8)
+    w = rng.standard_normal((rows, cols)).astype(np.float32)
+    x = rng.standard_normal((rows, cols)).astype(np.float32)
+    b = rng.standard_normal(cols).astype(np.float32)
+    W, X, B = dev.from_numpy(w), dev.from_numpy(x), dev.from_numpy(b)
+    t = ops.Tape(3, row_vectors=[2])
+    u = t.op("tanh", t.op("fma", t.input(0), t.input(1), t.input(2)))
+    t.output(u)
+    t.output(t.op("mul", u, t.input(0)), col_sum=True)
+    full, sums = dev.empty((rows, cols), np.float32), dev.empty((cols,), np.float32)
+    ops.map_tape(stream, t, [W, X, B], [full, sums], rows, cols)
+    stream.check()
+    want_u = np.tanh(w.astype(np.float64) * x + b[None, :])
+    got_u, got_s = full.download(), sums.download()
+    assert np.abs(got_u - want_u).max() < 1e-6
+    want_s = (want_u * w).sum(axis=0)
+    assert np.abs(got_s - want_s).max() <= 1e-5 * np.abs(want_u * w).sum(axis=0).max()
+    again = dev.empty((cols,), np.float32)
+    ops.map_tape(stream, t, [W, X, B], [full, again], rows, cols)
+    stream.check()
+    assert np.array_equal(again.download().view(np.uint32), got_s.view(np.uint32))     # deterministic
+    with pytest.raises(L.VrhiError) as e:                                               # the interpreter has no such epilogue
+        ops.map_tape(stream, t, [W, X, B], [full, again], rows, cols, interpret=True)
+    assert e.value.status == L.ERR_UNSUPPORTED

@@ -66,7 +66,15 @@ def _broadcasts():
     return t
 
 
-@pytest.mark.parametrize("make", [_chain, _every_op, _broadcasts])
+def _column_sum():
+    t = ops.Tape(3, row_vectors=[2])
+    u = t.op("tanh", t.op("fma", t.input(0), t.input(1), t.input(2)))
+    t.output(u)
+    t.output(t.op("mul", u, t.input(0)), col_sum=True)               # summed over the rows inside the kernel
+    return t
+
+
+@pytest.mark.parametrize("make", [_chain, _every_op, _broadcasts, _column_sum])
 def test_generated_source_compiles_for_sm_100a(make):
     src = ops.tape_source(make())
     assert 'extern "C" __global__' in src and "tape_body" in src

@@ -97,7 +97,7 @@ class TapeParams(C.Structure):
                 ("n_instr", C.c_uint32), ("rows", C.c_uint64), ("cols", C.c_uint64),
                 ("row_vector_mask", C.c_uint32), ("col_vector_mask", C.c_uint32),
                 ("scalar_mask", C.c_uint32), ("out_value", C.c_uint32 * TAPE_MAX_OUTPUTS),
-                ("instr", TapeInstr * TAPE_MAX_INSTR), ("flags", C.c_uint32)]
+                ("instr", TapeInstr * TAPE_MAX_INSTR), ("flags", C.c_uint32), ("colsum_mask", C.c_uint32)]
 
 
 TAPE_FLAG_INTERPRET = 1

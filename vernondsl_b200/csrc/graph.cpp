@@ -281,6 +281,7 @@ struct Planner {
   std::vector<int> stage;
   std::vector<vrhi_buffer> storage;  // node -> buffer holding it (leaves and roots)
   std::map<int, int> op_ids;
+  std::map<int, int> folded;  // elementwise root -> the column-sum node that is its only reader (summed inside the map kernel)
   int next_order = 0;
 
   bool leaf(int i) const {
@@ -405,10 +406,18 @@ struct Planner {
     s.stage = st;
     s.order = next_order++;
     for (int l : leaf_list) s.args.push_back(arg_of(l, VRHI_INPUT));
-    for (int r : roots) s.args.push_back(arg_of(r, VRHI_OUTPUT));
+    for (size_t k = 0; k < roots.size(); ++k) {
+      auto f = folded.find(roots[k]);
+      if (f == folded.end()) {
+        s.args.push_back(arg_of(roots[k], VRHI_OUTPUT));
+      } else {  // the map kernel writes the column sums straight into the reduction's array
+        P.colsum_mask |= 1u << k;
+        s.args.push_back(arg_of(f->second, VRHI_OUTPUT));
+      }
+    }
     std::ostringstream text;
     bool special = false;
-    if (!(g->flags & 1u) && shape == VRHI_SHAPE_FULL && roots.size() == 1 && leaf_list.size() == 3 && P.row_vector_mask == 0 && P.col_vector_mask == 0 && P.scalar_mask == 0) {
+    if (!(g->flags & 1u) && P.colsum_mask == 0 && shape == VRHI_SHAPE_FULL && roots.size() == 1 && leaf_list.size() == 3 && P.row_vector_mask == 0 && P.col_vector_mask == 0 && P.scalar_mask == 0) {
       // the map-workload chain, operands of commutative nodes in any order
       special = match_chain(roots[0], leaf_list, &s);
     }
@@ -419,6 +428,8 @@ struct Planner {
       s.params.assign((unsigned char *)&P, (unsigned char *)&P + sizeof P);
       text << "map_tape    stage " << st << " shape=" << shape_name(shape) << " inputs=" << P.n_inputs << " outputs=" << P.n_outputs
            << " instr=" << P.n_instr;
+      for (uint32_t k = 0; k < P.n_outputs; ++k)
+        if ((P.colsum_mask >> k) & 1u) text << " (output " << k << ": col_sum folded into the kernel)";
     }
     s.text = text.str();
     g->steps.push_back(s);
@@ -714,8 +725,30 @@ struct Planner {
           if (!storage[i]) VRHI_TRY(temp_for(i));
         }
       }
+      // A full-size elementwise value whose only reader is a column sum is never written: the map kernel
+      // that computes it adds it up column by column (compiled tapes only, columns a multiple of 4).
+      folded.clear();
+      if (g->cols % 4 == 0 && tape_jit_available()) {
+        // readers that need the value in memory: reductions and softmax (elementwise readers recompute it
+        // inside their own kernel from the leaves)
+        std::vector<int> readers(N, 0);
+        for (int i = 0; i < N; ++i) {
+          if (!live[i]) continue;
+          const Node &n = g->nodes[i];
+          if (n.kind != K_REDUCE && n.kind != K_SOFTMAX) continue;
+          if (n.a >= 0) ++readers[n.a];
+        }
+        for (int i = 0; i < N; ++i) {
+          const Node &n = g->nodes[i];
+          if (!live[i] || n.kind != K_REDUCE || n.op != VRHI_R_COL_SUM) continue;
+          const int a = n.a;
+          if (!is_elementwise(g->nodes[a].kind) || g->nodes[a].shape != VRHI_SHAPE_FULL) continue;
+          if (readers[a] != 1 || seen_out.count(a) || storage[a]) continue;
+          folded[a] = i;
+        }
+      }
       for (int i = 0; i < N; ++i)
-        if (live[i] && root[i] && !storage[i]) VRHI_TRY(temp_for(i));
+        if (live[i] && root[i] && !storage[i] && !folded.count(i)) VRHI_TRY(temp_for(i));
       for (int i = 0; i < N; ++i)
         if (live[i]) node_stage(i);
       // group roots by (shape, stage), merging those that share a leaf or interior node
@@ -756,7 +789,11 @@ struct Planner {
         VRHI_TRY(emit_map(group, leaves, st));
       }
       for (int i = 0; i < N; ++i)
-        if (live[i] && (g->nodes[i].kind == K_REDUCE || g->nodes[i].kind == K_SOFTMAX)) VRHI_TRY(emit_reduce(i));
+        if (live[i] && (g->nodes[i].kind == K_REDUCE || g->nodes[i].kind == K_SOFTMAX)) {
+          bool in_kernel = false;
+          for (auto &f : folded) in_kernel = in_kernel || f.second == i;
+          if (!in_kernel) VRHI_TRY(emit_reduce(i));
+        }
       std::stable_sort(g->steps.begin(), g->steps.end(), [](const Step &x, const Step &y) {
         return x.stage != y.stage ? x.stage < y.stage : x.order < y.order;
       });

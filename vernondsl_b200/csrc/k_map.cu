@@ -474,7 +474,8 @@ int launch_map_tape(vrhi_stream_t *st, const ArgView *args, int n_args, const vo
   }
   for (uint32_t k = 0; k < q.n_outputs; ++k) {
     const ArgView &o = args[q.n_inputs + k];
-    if (o.bytes < n * 4) return fail(VRHI_ERR_SIZE, "map_tape: output %u holds %llu bytes, %llu needed", k, (unsigned long long)o.bytes, (unsigned long long)n * 4);
+    const uint64_t out_bytes = ((q.colsum_mask >> k) & 1u) ? q.cols * 4 : n * 4;
+    if (o.bytes < out_bytes) return fail(VRHI_ERR_SIZE, "map_tape: output %u holds %llu bytes, %llu needed", k, (unsigned long long)o.bytes, (unsigned long long)out_bytes);
     if (!writable(o)) return fail(VRHI_ERR_INVALID, "map_tape: output %u is read-only (class %s)", k, vrhi_arg_class_name(o.buf_cls));
     T.out[k] = (float *)o.ptr;
   }
@@ -484,6 +485,7 @@ int launch_map_tape(vrhi_stream_t *st, const ArgView *args, int n_args, const vo
     const int rc = tape_jit_launch(st, q, T.in, T.out);
     if (rc == VRHI_OK) return post_launch(st, "map_tape (compiled)");
     if (rc != 1) return rc;
+    if (q.colsum_mask) return fail(VRHI_ERR_UNSUPPORTED, "map_tape: column-summed outputs need the compiled path (run-time compiler present, columns a multiple of 4, 16-byte aligned arrays)");
   }
   const int slot_capacity = kTapeSlotBytes / (kTapeThreads * (int)sizeof(float4));  // 24 slots of one group
   VRHI_TRY(plan_tape(q, &T, slot_capacity));

@@ -174,7 +174,7 @@ std::string expression(const vrhi_tape_instr &I) {
 // column vectors the data is one long array (`flat`): the host picks a convenient row length.
 std::string generate(const vrhi_tape_params &q, bool *flat_out, int unroll = 2) {
   const unsigned NI = q.n_inputs, NO = q.n_outputs, NT = q.n_instr;
-  const bool flat = (q.row_vector_mask | q.col_vector_mask) == 0;
+  const bool flat = (q.row_vector_mask | q.col_vector_mask) == 0 && q.colsum_mask == 0;  // column sums need a thread to keep its columns
   *flat_out = flat;
   std::vector<bool> used(NI + NT, false);
   for (unsigned t = 0; t < NT; ++t) {
@@ -228,9 +228,17 @@ std::string generate(const vrhi_tape_params &q, bool *flat_out, int unroll = 2) 
       for (unsigned k = 0; k < NO; ++k) t += "o" + std::to_string(k) + "." + comp + (k + 1 < NO ? ", " : "");
       t += ");\n";
     }
-    for (unsigned k = 0; k < NO; ++k) t += "        __stcs(reinterpret_cast<float4 *>(out" + std::to_string(k) + ") + " + idx + ", o" + std::to_string(k) + ");\n";
+    for (unsigned k = 0; k < NO; ++k) {
+      const std::string K = std::to_string(k);
+      if ((q.colsum_mask >> k) & 1u)  // rows are visited in a fixed order: the sum does not depend on scheduling
+        t += "        acc" + K + ".x += o" + K + ".x; acc" + K + ".y += o" + K + ".y; acc" + K + ".z += o" + K + ".z; acc" + K + ".w += o" + K + ".w;\n";
+      else
+        t += "        __stcs(reinterpret_cast<float4 *>(out" + K + ") + " + idx + ", o" + K + ");\n";
+    }
     return t + "      }\n";
   };
+  for (unsigned k = 0; k < NO; ++k)
+    if ((q.colsum_mask >> k) & 1u) s += "  float4 acc" + std::to_string(k) + " = make_float4(0.f, 0.f, 0.f, 0.f);\n";
   s += "  unsigned long long row = blockIdx.y;\n";
   const std::string U = std::to_string(unroll);
   s += "  for (; row + " + std::to_string(unroll - 1) + "ull * gridDim.y < rows_full; row += " + U + "ull * gridDim.y) {  // " + U + " complete rows per trip: all loads first\n";
@@ -244,7 +252,12 @@ std::string generate(const vrhi_tape_params &q, bool *flat_out, int unroll = 2) 
   s += "  for (; row < rows; row += gridDim.y) {  // rows left over; the last one may be ragged\n";
   s += "      const unsigned long long i0 = row * cols4 + c4;\n      if (i0 >= n4) break;\n";
   s += loads("0", "i0", "row") + work("0", "i0");
-  s += "  }\n}\n";
+  s += "  }\n";
+  // column-summed outputs: this block's partial row, [gridDim.y][cols]; a second kernel adds the partial rows
+  for (unsigned k = 0; k < NO; ++k)
+    if ((q.colsum_mask >> k) & 1u)
+      s += "  reinterpret_cast<float4 *>(out" + std::to_string(k) + ")[(unsigned long long)blockIdx.y * cols4 + c4] = acc" + std::to_string(k) + ";\n";
+  s += "}\n";
   return s;
 }
 
@@ -327,6 +340,7 @@ int tape_jit_launch(vrhi_stream_t *st, const vrhi_tape_params &q, const float *c
                               q.row_vector_mask, q.col_vector_mask, q.scalar_mask};
     key.append(reinterpret_cast<const char *>(head), sizeof head);
     key.append(reinterpret_cast<const char *>(q.out_value), sizeof(uint32_t) * q.n_outputs);
+    key.append(reinterpret_cast<const char *>(&q.colsum_mask), sizeof q.colsum_mask);
     for (uint32_t t = 0; t < q.n_instr; ++t) {  // field by field: padding bytes of the struct are not defined
       const vrhi_tape_instr &I = q.instr[t];
       const uint16_t f[4] = {I.op, I.a, I.b, I.c};
@@ -371,7 +385,15 @@ int tape_jit_launch(vrhi_stream_t *st, const vrhi_tape_params &q, const float *c
   float *out_copy[VRHI_TAPE_MAX_OUTPUTS];
   int n = 0;
   for (uint32_t k = 0; k < q.n_inputs; ++k) { in_copy[k] = in[k]; args[n++] = &in_copy[k]; }
-  for (uint32_t k = 0; k < q.n_outputs; ++k) { out_copy[k] = out[k]; args[n++] = &out_copy[k]; }
+  char *scratch = nullptr;
+  if (q.colsum_mask) {
+    const size_t per_output = (size_t)gy * q.cols * sizeof(float);
+    VRHI_TRY(stream_arena(st, per_output * VRHI_TAPE_MAX_OUTPUTS, nullptr, &scratch));
+  }
+  for (uint32_t k = 0; k < q.n_outputs; ++k) {
+    out_copy[k] = ((q.colsum_mask >> k) & 1u) ? reinterpret_cast<float *>(scratch + (size_t)k * gy * q.cols * sizeof(float)) : out[k];
+    args[n++] = &out_copy[k];
+  }
   uint64_t n4_arg = n4, rows_arg = rows, rows_full = n4 / cols4;  // rows_full: rows that hold all cols4 groups
   args[n++] = &n4_arg; args[n++] = &rows_arg; args[n++] = &rows_full; args[n++] = &cols4;
   CUresult cr = g_driver.launch_kernel(it->second.fn, gx, (unsigned)gy, 1, 256, 1, 1, 0, reinterpret_cast<CUstream>(st->s), args, nullptr);
@@ -381,7 +403,18 @@ int tape_jit_launch(vrhi_stream_t *st, const vrhi_tape_params &q, const float *c
     return fail(VRHI_ERR_CUDA, "launch of a compiled tape failed: %s", msg);
   }
   ++g_launches;
+  for (uint32_t k = 0; k < q.n_outputs; ++k)
+    if ((q.colsum_mask >> k) & 1u) VRHI_TRY(col_finalize(st, out_copy[k], out[k], (uint32_t)gy, q.cols, 1.0f));
   return VRHI_OK;
+}
+
+bool tape_jit_available() {
+  if (const char *e = getenv("VRHI_TAPE_JIT")) {
+    if (atoi(e) == 0) return false;
+  }
+  std::lock_guard<std::mutex> lock(g_mu);
+  load_once();
+  return g_nvrtc.ok && g_driver.ok;
 }
 
 void tape_jit_counters(uint64_t *compiled, uint64_t *launches, int *compiler_version, int *built_version) {

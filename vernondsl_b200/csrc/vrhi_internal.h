@@ -134,6 +134,8 @@ inline int tape_arity(int op) {
 // Run-time compiled tapes (tape_jit.cpp).  tape_jit_launch returns VRHI_OK (launched), 1 (leave it to
 // the interpreter) or an error code.
 int tape_jit_launch(vrhi_stream_t *st, const vrhi_tape_params &q, const float *const *in, float *const *out);
+bool tape_jit_available();
+int col_finalize(vrhi_stream_t *st, const float *partial, float *out, uint32_t groups, uint64_t cols, float scale);
 void tape_jit_counters(uint64_t *compiled, uint64_t *launches, int *compiler_version, int *built_version);
 std::string tape_jit_source(const vrhi_tape_params &q);
 

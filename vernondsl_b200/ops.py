@@ -147,7 +147,11 @@ class Tape:
         self.instr.append((L.T[name], a, b, c, 0.0))
         return self.n_inputs + len(self.instr) - 1
 
-    def output(self, value: int) -> None:
+    def output(self, value: int, col_sum: bool = False) -> None:
+        """Store ``value`` to the next output array; with ``col_sum`` the output array is a [cols] vector that
+        receives the column sums of the value instead (the full-size value is never written)."""
+        if col_sum:
+            self.colsum_mask = getattr(self, "colsum_mask", 0) | (1 << len(self.outputs))
         self.outputs.append(value)
 
     def params(self, rows: int, cols: int) -> L.TapeParams:
@@ -158,6 +162,7 @@ class Tape:
         p.n_inputs, p.n_outputs, p.n_instr = self.n_inputs, len(self.outputs), len(self.instr)
         p.rows, p.cols = int(rows), int(cols)
         p.row_vector_mask, p.col_vector_mask, p.scalar_mask = self.row_mask, self.col_mask, self.scalar_mask
+        p.colsum_mask = getattr(self, "colsum_mask", 0)
         for k, v in enumerate(self.outputs):
             p.out_value[k] = v
         for k, (op, a, b, c, imm) in enumerate(self.instr):

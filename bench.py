@@ -318,6 +318,15 @@ def other_workloads(dev, st, torch, hbm_peak, peak_kind, fp32_peak):
          f"graph: {g.kernel_count()} kernels", ms, 20 * R * Cc + 8 * Cc,
          "algorithmic bytes as above; where the column sum is folded into the tape kernel the plan is one step (plus the finalize of the partial rows)")
     g.close()
+    g = Graph(dev, R, Cc, specialize=False)
+    nW, nx, nt = g.input(bW), g.input(bx), g.input(bt_)
+    nb = g.input(bb, L.SHAPE_ROWVEC)
+    g.output(g.mean(g.square(g.tanh(nW * nx + nb) - nt)), bl)
+    g.compile()
+    ms = time_launches(dev, st, lambda: g.launch(st), 10)
+    line("the loss alone from the execution graph without the hand-written kernel", f"graph: {g.kernel_count()} kernels", ms, 12 * R * Cc,
+         "the squared error is summed inside the compiled tape; a flat sum and a scale follow")
+    g.close()
     return out
 
 

@@ -281,7 +281,12 @@ struct Planner {
   std::vector<int> stage;
   std::vector<vrhi_buffer> storage;  // node -> buffer holding it (leaves and roots)
   std::map<int, int> op_ids;
-  std::map<int, int> folded;  // elementwise root -> the column-sum node that is its only reader (summed inside the map kernel)
+  // Elementwise roots that are summed over the rows inside the map kernel instead of being stored:
+  // root -> the [cols] array that receives the sums.  `folded_nodes`: column-sum nodes that need no
+  // step of their own; `folded_mid`: full sums / means whose first half (the column sum) is done.
+  std::map<int, vrhi_buffer> folded;
+  std::set<int> folded_nodes;
+  std::map<int, vrhi_buffer> folded_mid;
   int next_order = 0;
 
   bool leaf(int i) const {
@@ -412,7 +417,9 @@ struct Planner {
         s.args.push_back(arg_of(roots[k], VRHI_OUTPUT));
       } else {  // the map kernel writes the column sums straight into the reduction's array
         P.colsum_mask |= 1u << k;
-        s.args.push_back(arg_of(f->second, VRHI_OUTPUT));
+        vrhi_arg a{};
+        a.buffer = f->second; a.offset = 0; a.bytes = g->cols * 4; a.arg_class = VRHI_OUTPUT;
+        s.args.push_back(a);
       }
     }
     std::ostringstream text;
@@ -642,7 +649,12 @@ struct Planner {
         vrhi_arg flat_in = arg_of(n.a, VRHI_INPUT);
         uint64_t len = g->elems(in_shape);
         vrhi_arg dst = arg_of(i, VRHI_OUTPUT);
-        if (in_shape == VRHI_SHAPE_FULL) {
+        auto mid_it = folded_mid.find(i);
+        if (mid_it != folded_mid.end()) {  // the map kernel already left the column sums here
+          vrhi_arg mid{}; mid.buffer = mid_it->second; mid.bytes = g->cols * 4; mid.arg_class = VRHI_INPUT;
+          flat_in = mid;
+          len = g->cols;
+        } else if (in_shape == VRHI_SHAPE_FULL) {
           vrhi_buffer t = nullptr;
           VRHI_TRY(vrhi_buffer_create(g->dev, g->cols * 4, VRHI_STORAGE_BUFFER, &t));
           g->temps.push_back(t);
@@ -727,7 +739,7 @@ struct Planner {
       }
       // A full-size elementwise value whose only reader is a column sum is never written: the map kernel
       // that computes it adds it up column by column (compiled tapes only, columns a multiple of 4).
-      folded.clear();
+      folded.clear(); folded_nodes.clear(); folded_mid.clear();
       if (g->cols % 4 == 0 && tape_jit_available()) {
         // readers that need the value in memory: reductions and softmax (elementwise readers recompute it
         // inside their own kernel from the leaves)
@@ -740,11 +752,21 @@ struct Planner {
         }
         for (int i = 0; i < N; ++i) {
           const Node &n = g->nodes[i];
-          if (!live[i] || n.kind != K_REDUCE || n.op != VRHI_R_COL_SUM) continue;
+          if (!live[i] || n.kind != K_REDUCE) continue;
+          if (n.op != VRHI_R_COL_SUM && n.op != VRHI_R_SUM_ALL && n.op != VRHI_R_MEAN_ALL) continue;
           const int a = n.a;
           if (!is_elementwise(g->nodes[a].kind) || g->nodes[a].shape != VRHI_SHAPE_FULL) continue;
-          if (readers[a] != 1 || seen_out.count(a) || storage[a]) continue;
-          folded[a] = i;
+          if (readers[a] != 1 || seen_out.count(a) || storage[a] || folded.count(a)) continue;
+          if (n.op == VRHI_R_COL_SUM) {
+            folded[a] = storage[i];
+            folded_nodes.insert(i);
+          } else {  // a full sum is a column sum followed by a flat sum: the first half goes into the kernel
+            vrhi_buffer t = nullptr;
+            VRHI_TRY(vrhi_buffer_create(g->dev, g->cols * 4, VRHI_STORAGE_BUFFER, &t));
+            g->temps.push_back(t);
+            folded[a] = t;
+            folded_mid[i] = t;
+          }
         }
       }
       for (int i = 0; i < N; ++i)
@@ -790,9 +812,7 @@ struct Planner {
       }
       for (int i = 0; i < N; ++i)
         if (live[i] && (g->nodes[i].kind == K_REDUCE || g->nodes[i].kind == K_SOFTMAX)) {
-          bool in_kernel = false;
-          for (auto &f : folded) in_kernel = in_kernel || f.second == i;
-          if (!in_kernel) VRHI_TRY(emit_reduce(i));
+          if (!folded_nodes.count(i)) VRHI_TRY(emit_reduce(i));
         }
       std::stable_sort(g->steps.begin(), g->steps.end(), [](const Step &x, const Step &y) {
         return x.stage != y.stage ? x.stage < y.stage : x.order < y.order;

@@ -20,75 +20,9 @@
 #include <type_traits>
 #include <unordered_map>
 
-#include "vrhi_internal.h"
+#include "escape_common.cuh"
 
 namespace vrhi {
-
-struct EscapeDev {
-  uint32_t width, height, max_iter;
-  float x0, y0, dx, dy, cr, ci, bound, color_scale;
-  uint32_t chunk_rows, chunk_first, chunk_step;
-  uint32_t rows_owned;       // rows this launch computes
-  uint32_t tiles_per_row;    // ceil(width / 32)
-  uint32_t batch_tiles;      // tiles per stolen batch (a batch never straddles a row)
-  uint32_t batches_per_row;
-  uint32_t n_batches;
-  uint32_t transposed;       // 1: the row coordinate is the real part and the column coordinate the imaginary part
-};
-
-// Step primitives.  EXACT keeps a = zr*zr and b = zi*zi alongside z so that one update costs six
-// instructions; FAST lets multiply-adds fuse (four instructions per update) and is a different,
-// equally well-defined rounding sequence:
-//     test  s = fma(zi, zi, zr*zr)        update  zi' = fma(zr+zr, zi, ci);  zr' = fma(zr, zr, fma(-zi, zi, cr))
-template <int MODE>
-__device__ __forceinline__ void z_squares(float zr, float zi, float &a, float &b) {
-  if (MODE == VRHI_ESCAPE_EXACT) { a = __fmul_rn(zr, zr); b = __fmul_rn(zi, zi); }
-}
-template <int MODE>
-__device__ __forceinline__ float z_norm2(float zr, float zi, float a, float b) {
-  if (MODE == VRHI_ESCAPE_EXACT) return __fadd_rn(a, b);
-  return __fmaf_rn(zi, zi, __fmul_rn(zr, zr));
-}
-template <int MODE>
-__device__ __forceinline__ void z_advance(float &zr, float &zi, float &a, float &b, float cr, float ci) {
-  if (MODE == VRHI_ESCAPE_EXACT) {
-    const float t = __fmul_rn(zr, zi);
-    zi = __fmaf_rn(2.0f, t, ci);
-    zr = __fadd_rn(__fsub_rn(a, b), cr);
-    a = __fmul_rn(zr, zr);
-    b = __fmul_rn(zi, zi);
-  } else {
-    const float nzi = __fmaf_rn(__fadd_rn(zr, zr), zi, ci);
-    zr = __fmaf_rn(zr, zr, __fmaf_rn(-zi, zi, cr));
-    zi = nzi;
-  }
-}
-
-template <int TEST>
-__device__ __forceinline__ bool escaped(float s, float bound) {
-  if (TEST == VRHI_TEST_NORM2_GT) return !(s <= bound);  // NaN counts as escaped; s > bound otherwise
-  return !(__fsqrt_rn(s) < bound);
-}
-
-template <int OUT>
-__device__ __forceinline__ void store_count(void *image, size_t pix, uint32_t count, float color_scale) {
-  if (OUT == VRHI_OUT_COUNT_U32)
-    static_cast<uint32_t *>(image)[pix] = count;
-  else if (OUT == VRHI_OUT_COUNT_U16)
-    static_cast<uint16_t *>(image)[pix] = (uint16_t)count;
-  else
-    static_cast<float *>(image)[pix] = __fsub_rn(1.0f, __fmul_rn((float)count, color_scale));
-}
-
-// Second copy of a count as uint16 at the same pixel index (the compact form a rank sends to its
-// peers when the image is gathered; counts up to 65535 lose nothing).
-__device__ __forceinline__ void store_wire(uint16_t *wire, size_t pix, uint32_t count) { wire[pix] = (uint16_t)count; }
-
-// Row of the image that owned row r maps to (rows are owned in chunks dealt round-robin).
-__device__ __forceinline__ uint32_t owned_row_to_image_row(const EscapeDev &p, uint32_t r) {
-  uint32_t k = r / p.chunk_rows;
-  return (p.chunk_first + k * p.chunk_step) * p.chunk_rows + (r - k * p.chunk_rows);
-}
 
 template <int KIND, int MODE, int TEST, int OUT>
 __global__ void __launch_bounds__(256) escape_checked_kernel(EscapeDev p, void *image, uint32_t *work_counter, uint16_t *wire) {
@@ -329,46 +263,6 @@ __global__ void __launch_bounds__(256, 6) escape_regroup_kernel(EscapeDev p, voi
   }
 }
 
-// Launch of the regrouping kernel with its residency pinned.  The kernel is a persistent grid of
-// `per_sm` blocks per SM that steal work; that only balances if the blocks really sit per_sm to an
-// SM.  On an idle GPU they do, but when blocks of another stream's kernel are resident at launch
-// time the hardware packs the grid onto whichever SMs have room (up to 6 blocks fit by registers),
-// and the SMs that got more than their share then finish late (measured: 3.7 ms instead of 2.5 ms
-// for the 16384^2 image).  Unused dynamic shared memory sized so that exactly per_sm blocks fit makes
-// the surplus blocks wait for their own SM instead.
-template <class Kern>
-static int launch_regroup_pinned(Kern kern, int grid, int per_sm, vrhi_stream_t *st, const EscapeDev &p, void *image,
-                                 uint32_t *counter, uint16_t *wire) {
-  static std::mutex mu;
-  static std::unordered_map<const void *, size_t> static_bytes;
-  size_t fixed = 0;
-  {
-    std::lock_guard<std::mutex> lock(mu);
-    auto it = static_bytes.find(reinterpret_cast<const void *>(kern));
-    if (it == static_bytes.end()) {
-      cudaFuncAttributes fa{};
-      VRHI_CUDA(cudaFuncGetAttributes(&fa, kern));
-      it = static_bytes.emplace(reinterpret_cast<const void *>(kern), fa.sharedSizeBytes).first;
-    }
-    fixed = it->second;
-  }
-  const size_t per_sm_bytes = st->dev->prop.sharedMemPerMultiprocessor;  // each resident block also reserves 1 KB
-  size_t total = ((size_t)((double)per_sm_bytes / (per_sm + 0.5)) - 1024) & ~size_t(127);
-  const size_t optin = st->dev->prop.sharedMemPerBlockOptin;
-  if (total > optin) total = optin;
-  size_t dyn = total > fixed ? total - fixed : 0;
-  // Small images (2 blocks per SM) are short launches, usually frames of a sequence: there the next
-  // frame's blocks should move in while this frame's last ones drain (65 -> 41 us per 1080p frame
-  // with two alternating streams), and a few tens of microseconds cannot go far out of balance.
-  if (per_sm < 4) dyn = 0;
-  if (const char *e = getenv("VRHI_ESCAPE_PIN")) {  // tuning aid: 0 launches without the padding
-    if (atoi(e) == 0) dyn = 0;
-  }
-  VRHI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
-  kern<<<grid, 256, dyn, st->s>>>(p, image, counter, wire);
-  return VRHI_OK;
-}
-
 template <int KIND, int MODE, int TEST>
 static void launch_checked_out(int out, int grid, cudaStream_t s, const EscapeDev &p, void *image, uint32_t *ctr, uint16_t *wire) {
   switch (out) {
@@ -433,33 +327,39 @@ int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const
     p.rows_owned = (uint32_t)rows;
   }
   if (p.rows_owned == 0) return VRHI_OK;  // an empty band is not an error
-  p.tiles_per_row = (q.width + 31u) / 32u;
+  p.neg_zero = -0.0f;
+  // tuning aids, read once per process
+  static const int env_batch = [] { const char *e = getenv("VRHI_ESCAPE_BATCH"); return e ? atoi(e) : 0; }();
+  static const int env_per_sm = [] { const char *e = getenv("VRHI_ESCAPE_CTAS_PER_SM"); return e ? atoi(e) : 0; }();
+  static const int env_pair = [] { const char *e = getenv("VRHI_ESCAPE_PAIR"); return e ? atoi(e) : 1; }();  // 0: one pixel per lane
+  const int sms = st->dev->prop.multiProcessorCount;
+  // The regrouping kernels take what their exactness argument covers; everything else, and callers
+  // that ask for it, runs the step-by-step kernel.
+  const double c2 = (double)q.cr * q.cr + (double)q.ci * q.ci;
+  const bool regroup_ok = q.test == VRHI_TEST_NORM2_GT && q.bound >= 4.0f && q.bound < 3.0e38f &&
+                          q.max_iter >= 64u && q.max_iter <= (1u << 30) && (uint64_t)q.width * q.height <= 0xffffffffull &&
+                          (q.kind == VRHI_ESCAPE_MANDELBROT || c2 <= 2.25) && !(q.flags & VRHI_ESCAPE_FLAG_CHECKED_ONLY);
+  const bool pair = regroup_ok && env_pair != 0;
+  const uint32_t tile_px = pair ? 64u : 32u;  // pixels a warp takes in per intake trip
+  p.tiles_per_row = (q.width + tile_px - 1) / tile_px;
   {
-    // batch = unit of work stealing: 16 tiles for large images; small images get smaller batches so
-    // that every resident warp still sees several of them and the tail stays short
-    const uint64_t resident_warps = (uint64_t)st->dev->prop.multiProcessorCount * 48;
+    // batch = unit of work stealing: 512 pixels of one row for large images; small images get smaller
+    // batches so that every resident warp still sees several of them and the tail stays short
+    const uint64_t resident_warps = (uint64_t)sms * 48;
     const uint64_t tiles = (uint64_t)p.tiles_per_row * p.rows_owned;
+    const uint64_t most = 512 / tile_px;
     uint64_t bt = tiles / (resident_warps * 8);
-    p.batch_tiles = (uint32_t)(bt < 2 ? 2 : bt > 16 ? 16 : bt);
-    if (const char *e = getenv("VRHI_ESCAPE_BATCH")) {  // tuning aid
-      const int b = atoi(e);
-      if (b >= 1 && b <= 64) p.batch_tiles = (uint32_t)b;
-    }
+    const uint64_t least = pair ? 1 : 2;
+    p.batch_tiles = (uint32_t)(bt < least ? least : bt > most ? most : bt);
+    if (env_batch >= 1 && env_batch <= 64) p.batch_tiles = (uint32_t)env_batch;
   }
   p.batches_per_row = (p.tiles_per_row + p.batch_tiles - 1) / p.batch_tiles;
   uint64_t nb = (uint64_t)p.batches_per_row * p.rows_owned;
   if (nb > 0xfffffff0ull) return fail(VRHI_ERR_UNSUPPORTED, "escape_time: image too large for 32-bit batch indices");
   p.n_batches = (uint32_t)nb;
 
-  const int sms = st->dev->prop.multiProcessorCount;
   uint64_t warps_needed = nb;
   int grid = (int)((warps_needed + 7) / 8 < (uint64_t)sms * 8 ? (warps_needed + 7) / 8 : (uint64_t)sms * 8);
-  // The regrouping kernel takes what its exactness argument covers; everything else, and callers
-  // that ask for it, runs the step-by-step kernel.
-  const double c2 = (double)q.cr * q.cr + (double)q.ci * q.ci;
-  const bool regroup_ok = q.test == VRHI_TEST_NORM2_GT && q.bound >= 4.0f && q.bound < 3.0e38f &&
-                          q.max_iter >= 64u && q.max_iter <= (1u << 30) && (uint64_t)q.width * q.height <= 0xffffffffull &&
-                          (q.kind == VRHI_ESCAPE_MANDELBROT || c2 <= 2.25) && !(q.flags & VRHI_ESCAPE_FLAG_CHECKED_ONLY);
   // A frame of a few batches per warp (the 640 x 320 frame of fractal.py:7-8 is one) is dealt out
   // statically: resetting a work counter would be a second node per frame and cost as much as the frame.
   const bool dealt = !regroup_ok && nb <= (uint64_t)grid * 8 * 4;
@@ -471,29 +371,33 @@ int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const
     VRHI_CUDA(cudaMemsetAsync(counter, 0, sizeof(uint32_t), st->s));
   }
   if (regroup_ok) {
-    // Measured on B200: 3-4 CTAs of 256 threads per SM are as fast as the 6 that fit (the kernel is
-    // issue-bound, not latency-bound); small images run faster still with 2, because each warp then
-    // owns enough tiles to keep its pool busy and the drain at the end is shorter.
+    // Measured on B200: 3-4 CTAs of 256 threads per SM are as fast as more (the kernels are bound by
+    // issue or by the binary32 pipe, not by latency); small images run faster still with 2, because
+    // each warp then owns enough tiles to keep its pool busy and the drain at the end is shorter.
     uint64_t ctas = (nb + 7) / 8;
-    const uint64_t tiles_total = (uint64_t)p.tiles_per_row * p.rows_owned;
-    uint64_t per_sm = tiles_total / ((uint64_t)sms * 4 * 8) < 32 ? 2 : 4;
-    uint64_t cap = (uint64_t)sms * per_sm;
+    const uint64_t px_total = (uint64_t)p.tiles_per_row * tile_px * p.rows_owned;
+    uint64_t per_sm = px_total / ((uint64_t)sms * 4 * 8) < 1024 ? 2 : 4;
+    if (env_per_sm >= 1 && env_per_sm <= 6) per_sm = (uint64_t)env_per_sm;
+    const uint64_t cap = (uint64_t)sms * per_sm;
     grid = (int)(ctas < cap ? ctas : cap);
-    // Tuning aid: VRHI_ESCAPE_CTAS_PER_SM overrides the residency chosen above.
-    if (const char *e = getenv("VRHI_ESCAPE_CTAS_PER_SM")) {
-      const int tc = atoi(e);
-      if (tc >= 1 && tc <= 6) { per_sm = (uint64_t)tc; cap = (uint64_t)sms * tc; grid = (int)(ctas < cap ? ctas : cap); }
+    // Small images (2 blocks per SM) are short launches, usually frames of a sequence: there the next
+    // frame's blocks should move in while this frame's last ones drain (65 -> 41 us per 1080p frame
+    // with two alternating streams), and a few tens of microseconds cannot go far out of balance.
+    const bool pin = per_sm >= 4;
+    if (pair) {
+      VRHI_TRY(launch_escape_pair(st, q, p, grid, (int)per_sm, pin, args[0].ptr, counter, wire));
+      return post_launch(st, "escape_time (two pixels per lane)");
     }
     // U = 12, T = 8, K = 8: a sweep on B200 (U = 8..16, T = 4..12, K = 4..12) was flat within 2 % around this point
 #define REGROUP(KIND, OUT)                                                                                             \
   do {                                                                                                                 \
-    if (q.mode == VRHI_ESCAPE_EXACT) VRHI_TRY(launch_regroup_pinned(escape_regroup_kernel<KIND, OUT, 12, 8, 8, VRHI_ESCAPE_EXACT>, grid, (int)per_sm, st, p, args[0].ptr, counter, nullptr)); \
-    else VRHI_TRY(launch_regroup_pinned(escape_regroup_kernel<KIND, OUT, 12, 8, 8, VRHI_ESCAPE_FAST>, grid, (int)per_sm, st, p, args[0].ptr, counter, nullptr));   \
+    if (q.mode == VRHI_ESCAPE_EXACT) VRHI_TRY(launch_pinned(escape_regroup_kernel<KIND, OUT, 12, 8, 8, VRHI_ESCAPE_EXACT>, grid, (int)per_sm, st, p, args[0].ptr, counter, nullptr, pin)); \
+    else VRHI_TRY(launch_pinned(escape_regroup_kernel<KIND, OUT, 12, 8, 8, VRHI_ESCAPE_FAST>, grid, (int)per_sm, st, p, args[0].ptr, counter, nullptr, pin));   \
   } while (0)
 #define REGROUP_WIRE(KIND)                                                                                              \
   do {                                                                                                                 \
-    if (q.mode == VRHI_ESCAPE_EXACT) VRHI_TRY(launch_regroup_pinned(escape_regroup_kernel<KIND, VRHI_OUT_COUNT_U32, 12, 8, 8, VRHI_ESCAPE_EXACT, true>, grid, (int)per_sm, st, p, args[0].ptr, counter, wire)); \
-    else VRHI_TRY(launch_regroup_pinned(escape_regroup_kernel<KIND, VRHI_OUT_COUNT_U32, 12, 8, 8, VRHI_ESCAPE_FAST, true>, grid, (int)per_sm, st, p, args[0].ptr, counter, wire));   \
+    if (q.mode == VRHI_ESCAPE_EXACT) VRHI_TRY(launch_pinned(escape_regroup_kernel<KIND, VRHI_OUT_COUNT_U32, 12, 8, 8, VRHI_ESCAPE_EXACT, true>, grid, (int)per_sm, st, p, args[0].ptr, counter, wire, pin)); \
+    else VRHI_TRY(launch_pinned(escape_regroup_kernel<KIND, VRHI_OUT_COUNT_U32, 12, 8, 8, VRHI_ESCAPE_FAST, true>, grid, (int)per_sm, st, p, args[0].ptr, counter, wire, pin));   \
   } while (0)
     if (wire) {
       if (q.kind == VRHI_ESCAPE_MANDELBROT) REGROUP_WIRE(VRHI_ESCAPE_MANDELBROT);

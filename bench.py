@@ -158,37 +158,318 @@ def time_launches(dev, st, fn, iters, warmup=3):
     return ms
 
 
-def other_workloads(dev, st, torch, hbm_peak, peak_kind, fp32_peak):
-    """Single-GPU lines for the remaining workloads; inputs are generated on the device (seeded)."""
-    from vernondsl_b200 import _lib as L
-    from vernondsl_b200 import ops
+# ------------------------------------------------------------------------------------------------
+# Checks of the HBM-bound workloads at their full shapes.  Test infrastructure: the CPU oracle is
+# the checker here, outside every timed region; tests/test_baseline_shapes_gpu.py runs the same
+# functions.  Tolerances: the fused chain inside the bound that 2-ulp primitives imply (and within
+# 4 ulp of its largest intermediate); reductions, softmax, loss and gradients within 1e-5 relative
+# (sums against the sum of magnitudes, gradients norm-wise).
+RTOL = 1e-5
 
-    out = []
-    device = f"cuda:{dev.ordinal}"
+
+def spread(n, k):
+    """k indices spread over range(n), first and last included."""
+    return np.unique(np.linspace(0, n - 1, min(k, n)).astype(np.int64))
+
+
+def baseline_inputs(torch, device, config):
+    """Seeded inputs of one workload at its full shape, generated on the device."""
     gen = torch.Generator(device=device)
 
     def randn(shape, seed, scale=1.0):
         gen.manual_seed(seed)
-        return torch.randn(shape, generator=gen, device=device, dtype=torch.float32) * scale
+        t = torch.randn(shape, generator=gen, device=device, dtype=torch.float32)
+        return t * scale if scale != 1.0 else t
 
-    def line(name, kernel, ms, algo_bytes, note=""):
+    if config == 2:      # fused map chain: x, y ~ N(0,1), a ~ U(-1,1), 2^28 elements
+        n = 1 << 28
+        gen.manual_seed(1003)
+        a = torch.rand(n, generator=gen, device=device, dtype=torch.float32) * 2 - 1
+        return a, randn(n, 1001), randn(n, 1002)
+    if config == 3:      # [65536, 4096], N(0, 4) read as sigma = 2
+        return (randn((65536, 4096), 2001, 2.0),)
+    if config == 4:      # W, x, t [32768, 4096], b [4096], N(0,1)
+        return randn((32768, 4096), 3001), randn((32768, 4096), 3002), randn(4096, 3004), randn((32768, 4096), 3003)
+    raise ValueError(config)
+
+
+def check_fused_map(a, x, y, out):
+    """Windows of the chain's output (head, tail and 62 windows between) against the binary64 oracle.
+    -> (ok, worst error as a fraction of the allowed bound)."""
+    import oracle
+
+    n = out.numel()
+    win = 4096
+    starts = sorted(set([0, max(0, n - 65536)] + [int(v) // 16 * 16 for v in np.linspace(0, max(0, n - win), 62)]))
+    worst = 0.0
+    for s0 in starts:
+        s1 = min(n, s0 + (65536 if s0 in (0, max(0, n - 65536)) else win))
+        ha, hx, hy, ho = (t[s0:s1].cpu().numpy() for t in (a, x, y, out))
+        want, scale = oracle.fused_map(ha, hx, hy, want_scale=True)
+        bound = oracle.fused_map_bound(ha, hx, hy, 2.0) + 0.5 * np.spacing(np.abs(want)).astype(np.float64)
+        err = np.abs(ho.astype(np.float64) - want.astype(np.float64))
+        unit = np.spacing(np.maximum(scale, np.abs(want)).astype(np.float32)).astype(np.float64)
+        worst = max(worst, float((err / bound).max()), float((err / unit).max()) / 4.0)
+    return worst <= 1.0, worst
+
+
+def check_rows(m, row_sum=None, row_max=None, softmax=None, k=64):
+    """k rows spread over the matrix (first and last included) against the oracle.
+    -> (ok, worst error as a fraction of the tolerance)."""
+    import oracle
+
+    import torch
+
+    rows = spread(m.shape[0], k)
+    idx = torch.from_numpy(rows).to(m.device)
+    hm = m[idx].cpu().numpy()
+    worst = 0.0
+    if row_sum is not None:
+        scale = np.abs(hm).astype(np.float64).sum(axis=1)
+        worst = max(worst, float((np.abs(row_sum[idx].cpu().numpy() - oracle.row_sum(hm)) / (RTOL * scale + 1e-30)).max()))
+    if row_max is not None and not np.array_equal(row_max[idx].cpu().numpy(), oracle.row_max(hm)):
+        worst = float("inf")
+    if softmax is not None:
+        got, want = softmax[idx].cpu().numpy().astype(np.float64), oracle.row_softmax(hm).astype(np.float64)
+        worst = max(worst, float((np.abs(got - want) / (RTOL * np.abs(want) + 1e-38)).max()),
+                    float(np.abs(got.sum(axis=1) - 1.0).max() / 1e-5))
+    return worst <= 1.0, worst
+
+
+def check_mse(W, x, b, t, denom, dW=None, dx=None, row0=0, db=None, loss=None, k=256):
+    """Gradients and loss of the tanh-MSE problem.  W, x, t are the WHOLE problem (the oracle sums db
+    and the loss over all rows); dW / dx may be a row shard starting at row0, checked on k rows
+    spread over the shard; db and loss, when given, are the whole problem's.
+    -> (ok, worst norm-wise error as a fraction of the tolerance)."""
+    import oracle
+
+    import torch
+
+    worst = 0.0
+    hb = b.cpu().numpy()
+    if db is not None or loss is not None:
+        hW, hx, ht = W.cpu().numpy(), x.cpu().numpy(), t.cpu().numpy()
+        if db is not None:
+            _, _, rb = oracle.mse_tanh_bwd(hW, hx, hb, ht, denom)
+            worst = max(worst, float(np.abs(db.cpu().numpy().astype(np.float64) - rb).max() / np.abs(rb).max()) / RTOL)
+        if loss is not None:
+            want = oracle.mse_tanh_fwd(hW, hx, hb, ht, denom)
+            worst = max(worst, abs(float(loss) - want) / abs(want) / RTOL)
+        del hW, hx, ht
+    if dW is not None:
+        rows = spread(dW.shape[0], k)
+        gi = torch.from_numpy(rows + row0).to(W.device)
+        li = torch.from_numpy(rows).to(W.device)
+        rW, rx, _ = oracle.mse_tanh_bwd(W[gi].cpu().numpy(), x[gi].cpu().numpy(), hb, t[gi].cpu().numpy(), denom)
+        for got, want in ((dW[li], rW), (dx[li], rx)):
+            worst = max(worst, float(np.abs(got.cpu().numpy().astype(np.float64) - want).max() / np.abs(want).max()) / RTOL)
+    return worst <= 1.0, worst
+
+
+def hbm_workloads(dev, st, tstream, torch, rank, world, hbm_peak, peak_kind, graphs=True):
+    """The map, row and backward workloads at their full shapes, split along the leading axis over
+    `world` ranks (no collective, except the all-reduce of db and the loss), each checked against the
+    oracle after its timed loop.  `st` is the library's handle of the torch stream `tstream`.  Inputs are generated on the device (seeded).  Times are CUDA events
+    on the launching stream, the maximum over ranks; GB/s is the whole job's."""
+    import torch.distributed as dist
+
+    from vernondsl_b200 import _lib as L
+    from vernondsl_b200 import ops, partition
+
+    import oracle   # the checker, outside every timed region
+
+    oracle.set_num_threads(max(1, (len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)) // world))
+    out = []
+    device = f"cuda:{dev.ordinal}"
+
+    def timed(fn, iters=10):
+        if world > 1:
+            dist.barrier()
+        ms = time_launches(dev, st, fn, iters)
+        if world > 1:
+            v = torch.tensor([ms], device=device)
+            dist.all_reduce(v, op=dist.ReduceOp.MAX)
+            ms = float(v.item())
+        return ms
+
+    def agree(ok, worst):
+        if world > 1:
+            v = torch.tensor([0.0 if ok else 1.0, min(worst, 1e30)], device=device, dtype=torch.float64)
+            dist.all_reduce(v, op=dist.ReduceOp.MAX)
+            return bool(v[0].item() == 0.0), float(v[1].item())
+        return bool(ok), float(worst)
+
+    def line(name, kernel, ms, algo_bytes, check, **extra):
+        ok, worst = agree(*check)
         gbs = algo_bytes / (ms * 1e-3) / 1e9
-        out.append({"workload": name, "kernel": kernel, "ms": ms, "algorithmic_bytes": algo_bytes, "achieved_gbs": gbs,
-                    "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak,
-                                 "peak_kind": peak_kind, "frac_of_nominal_8tbs": gbs / 8000.0}, "note": note})
+        out.append(dict({"workload": name, "kernel": kernel, "ms": ms, "algorithmic_bytes": algo_bytes, "achieved_gbs": gbs,
+                         "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_peak * world, "unit": "GB/s", "frac": gbs / (hbm_peak * world),
+                                      "peak_kind": peak_kind, "frac_of_nominal_8tbs": gbs / (8000.0 * world)},
+                         "verified": ok, "max_err": worst}, **extra))
 
-    # Mandelbrot 1920x1080, max_iter 256: frames back to back (the image is 8.3 MB, so this one is not DRAM-sized)
+    # ---- fused map chain, 2^28 elements
+    a, x, y = baseline_inputs(torch, device, 2)
+    n = a.numel()
+    o = torch.zeros_like(x)
+    torch.cuda.synchronize()   # the inputs were made on torch's default stream; the kernels run on `st`
+    lo, cnt = partition.leading_slice(n, world, rank)
+    sa, sx, sy, so = (t[lo:lo + cnt] for t in (a, x, y, o))
+    A, X, Y, O = (dev.wrap_tensor(t) for t in (sa, sx, sy, so))
+    ms = timed(lambda: ops.fused_map(st, A, X, Y, O, cnt))
+    st.check()
+    line("fused map chain 2^28", "fused_map", ms, 16 * n, check_fused_map(sa, sx, sy, so))
+    if cnt % 4096 == 0:
+        # the same chain through the generic fused-tape kernel (what an arbitrary DSL chain runs on)
+        tp = ops.Tape(3)
+        u = tp.op("fma", tp.input(0), tp.input(1), tp.input(2))
+        e = tp.op("exp", tp.op("mul", tp.op("mul", tp.const(-0.5), tp.input(1)), tp.input(1)))
+        q = tp.op("sqrt", tp.op("add", tp.op("abs", tp.input(2)), tp.const(1e-3)))
+        tp.output(tp.op("fma", tp.op("tanh", u), e, q))
+        so.zero_(); torch.cuda.synchronize()
+        before = ops.tape_jit_stats()["launches"]
+        ms = timed(lambda: ops.map_tape(st, tp, [A, X, Y], [O], cnt // 4096, 4096))
+        st.check()
+        compiled = ops.tape_jit_stats()["launches"] > before
+        line("the chain as a generic tape 2^28", "map_tape (compiled at first use)" if compiled else "map_tape (interpreted: no run-time compiler)",
+             ms, 16 * n, check_fused_map(sa, sx, sy, so))
+        if compiled and world == 1:
+            so.zero_(); torch.cuda.synchronize()
+            ms = timed(lambda: ops.map_tape(st, tp, [A, X, Y], [O], cnt // 4096, 4096, interpret=True))
+            st.check()
+            line("the tape interpreted 2^28", "map_tape (interpreted)", ms, 16 * n, check_fused_map(sa, sx, sy, so), bound_by="instruction issue")
+    del a, x, y, o, sa, sx, sy, so
+    torch.cuda.empty_cache()
+
+    # ---- row reductions and softmax, [65536, 4096]
+    (m,) = baseline_inputs(torch, device, 3)
+    R, Cc = m.shape
+    lo, cnt = partition.leading_slice(R, world, rank)
+    sm_in = m[lo:lo + cnt]
+    sm = torch.zeros_like(sm_in)
+    rs, rm = torch.zeros(cnt, device=device), torch.zeros(cnt, device=device)
+    torch.cuda.synchronize()
+    M, SM, RS, RM = (dev.wrap_tensor(t) for t in (sm_in, sm, rs, rm))
+    ms = timed(lambda: ops.row_sum(st, M, RS, cnt, Cc))
+    st.check()
+    line("row sum [65536,4096]", "row_sum", ms, 4 * R * Cc + 4 * R, check_rows(sm_in, row_sum=rs))
+    ms = timed(lambda: ops.row_max(st, M, RM, cnt, Cc))
+    st.check()
+    line("row max [65536,4096]", "row_max", ms, 4 * R * Cc + 4 * R, check_rows(sm_in, row_max=rm))
+    ms = timed(lambda: ops.row_softmax(st, M, SM, cnt, Cc))
+    st.check()
+    line("row softmax [65536,4096]", "row_softmax", ms, 8 * R * Cc, check_rows(sm_in, softmax=sm))
+    sm.zero_(); rs.zero_(); rm.zero_(); torch.cuda.synchronize()
+    ms = timed(lambda: ops.row_stats_softmax(st, M, RS, RM, SM, cnt, Cc))
+    st.check()
+    line("row sum+max+softmax one pass [65536,4096]", "row_stats_softmax", ms, 8 * R * Cc + 8 * R, check_rows(sm_in, rs, rm, sm))
+    del m, sm, sm_in
+    torch.cuda.empty_cache()
+
+    # ---- tanh-MSE loss and backward, [32768, 4096]; rows split, db and the loss all-reduced
+    Wt, xt, bt, tt = baseline_inputs(torch, device, 4)
+    R, Cc = Wt.shape
+    denom = float(R * Cc)
+    lo, cnt = partition.leading_slice(R, world, rank)
+    sW, sx, stt = (t[lo:lo + cnt] for t in (Wt, xt, tt))
+    dWt, dxt = torch.zeros_like(sW), torch.zeros_like(sW)
+    small = torch.zeros(Cc + 4, device=device)       # db [4096] and the loss in one array: one all-reduce
+    dbt, lt = small[:Cc], small[Cc:Cc + 1]
+    torch.cuda.synchronize()
+    bW, bx, bb, bt_, bdW, bdx, bdb, bl = (dev.wrap_tensor(t) for t in (sW, sx, bt, stt, dWt, dxt, dbt, lt))
+    def reduce_small():
+        if world > 1:
+            with torch.cuda.stream(tstream):
+                dist.all_reduce(small)
+
+    def fwd():
+        ops.mse_tanh_fwd(st, bW, bx, bb, bt_, bl, cnt, Cc, denom)
+        reduce_small()
+
+    ms = timed(fwd)
+    st.check()
+    small.zero_(); torch.cuda.synchronize(); fwd(); st.check()
+    line("tanh-MSE loss [32768,4096]", "mse_tanh_fwd" + (" + all-reduce" if world > 1 else ""), ms, 12 * R * Cc,
+         check_mse(Wt, xt, bt, tt, denom, loss=lt.item()) if rank == 0 else (True, 0.0))
+
+    def bwd(reduce=True):
+        ops.mse_tanh_bwd(st, bW, bx, bb, bt_, bdW, bdx, bdb, cnt, Cc, denom, bl)
+        if reduce:
+            reduce_small()
+
+    ms = timed(bwd)
+    extra = {}
+    if world > 1:
+        extra["ms_without_all_reduce"] = timed(lambda: bwd(False))
+    st.check()
+    small.zero_(); torch.cuda.synchronize(); bwd(); st.check()
+    ok_rows = check_mse(Wt, xt, bt, tt, denom, dWt, dxt, lo)
+    ok_sum = check_mse(Wt, xt, bt, tt, denom, db=dbt, loss=lt.item()) if rank == 0 else (True, 0.0)
+    line("tanh-MSE backward dW,dx,db,loss [32768,4096]", "mse_tanh_bwd" + (" + all-reduce of db and loss" if world > 1 else ""), ms,
+         20 * R * Cc + 8 * Cc, (ok_rows[0] and ok_sum[0], max(ok_rows[1], ok_sum[1])), **extra)
+    if graphs and world == 1:
+        # The same gradients through the generic path: the execution graph differentiates the loss and fuses the
+        # elementwise parts into one tape, compiled at first use, whose third output (the adjoint of b) is summed over
+        # the rows inside the kernel; no hand-written loss kernel is selected.
+        from vernondsl_b200.graph import Graph
+
+        dWt.zero_(); dxt.zero_(); small.zero_(); torch.cuda.synchronize()
+        g = Graph(dev, R, Cc, specialize=False)
+        nW, nx, nt = g.input(bW), g.input(bx), g.input(bt_)
+        nb = g.input(bb, L.SHAPE_ROWVEC)
+        loss = g.mean(g.square(g.tanh(nW * nx + nb) - nt))
+        gW, gx, gb = g.grad(loss, [nW, nx, nb])
+        g.output(gW, bdW)
+        g.output(gx, bdx)
+        g.output(gb, bdb)
+        g.compile()
+        ms = timed(lambda: g.launch(st))
+        st.check()
+        ok_rows = check_mse(Wt, xt, bt, tt, denom, dWt, dxt, 0)
+        ok_sum = check_mse(Wt, xt, bt, tt, denom, db=dbt)
+        line("the gradients from the execution graph (autodiff, no hand-written kernel)", f"graph: {g.kernel_count()} kernels", ms,
+             20 * R * Cc + 8 * Cc, (ok_rows[0] and ok_sum[0], max(ok_rows[1], ok_sum[1])))
+        g.close()
+        small.zero_(); torch.cuda.synchronize()
+        g = Graph(dev, R, Cc, specialize=False)
+        nW, nx, nt = g.input(bW), g.input(bx), g.input(bt_)
+        nb = g.input(bb, L.SHAPE_ROWVEC)
+        g.output(g.mean(g.square(g.tanh(nW * nx + nb) - nt)), bl)
+        g.compile()
+        ms = timed(lambda: g.launch(st))
+        st.check()
+        line("the loss from the execution graph (no hand-written kernel)", f"graph: {g.kernel_count()} kernels", ms, 12 * R * Cc,
+             check_mse(Wt, xt, bt, tt, denom, loss=lt.item()))
+        g.close()
+    return out
+
+
+def frame_workloads(dev, st, torch, fp32_peak, fp32_nominal):
+    """Single-GPU lines for the frame-sized escape-time workloads (launch- and drain-bound, not DRAM-sized)."""
+    from vernondsl_b200 import _lib as L
+    from vernondsl_b200 import ops
+
+    out = []
+    # Mandelbrot 1920x1080, max_iter 256: frames back to back on one stream, every frame checked by its exact digest
     W, H = 1920, 1080
     dx, dy = ops.grid_steps(-2.5, 1.0, -1.0, 1.0, W, H)
     img = dev.empty((H, W), np.uint32, L.IMAGE)
     p = ops.escape_params(L.MANDELBROT, W, H, -2.5, -1.0, dx, dy, max_iter=256)
     ms = time_launches(dev, st, lambda: ops.escape_time(st, img, p), 50)
-    total = int(np.load(os.path.join(ROOT, "tests", "golden", "golden.npz"))["mandelbrot_1080p_digest"][0])
-    rate = total / (ms * 1e-3)
-    out.append({"workload": "mandelbrot 1920x1080 max_iter=256 u32 exact, 50 frames back to back", "kernel": "escape_time", "ms": ms,
-                "gpixel_iters_per_s": rate / 1e9,
-                "roofline": {"bound": "fp32", "achieved": OPS_PER_ITER * rate / 1e9, "peak": fp32_peak, "unit": "Gop/s",
-                             "frac": OPS_PER_ITER * rate / 1e9 / fp32_peak}})
+    want = [int(v) for v in np.load(os.path.join(ROOT, "tests", "golden", "golden.npz"))["mandelbrot_1080p_digest"]]
+    total = want[0]
+
+    def digest(buf):
+        t = buf.as_tensor(np.uint32, (H, W)).view(-1).to(torch.int64)
+        idx = torch.arange(1, H * W + 1, device=t.device, dtype=torch.int64)
+        return [int(t.sum().item()), int((t * idx).sum().item()) & 0xFFFFFFFFFFFFFFFF]
+
+    def frame_line(name, ms_frame, ok):
+        rate = total / (ms_frame * 1e-3)
+        out.append({"workload": name, "kernel": "escape_time", "ms": ms_frame, "gpixel_iters_per_s": rate / 1e9, "verified": ok,
+                    "roofline": {"bound": "fp32", "achieved": OPS_PER_ITER * rate / 1e9, "peak": fp32_peak, "unit": "Gop/s",
+                                 "frac": OPS_PER_ITER * rate / 1e9 / fp32_peak, "frac_of_nominal": OPS_PER_ITER * rate / 1e9 / fp32_nominal}})
+
+    frame_line("mandelbrot 1080p max_iter=256, 50 frames back to back on one stream", ms, digest(img) == want)
     # The same frames into a ring of 4 images from two streams in turn, recorded once: the first blocks of a
     # frame start while the last blocks of the frame before drain (a frame is far too short to fill the GPU to its end).
     side = dev.stream()
@@ -202,12 +483,7 @@ def other_workloads(dev, st, torch, hbm_peak, peak_kind, fp32_peak):
             ops.escape_time(st if k % 2 == 0 else side, ring[k % 4], p)
     ms2 = time_launches(dev, st, lambda: seq.launch(), 5) / 48
     st.check()
-    ok = all(int(r.as_tensor(np.uint32, (H, W)).sum(dtype=torch.int64).item()) == total for r in ring)
-    rate2 = total / (ms2 * 1e-3)
-    out.append({"workload": "mandelbrot 1920x1080 max_iter=256 u32 exact, 48 frames as one recorded sequence on two alternating streams, ring of 4 images",
-                "kernel": "escape_time", "ms": ms2, "gpixel_iters_per_s": rate2 / 1e9, "sum_of_counts_matches_every_frame": ok,
-                "roofline": {"bound": "fp32", "achieved": OPS_PER_ITER * rate2 / 1e9, "peak": fp32_peak, "unit": "Gop/s",
-                             "frac": OPS_PER_ITER * rate2 / 1e9 / fp32_peak}})
+    frame_line("mandelbrot 1080p, 48 frames recorded on two alternating streams, ring of 4", ms2, all(digest(r) == want for r in ring))
     seq.close()
     for b in ring:
         b.close()
@@ -235,99 +511,38 @@ def other_workloads(dev, st, torch, hbm_peak, peak_kind, fp32_peak):
         st.fork_recording(side)
         run_frames([st, side])
     ms_seq2 = time_launches(dev, st, lambda: seq2.launch(), 5) / frames
-    out.append({"workload": f"fractal.py frame 640x320 f32 colour, max_iter=50, {frames} frames with a new uniform each, ring of 4 device frames",
-                "kernel": "escape_time", "ms_per_frame_plain_launches": ms_plain, "ms_per_frame_recorded_sequence": ms_seq,
-                "ms_per_frame_recorded_two_streams": ms_seq2, "frames_per_s_recorded_two_streams": 1e3 / ms_seq2,
-                "note": "launch-bound: one CUDA graph submission for all frames against one launch call per frame; with two "
-                        "alternating streams consecutive frames overlap"})
+    st.check()
+    out.append({"workload": f"fractal.py frame 640x320 f32 colour max_iter=50, {frames} frames, a new uniform each", "kernel": "escape_time",
+                "ms": ms_seq2, "ms_plain_launches": ms_plain, "ms_recorded": ms_seq, "ms_recorded_two_streams": ms_seq2,
+                "frames_per_s": 1e3 / ms_seq2})
     seq.close()
     seq2.close()
     side.close()
     for b in ring:
         b.close()
-
-    # fused map chain, 2^28 elements
-    n = 1 << 28
-    gen.manual_seed(1003)
-    a = torch.rand(n, generator=gen, device=device, dtype=torch.float32) * 2 - 1
-    x, y = randn(n, 1001), randn(n, 1002)
-    o = torch.empty_like(x)
-    A, X, Y, O = (dev.wrap_tensor(t) for t in (a, x, y, o))
-    ms = time_launches(dev, st, lambda: ops.fused_map(st, A, X, Y, O, n), 10)
-    line("fused map chain, 2^28 f32", "fused_map", ms, 16 * n)
-    # the same chain through the generic fused-tape kernel (what an arbitrary DSL chain runs on)
-    t = ops.Tape(3)
-    u = t.op("fma", t.input(0), t.input(1), t.input(2))
-    e = t.op("exp", t.op("mul", t.op("mul", t.const(-0.5), t.input(1)), t.input(1)))
-    q = t.op("sqrt", t.op("add", t.op("abs", t.input(2)), t.const(1e-3)))
-    t.output(t.op("fma", t.op("tanh", u), e, q))
-    before = ops.tape_jit_stats()["launches"]
-    ms = time_launches(dev, st, lambda: ops.map_tape(st, t, [A, X, Y], [O], n // 4096, 4096), 10)
-    compiled = ops.tape_jit_stats()["launches"] > before
-    line("the same chain as a generic tape, 2^28 f32 (kernel compiled for the tape at first use)" if compiled else
-         "the same chain as a generic tape, 2^28 f32 (interpreting kernel: no run-time compiler on this box)", "map_tape", ms, 16 * n)
-    if compiled:
-        ms = time_launches(dev, st, lambda: ops.map_tape(st, t, [A, X, Y], [O], n // 4096, 4096, interpret=True), 10)
-        line("the same tape through the interpreting kernel, 2^28 f32", "map_tape (interpreted)", ms, 16 * n,
-             note="bound by instruction issue and shared-memory traffic, not by HBM")
-    del a, x, y, o
-
-    # row reductions and softmax, [65536, 4096], N(0,4) read as sigma = 2
-    R, Cc = 65536, 4096
-    m = randn((R, Cc), 2001, 2.0)
-    sm = torch.empty_like(m)
-    rs, rm = torch.empty(R, device=device), torch.empty(R, device=device)
-    M, SM, RS, RM = (dev.wrap_tensor(t) for t in (m, sm, rs, rm))
-    ms = time_launches(dev, st, lambda: ops.row_sum(st, M, RS, R, Cc), 10)
-    line("row sum [65536,4096] f32", "row_sum", ms, 4 * R * Cc + 4 * R)
-    ms = time_launches(dev, st, lambda: ops.row_max(st, M, RM, R, Cc), 10)
-    line("row max [65536,4096] f32", "row_max", ms, 4 * R * Cc + 4 * R)
-    ms = time_launches(dev, st, lambda: ops.row_softmax(st, M, SM, R, Cc), 10)
-    line("row softmax [65536,4096] f32", "row_softmax", ms, 8 * R * Cc)
-    ms = time_launches(dev, st, lambda: ops.row_stats_softmax(st, M, RS, RM, SM, R, Cc), 10)
-    line("row sum+max+softmax in one pass [65536,4096] f32", "row_stats_softmax", ms, 8 * R * Cc + 8 * R)
-    del m, sm
-
-    # tanh-MSE forward and backward, [32768, 4096]
-    R, Cc = 32768, 4096
-    Wt, xt, tt = randn((R, Cc), 3001), randn((R, Cc), 3002), randn((R, Cc), 3003)
-    bt = randn(Cc, 3004)
-    dWt, dxt = torch.empty_like(Wt), torch.empty_like(Wt)
-    dbt, lt = torch.empty(Cc, device=device), torch.empty(4, device=device)
-    bW, bx, bb, bt_, bdW, bdx, bdb, bl = (dev.wrap_tensor(t) for t in (Wt, xt, bt, tt, dWt, dxt, dbt, lt))
-    ms = time_launches(dev, st, lambda: ops.mse_tanh_fwd(st, bW, bx, bb, bt_, bl, R, Cc), 10)
-    line("tanh-MSE loss [32768,4096] f32", "mse_tanh_fwd", ms, 12 * R * Cc)
-    ms = time_launches(dev, st, lambda: ops.mse_tanh_bwd(st, bW, bx, bb, bt_, bdW, bdx, bdb, R, Cc), 10)
-    line("tanh-MSE backward dW,dx,db [32768,4096] f32 (forward recomputed)", "mse_tanh_bwd", ms, 20 * R * Cc + 8 * Cc,
-         "includes the column-sum finalize kernel")
-    # The same gradients through the generic path: the execution graph differentiates the loss and fuses the elementwise
-    # parts into one tape, compiled at first use, whose third output (the adjoint of b) is summed over the rows inside
-    # the kernel; no hand-written loss kernel is selected.
-    from vernondsl_b200.graph import Graph
-    g = Graph(dev, R, Cc, specialize=False)
-    nW, nx, nt = g.input(bW), g.input(bx), g.input(bt_)
-    nb = g.input(bb, L.SHAPE_ROWVEC)
-    loss = g.mean(g.square(g.tanh(nW * nx + nb) - nt))
-    gW, gx, gb = g.grad(loss, [nW, nx, nb])
-    g.output(gW, bdW)
-    g.output(gx, bdx)
-    g.output(gb, bdb)
-    g.compile()
-    ms = time_launches(dev, st, lambda: g.launch(st), 10)
-    line("the same gradients from the execution graph without the hand-written kernel (autodiff, fused tapes, column sum)",
-         f"graph: {g.kernel_count()} kernels", ms, 20 * R * Cc + 8 * Cc,
-         "algorithmic bytes as above; where the column sum is folded into the tape kernel the plan is one step (plus the finalize of the partial rows)")
-    g.close()
-    g = Graph(dev, R, Cc, specialize=False)
-    nW, nx, nt = g.input(bW), g.input(bx), g.input(bt_)
-    nb = g.input(bb, L.SHAPE_ROWVEC)
-    g.output(g.mean(g.square(g.tanh(nW * nx + nb) - nt)), bl)
-    g.compile()
-    ms = time_launches(dev, st, lambda: g.launch(st), 10)
-    line("the loss alone from the execution graph without the hand-written kernel", f"graph: {g.kernel_count()} kernels", ms, 12 * R * Cc,
-         "the squared error is summed inside the compiled tape; a flat sum and a scale follow")
-    g.close()
     return out
+
+
+def compact(entries):
+    """The workload lines once more, a few dozen characters each, for the end of the JSON line:
+    [name, ms, fraction of the measured peak, fraction of the nominal peak, verified, worst error / tolerance]."""
+    rows = []
+    for e in entries:
+        r = e.get("roofline", {})
+        rows.append([e["kernel"] if e["kernel"] != "escape_time" else e["workload"][:28], float(f"{e['ms']:.4g}"),
+                     float(f"{r.get('frac', 0):.3g}"), float(f"{r.get('frac_of_nominal_8tbs', r.get('frac_of_nominal', 0)):.3g}"),
+                     e.get("verified"), float(f"{e.get('max_err', 0):.2g}")])
+    return rows
+
+
+def round_floats(obj, digits=5):
+    if isinstance(obj, float):
+        return float(f"{obj:.{digits}g}")
+    if isinstance(obj, dict):
+        return {k: round_floats(v, digits) for k, v in obj.items()}
+    if isinstance(obj, (list, tuple)):
+        return [round_floats(v, digits) for v in obj]
+    return obj
 
 
 def run_only(args):
@@ -758,7 +973,7 @@ def main():
         mismatch = float((image_t != exact_img).sum().item()) / (W * H)
         fast_mode = {"value": fast_iters / (fast_ms * 1e-3) / 1e9, "unit": "Gpixel-iters/s", "ms_per_step": fast_ms,
                      "pixel_mismatch_fraction_vs_exact": mismatch, "sum_of_counts": fast_iters,
-                     "note": "multiply-adds fused (4 instructions per update instead of 6); bit-exact against the oracle's contracted mode, not against the exact mode"}
+                     "note": "multiply-adds fused: its own rounding sequence, not bit-comparable with the exact mode"}
         del exact_img
         compute()  # leave the exact image in place for the end-to-end leg
 
@@ -847,9 +1062,25 @@ def main():
         secs = time.perf_counter() - t0
         ok16 = bool(int(host16.array.astype(np.uint64).sum()) == total_iters)
         e2e_u16 = {"value": total_iters * e2e_steps / secs / 1e9, "unit": "Gpixel-iters/s", "d2h_bytes_per_step": H * W * 2,
-                   "sum_of_counts_matches": ok16, "note": "counts delivered as uint16 instead of uint32; otherwise the e2e step"}
+                   "sum_of_counts_matches": ok16}
         host16.close()
         image16.close()
+
+    # the other workloads: frame-sized escape-time launches (one GPU), and the HBM-bound map / row / backward
+    # workloads at their full shapes, split along the leading axis at N > 1, each checked against the oracle
+    others = []
+    barrier()
+    if exchange is not None:
+        exchange.close()   # peers hold mappings of this rank's buffers: unmap them before anything is freed
+        exchange = None
+        barrier()
+    if args.workloads == "all":
+        image.close()
+        del image_t
+        torch.cuda.empty_cache()
+        if world == 1:
+            others += frame_workloads(dev, st, torch, fp32_peak, fp32_nominal)
+        others += hbm_workloads(dev, st, tstream, torch, rank, world, hbm_peak, peak_kind)
 
     if rank == 0:
         achieved = OPS_PER_ITER * total_iters / (compute_ms * 1e-3) / 1e9 / world  # per GPU
@@ -863,13 +1094,13 @@ def main():
             "verified_bit_exact": verified,
             "compute_only": {"value": compute_value, "ms_per_step": compute_ms},
             "roofline": {"bound": "fp32", "achieved": achieved, "peak": fp32_peak, "unit": "Gop/s", "frac": achieved / fp32_peak,
-                         # DRAM bytes per image: ncu capture of the 8192^2 image x 4 (profiles/escape_regroup_julia_8192.md)
-                         "traffic": 4 * 209.86e6,
+                         # DRAM bytes one GPU moves per step: the rows it computes, once (an ncu capture of the 8192^2
+                         # image showed 210.6 MB written for 268.4 MB of image, the rest still in L2, and 0.8 MB read)
+                         "traffic": float(H * W * 4 // world), "traffic_source": "bytes of the rows this GPU writes; not measured in this run",
                          "peak_kind": "FFMA-chain probe in this run (lane-instructions/s)",
                          "peak_nominal": fp32_nominal, "frac_of_nominal": achieved / fp32_nominal,
                          "algorithmic": f"{OPS_PER_ITER} f32 ops per pixel-iteration x {total_iters} iterations per image, per GPU"},
-            "e2e": {"value": e2e_value, "unit": "Gpixel-iters/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": d2h,
-                    "note": "kernel + download of this rank's rows into pinned host memory; uniforms travel as kernel parameters"},
+            "e2e": {"value": e2e_value, "unit": "Gpixel-iters/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": d2h},
             "gpu_launches": int(launches), "clocks": clocks, "fast_mode": fast_mode,
         }
         if e2e_u16 is not None:
@@ -883,12 +1114,12 @@ def main():
             secs = time.perf_counter() - t0
             line["cpu_baseline"] = {"value": tot / secs / 1e9, "unit": "Gpixel-iters/s", "cores": oracle.num_threads(), "kind": "port",
                                     "sample": "the whole 16384x16384 image, once"}
-        if world == 1 and args.workloads == "all":
-            image.close()
-            del image_t
-            torch.cuda.empty_cache()
-            line["other_workloads"] = other_workloads(dev, st, torch, hbm_peak, peak_kind, fp32_peak)
-        os.write(json_fd, (json.dumps(line) + "\n").encode())
+        if others:
+            line["other_workloads"] = others
+            # last key, short: [kernel or workload, ms, fraction of the measured peak, of the nominal peak, verified, worst error / tolerance]
+            line["summary"] = {"headline": [float(f"{ms_per_step:.4g}"), float(f"{achieved / fp32_peak:.3g}"), float(f"{achieved / fp32_nominal:.3g}"), verified],
+                               "others": compact(others)}
+        os.write(json_fd, (json.dumps(round_floats(line), separators=(",", ":")) + "\n").encode())
     barrier()
     if exchange is not None:
         exchange.close()

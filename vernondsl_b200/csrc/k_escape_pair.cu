@@ -1,23 +1,41 @@
-// Escape-time map, two pixels per lane in packed binary32 pairs (sm_100a).
+// Escape-time map, regrouping kernel: two pixels per lane in packed binary32 pairs (sm_100a).
 //
 // Loop rules as in k_escape.cu (fractal.py:11-25): test before update, count the updates, square
-// as (z0*z0 - z1*z1, (z1*z0)*2).  The machinery is that of the regrouping kernel there (unchecked
-// blocks of U updates justified by monotonic escape, checked blocks for the lanes that are
-// finishing, a per-warp pool fed by lock-step intake of fresh tiles, work stealing), with one
-// change of substance: every lane carries TWO pixels, and all arithmetic on them is issued as
-// packed instructions (fma/add/sub .rn.f32x2), one instruction for both pixels.
+// as (z0*z0 - z1*z1, (z1*z0)*2).  Accepted parameters: test "a+b > bound" with bound >= 4,
+// |c| <= 1.5 (Mandelbrot pixels with a larger constant are finished at intake), max_iter >= 64.
 //
-// Why.  On this GPU an SM sub-partition issues one instruction per clock and its binary32 pipe
-// retires 32 lane-operations per clock.  With one pixel per lane the six arithmetic instructions
-// of an update fill the issue slot on every clock, and every test, counter, ballot and address
-// computation costs a slot the arithmetic cannot use (measured: 36 % of all issued instructions).
-// A packed instruction occupies the pipe for two clocks but the issue slot for one, so the same
-// arithmetic rate leaves every second issue slot free, and the bookkeeping of this warp and of the
-// other resident warps runs in those slots.  The kernel is then bound by the binary32 pipe, not by
-// instruction issue.
+// Iteration counts inside a warp differ by orders of magnitude near the set, so one pixel per lane
+// with a test on every step leaves most lanes idle (about 36 % lane efficiency on the 16384^2
+// Julia workload) and spends 11 issue slots per step.  This kernel keeps the slots busy:
+//
+//  * UNCHECKED BLOCKS.  A slot runs U updates with no test and no counter (six arithmetic
+//    operations per update).  One test at the end decides whether the whole block was valid.  That
+//    is exact because, for bound >= 4 and |c| <= 1.5, escape is monotonic even in binary32: once
+//    a+b > bound then |z'| >= |z|^2 - |c| > 1.2|z|, so every later a+b is larger still, or Inf/NaN,
+//    and the test is written !(s <= bound) so that NaN counts as escaped.  A slot whose block failed
+//    the test (or would pass max_iter) is put back on its checkpoint and marked "finishing".
+//  * CHECKED BLOCKS.  When at least T slots are finishing or empty, the warp runs one block of U
+//    steps with the test and the counter on every step; slots still in flight simply advance,
+//    finishing slots find their exact count.  Finished pixels are stored and their slots freed.
+//  * POOL.  Freed slots are refilled from a per-warp ring in shared memory.  The ring is fed by
+//    INTAKE: 64 fresh pixels of a stolen tile run K checked steps in lock step (most pixels of the
+//    far exterior end there and are stored coalesced); survivors are pushed to the ring with their
+//    state.  Long-lived pixels therefore share warps with other long-lived pixels.
+//  * WORK STEALING.  Warps pull batches of up to 8 tiles (512 pixels of one row) from a global
+//    counter.  Nothing here waits on another warp or block: no spin loops, no barriers.
+//
+// TWO PIXELS PER LANE.  Every lane carries two slots, and all arithmetic on them is issued as packed
+// instructions (fma/add/sub .rn.f32x2), one instruction for both.  On this GPU an SM sub-partition
+// issues one instruction per clock and its binary32 pipe retires 32 lane-operations per clock.
+// With one pixel per lane the six arithmetic instructions of an update fill the issue slot on
+// every clock, and every test, counter, ballot and address computation costs a slot the arithmetic
+// cannot use (measured: 36 % of all issued instructions).  A packed instruction occupies the pipe
+// for two clocks but the issue slot for one, so part of the bookkeeping of this warp and of the
+// other resident warps runs in the slots between.  Measured on B200, 16384^2 Julia image: 2.49 ms
+// with one pixel per lane, 2.17 ms with two; 699 M -> 465 M issued instructions on the 8192^2 image.
 //
 // Exactness.  A packed operation rounds each half exactly like the scalar operation, so the counts
-// are the same bits as the one-pixel-per-lane kernels and the CPU statement.  One trap: the
+// are the same bits as the one-pixel-per-lane kernel and the CPU statement.  One trap: the
 // assembler contracts mul.rn.f32x2 followed by add/sub.rn.f32x2 into a fused multiply-add (it does
 // so even through fma(x, y, -0.0) with a literal -0.0), which changes the rounding of
 // (zr*zr - zi*zi).  Every product here is therefore fma(x, y, nz) with nz = -0.0 read from the
@@ -92,8 +110,9 @@ __device__ __forceinline__ void pair_advance(f32x2 &zr, f32x2 &zi, f32x2 &a, f32
 constexpr int kPairPool = 128;  // pool entries per warp: a refill wants up to 64, an intake trip adds up to 64
 
 // U = updates per block, T = waiting slots (of 64) that trigger a checked block, K = checked steps
-// a fresh pixel gets before it is pooled
-template <int KIND, int OUT, int U, int T, int K, int MODE, bool WIRE>
+// a fresh pixel gets before it is pooled, EX = bit k set: intake stops before step k when every
+// pixel of the tile has ended, NBLK = unchecked blocks between two counts of the waiting slots
+template <int KIND, int OUT, int U, int T, int K, int MODE, bool WIRE, int EX, int NBLK>
 __global__ void __launch_bounds__(256, 4) escape_pair_kernel(EscapeDev p, void *image, uint32_t *work_counter, uint16_t *wire) {
   constexpr bool PER_PIXEL_C = (KIND == VRHI_ESCAPE_MANDELBROT);
   __shared__ float4 s_pool[8][kPairPool];  // zr, zi, pixel index, count: one 16-byte access per entry
@@ -160,7 +179,7 @@ __global__ void __launch_bounds__(256, 4) escape_pair_kernel(EscapeDev p, void *
       l0 = l0 && (s0 <= bound);
       l1 = l1 && (s1 <= bound);
       // most tiles lie far outside the set and die within two or three steps, all slots together
-      if ((k == 2 || k == 4) && k < K - 1 && !__any_sync(FULL, l0 || l1)) break;
+      if (((EX >> k) & 1) && k < K - 1 && !__any_sync(FULL, l0 || l1)) break;
       pair_advance<MODE>(FZR, FZI, FA, FB, FCR, FCI, NZ, TWO);
       fc0 += l0 ? 1u : 0u;
       fc1 += l1 ? 1u : 0u;
@@ -286,19 +305,23 @@ __global__ void __launch_bounds__(256, 4) escape_pair_kernel(EscapeDev p, void *
     // ---- unchecked blocks until enough slots want attention (all of them once nothing can be refilled)
     const uint32_t threshold = (!fresh && pool_n == 0) ? 64u : (uint32_t)T;
     while (waiting < threshold) {
-      const f32x2 CKR = ZR, CKI = ZI;
 #pragma unroll
-      for (int k = 0; k < U; ++k) pair_advance<MODE>(ZR, ZI, A, B, CR, CI, NZ, TWO);
-      // slots that are not running (empty or finishing) computed garbage: they, and slots whose
-      // block failed, go back to the checkpoint; a and b are refreshed by the checked block
-      float s0, s1;
-      unpack2(pair_norm2<MODE>(ZR, ZI, A, B, NZ), s0, s1);
-      run0 = run0 && (s0 <= bound) && (cnt0 <= fast_limit);
-      run1 = run1 && (s1 <= bound) && (cnt1 <= fast_limit);
-      cnt0 += run0 ? (uint32_t)U : 0u;
-      cnt1 += run1 ? (uint32_t)U : 0u;
-      ZR = select2(run0, run1, ZR, CKR);
-      ZI = select2(run0, run1, ZI, CKI);
+      for (int nb = 0; nb < NBLK; ++nb) {
+        const f32x2 CKR = ZR, CKI = ZI;
+#pragma unroll
+        for (int k = 0; k < U; ++k) pair_advance<MODE>(ZR, ZI, A, B, CR, CI, NZ, TWO);
+        // slots that are not running (empty or finishing) computed garbage: they, and slots whose
+        // block failed, go back to the checkpoint; a and b are refreshed below or by the checked block
+        float s0, s1;
+        unpack2(pair_norm2<MODE>(ZR, ZI, A, B, NZ), s0, s1);
+        run0 = run0 && (s0 <= bound) && (cnt0 <= fast_limit);
+        run1 = run1 && (s1 <= bound) && (cnt1 <= fast_limit);
+        cnt0 += run0 ? (uint32_t)U : 0u;
+        cnt1 += run1 ? (uint32_t)U : 0u;
+        ZR = select2(run0, run1, ZR, CKR);
+        ZI = select2(run0, run1, ZI, CKI);
+        if (nb + 1 < NBLK) pair_squares<MODE>(ZR, ZI, NZ, A, B);
+      }
       waiting = __popc(__ballot_sync(FULL, !run0)) + __popc(__ballot_sync(FULL, !run1));
     }
     // ---- one checked block: finishing slots find their exact count, the others just advance
@@ -307,24 +330,17 @@ __global__ void __launch_bounds__(256, 4) escape_pair_kernel(EscapeDev p, void *
   }
 }
 
-// (U, T, K) of the shipped instantiations
-#ifndef VRHI_PAIR_U
-#define VRHI_PAIR_U 12
-#endif
-#ifndef VRHI_PAIR_T
-#define VRHI_PAIR_T 16
-#endif
-#ifndef VRHI_PAIR_K
-#define VRHI_PAIR_K 8
-#endif
+// The shipped instantiation: U = 12, T = 16 of 64, K = 12 with exits before steps 2, 4, 6 and 8, two blocks
+// between counts.  Sweeps on B200 (U = 6..24, T = 4..32, K = 4..16, one to four blocks between counts)
+// stayed within 3 % of this point on the 16384^2 Julia image.
 
 int launch_escape_pair(vrhi_stream_t *st, const vrhi_escape_params &q, const EscapeDev &p, int grid, int per_sm, bool pin, void *image,
                        uint32_t *counter, uint16_t *wire) {
-  constexpr int U = VRHI_PAIR_U, T = VRHI_PAIR_T, K = VRHI_PAIR_K;
+  constexpr int U = 12, T = 16, K = 12, EX = 0x154, NBLK = 2;
 #define PAIR(KIND, OUT, WIRE)                                                                                                        \
   do {                                                                                                                               \
-    if (q.mode == VRHI_ESCAPE_EXACT) return launch_pinned(escape_pair_kernel<KIND, OUT, U, T, K, VRHI_ESCAPE_EXACT, WIRE>, grid, per_sm, st, p, image, counter, wire, pin); \
-    return launch_pinned(escape_pair_kernel<KIND, OUT, U, T, K, VRHI_ESCAPE_FAST, WIRE>, grid, per_sm, st, p, image, counter, wire, pin);  \
+    if (q.mode == VRHI_ESCAPE_EXACT) return launch_pinned(escape_pair_kernel<KIND, OUT, U, T, K, VRHI_ESCAPE_EXACT, WIRE, EX, NBLK>, grid, per_sm, st, p, image, counter, wire, pin); \
+    return launch_pinned(escape_pair_kernel<KIND, OUT, U, T, K, VRHI_ESCAPE_FAST, WIRE, EX, NBLK>, grid, per_sm, st, p, image, counter, wire, pin);  \
   } while (0)
   if (wire) {
     if (q.kind == VRHI_ESCAPE_MANDELBROT) PAIR(VRHI_ESCAPE_MANDELBROT, VRHI_OUT_COUNT_U32, true);

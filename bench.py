@@ -266,10 +266,10 @@ def check_mse(W, x, b, t, denom, dW=None, dx=None, row0=0, db=None, loss=None, k
     return worst <= 1.0, worst
 
 
-def hbm_workloads(dev, st, tstream, torch, rank, world, hbm_peak, peak_kind, graphs=True):
+def hbm_workloads(dev, st, torch, rank, world, hbm_peak, peak_kind, grp=None, graphs=True):
     """The map, row and backward workloads at their full shapes, split along the leading axis over
     `world` ranks (no collective, except the all-reduce of db and the loss), each checked against the
-    oracle after its timed loop.  `st` is the library's handle of the torch stream `tstream`.  Inputs are generated on the device (seeded).  Times are CUDA events
+    oracle after its timed loop.  `grp` is the ranks' vernondsl_b200.group.Group (its all-reduce sums db and the loss).  Inputs are generated on the device (seeded).  Times are CUDA events
     on the launching stream, the maximum over ranks; GB/s is the whole job's."""
     import torch.distributed as dist
 
@@ -376,10 +376,11 @@ def hbm_workloads(dev, st, tstream, torch, rank, world, hbm_peak, peak_kind, gra
     dbt, lt = small[:Cc], small[Cc:Cc + 1]
     torch.cuda.synchronize()
     bW, bx, bb, bt_, bdW, bdx, bdb, bl = (dev.wrap_tensor(t) for t in (sW, sx, bt, stt, dWt, dxt, dbt, lt))
+    bsmall = dev.wrap_tensor(small)
+
     def reduce_small():
         if world > 1:
-            with torch.cuda.stream(tstream):
-                dist.all_reduce(small)
+            grp.all_reduce_sum(bsmall, Cc + 1, st)   # db and the loss: one call of the library's own all-reduce
 
     def fwd():
         ops.mse_tanh_fwd(st, bW, bx, bb, bt_, bl, cnt, Cc, denom)
@@ -692,9 +693,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workloads", default="all", choices=["all", "main"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--gather", default="p2p16", choices=["pull16", "p2p16", "p2p", "nccl"],
-                    help="N > 1: how the image is gathered.  pull16: every rank reads its peers' uint16 counts over NVLink and "
-                         "widens them in the same kernel; p2p16: uint16 counts pushed by the copy engines, widened on arrival; "
+    ap.add_argument("--gather", default="push16", choices=["push16", "pull16", "p2p", "nccl"],
+                    help="N > 1: how the image is gathered.  push16: the library's own exchange (vrhi_exchange_*): uint16 counts stored "
+                         "into the peers by a small kernel, no collective library; pull16: every rank reads its peers' uint16 counts over NVLink and "
+                         "widens them in the same kernel; "
                          "p2p: uint32 rows pushed by the copy engines; nccl: NCCL all-gather")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -716,7 +718,7 @@ def main():
 
     import vernondsl_b200 as vd
     from vernondsl_b200 import _lib as L
-    from vernondsl_b200 import ops, partition
+    from vernondsl_b200 import group, ops, partition
 
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -769,7 +771,7 @@ def main():
     COMM_STREAMS = 2 if (os.environ.get("VRHI_BENCH_COMM_STREAMS", "1") == "2" and world > 2) else 1   # pushes to odd and even peers on two streams
     # Group g takes slabs g, g+GROUPS, g+2*GROUPS, ...: every group is a thin comb over the whole image, so the
     # groups cost the same although the rows near the set cost far more than the rows at the edges.
-    exchange = None
+    exchange, grp = None, None
     n_slabs = plan.part.chunk_count
     group_params, group_slabs = [], []
     if world > 1:
@@ -784,16 +786,15 @@ def main():
             comm_stream2 = torch.cuda.Stream(device=local)
             comm_st2 = dev.wrap_stream(comm_stream2.cuda_stream)
         exchange = None
+        grp = group.Group(dev, world, rank, group.torch_allgather())   # bootstrap over the process group; the data path is the library's
         if args.gather != "nccl":
             try:
-                if args.gather == "pull16":
+                if args.gather == "push16":
+                    exchange = grp.image_exchange(image, W, H, 128)
+                elif args.gather == "pull16":
                     exchange = partition.PullImageExchange(dev, image, plan, W, groups=len(group_params))
                     sig_stream = torch.cuda.Stream(device=local)
                     sig_st = dev.wrap_stream(sig_stream.cuda_stream)
-                elif args.gather == "p2p16":
-                    exchange = partition.WireImageExchange(dev, image, plan, W)
-                    arrive_stream = torch.cuda.Stream(device=local)
-                    arrive_st = dev.wrap_stream(arrive_stream.cuda_stream)
                 else:
                     exchange = partition.PeerImageExchange(dev, image, plan, W * 4)
             except Exception as exc:  # no peer mapping on this box: fall back to the NCCL gather
@@ -804,7 +805,7 @@ def main():
         tstream2 = torch.cuda.Stream(device=local)
         st2 = dev.wrap_stream(tstream2.cuda_stream)
     pulling = isinstance(exchange, partition.PullImageExchange)
-    pushing16 = isinstance(exchange, partition.WireImageExchange)
+    native = isinstance(exchange, group.Exchange)
     trace = []   # (label, event) of one extra, untimed step when VRHI_BENCH_TRACE is set: where a step's time goes
     TRACING = [False]
 
@@ -820,7 +821,22 @@ def main():
             return
         works = []
         mark("start", tstream)
-        wire = exchange.wire if (pulling or pushing16) else None
+        if native:
+            # the whole exchange is the library's: publish after each group's launch, complete at the end of the step
+            wire = exchange.wire
+            if TWO_COMPUTE_STREAMS:
+                tstream2.wait_stream(tstream)
+            for gi, (gp, slabs) in enumerate(zip(group_params, group_slabs)):
+                cs_t, cs = (tstream2, st2) if (TWO_COMPUTE_STREAMS and gi % 2) else (tstream, st)
+                ops.escape_time(cs, image, gp, wire=wire)
+                mark(f"computed {gi}", cs_t)
+                exchange.publish(cs, slabs)
+            if TWO_COMPUTE_STREAMS:
+                tstream.wait_stream(tstream2)
+            exchange.complete(st)
+            mark("exchange complete", tstream)
+            return
+        wire = exchange.wire if pulling else None
         if TWO_COMPUTE_STREAMS:
             tstream2.wait_stream(tstream)
         for gi, (gp, slabs) in enumerate(zip(group_params, group_slabs)):
@@ -847,18 +863,6 @@ def main():
                 else:
                     exchange.push(comm_st, slabs)
                 mark(f"pushed {gi}", comm_stream)
-                if pushing16:
-                    # arrival on a third stream, so that the next push does not queue behind it: the all-reduce and
-                    # the widening kernel get few issue slots while the escape-time kernel runs and catch up after it
-                    pev = torch.cuda.Event()
-                    pev.record(comm_stream)
-                    arrive_stream.wait_event(pev)
-                    if COMM_STREAMS == 2:
-                        pev2 = torch.cuda.Event()
-                        pev2.record(comm_stream2)
-                        arrive_stream.wait_event(pev2)
-                    exchange.finish(arrive_stream, arrive_st, slabs)
-                    mark(f"widened {gi}", arrive_stream)
             else:
                 with torch.cuda.stream(comm_stream):
                     works += partition.all_gather_image(image_t, plan, async_op=True, slabs=slabs)
@@ -869,12 +873,9 @@ def main():
             tstream.wait_stream(comm_stream)
             exchange.next_step()
         elif exchange is not None:
-            if pushing16:
-                tstream.wait_stream(arrive_stream)
-            else:
-                if COMM_STREAMS == 2:
-                    comm_stream.wait_stream(comm_stream2)
-                exchange.finish(comm_stream)
+            if COMM_STREAMS == 2:
+                comm_stream.wait_stream(comm_stream2)
+            exchange.finish(comm_stream)
             mark("exchange complete", comm_stream)
             tstream.wait_stream(comm_stream)
             if COMM_STREAMS == 2:
@@ -885,10 +886,10 @@ def main():
                     w.wait()   # the compute stream waits for the gathers: the step is complete after this
 
     EXCHANGE_NOTE = ("none" if world == 1 else
+                     "vrhi_exchange (C ABI, no collective library): every rank stores its uint16 rows into its peers' wire images over NVLink from a "
+                     "small kernel beside the next group's compute, sequence flags with bounded device waits, widened on arrival" if native else
                      "no collective: each rank reads its peers' rows as uint16 out of their memory over NVLink and widens them into "
                      "its uint32 image in one kernel, group by group while later groups compute; readiness flags with bounded device waits" if pulling else
-                     "counts pushed as uint16 into every peer's wire image by strided peer copies (copy engines over NVLink), overlapped "
-                     "with compute, widened into the uint32 image after a 4-byte NCCL all-reduce" if pushing16 else
                      "image chunks pushed into every peer's image by strided peer copies (copy engines over NVLink), overlapped with "
                      "compute; one 4-byte NCCL all-reduce orders completion" if exchange is not None else
                      "in-place NCCL all-gather of the image each step, overlapped with compute")
@@ -918,12 +919,12 @@ def main():
     def count_launches():
         # kernels of this library on every stream a step uses (compute, and the arrival or pull streams)
         n = st.launch_count()
+        if native:
+            n += exchange.launch_count()
         if world > 1:
             n += comm_st.launch_count()
             if TWO_COMPUTE_STREAMS:
                 n += st2.launch_count()
-            if pushing16:
-                n += arrive_st.launch_count()
             if pulling:
                 n += sig_st.launch_count()
         return n
@@ -1080,7 +1081,7 @@ def main():
         torch.cuda.empty_cache()
         if world == 1:
             others += frame_workloads(dev, st, torch, fp32_peak, fp32_nominal)
-        others += hbm_workloads(dev, st, tstream, torch, rank, world, hbm_peak, peak_kind)
+        others += hbm_workloads(dev, st, torch, rank, world, hbm_peak, peak_kind, grp)
 
     if rank == 0:
         achieved = OPS_PER_ITER * total_iters / (compute_ms * 1e-3) / 1e9 / world  # per GPU
@@ -1123,6 +1124,8 @@ def main():
     barrier()
     if exchange is not None:
         exchange.close()
+    if grp is not None:
+        grp.close()
     if world > 1:
         dist.destroy_process_group()
 

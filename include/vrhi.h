@@ -48,7 +48,8 @@ enum vrhi_status {
   VRHI_ERR_TIMEOUT = -5,     /* a bounded device-side wait gave up                            */
   VRHI_ERR_NOT_FOUND = -6,   /* unknown operator or semantic name                             */
   VRHI_ERR_SIZE = -7,        /* buffer too small / size mismatch / misaligned offset          */
-  VRHI_ERR_GRAPH = -8        /* execution-graph construction or compilation error            */
+  VRHI_ERR_GRAPH = -8,       /* execution-graph construction or compilation error            */
+  VRHI_ERR_PEER = -9         /* another rank's memory could not be mapped, or the caller's all-gather failed */
 };
 
 /* Thread-local text of the last error on this thread ("" if none).  Never NULL. */
@@ -80,6 +81,8 @@ typedef struct vrhi_stream_t *vrhi_stream;
 typedef struct vrhi_event_t *vrhi_event;
 typedef struct vrhi_graph_t *vrhi_graph;
 typedef struct vrhi_sequence_t *vrhi_sequence;
+typedef struct vrhi_group_t *vrhi_group;
+typedef struct vrhi_exchange_t *vrhi_exchange;
 
 /* ------------------------------------------------------------------- device ------------- */
 /* Stands in for fractal.py:5 (ti.init(arch=...)): choose and open the compute device. */
@@ -424,6 +427,71 @@ VRHI_API int vrhi_partition_rows(uint64_t total_rows, uint32_t chunk_rows, uint3
 /* Split `n` leading-axis units evenly (first n%world ranks get one more). */
 VRHI_API int vrhi_partition_leading(uint64_t n, uint32_t world, uint32_t rank, uint64_t *out_begin,
                                     uint64_t *out_count);
+
+/* ------------------------------------------------------------- groups of GPUs ----------- */
+/* N GPUs of one box, one rank per GPU; a rank is a process, or a thread of a process that drives
+ * several GPUs.  The reference runs on one device (fractal.py:5): none of this has a counterpart
+ * there.  The library brings no network layer and no collective library: to learn of each other's
+ * buffers the ranks need ONE service from the caller, an all-gather of small byte records (MPI,
+ * a key-value store, pipes, shared memory ...), used only while a group or an exchange is being
+ * created.  Everything after that is kernels of this library storing into mapped peer memory over
+ * NVLink and sequence numbers in flag arrays; each device-side wait is one warp with a time limit
+ * (default 2 s) that records VRHI_ERR_TIMEOUT in a status word instead of hanging.
+ *
+ * vrhi_allgather_fn: `send` holds `bytes` bytes of this rank; on return `recv` holds world*bytes
+ * bytes, rank r's record at offset r*bytes.  Returns 0 on success.  Every rank calls the creating
+ * functions in the same order, so the all-gathers match up. */
+typedef int (*vrhi_allgather_fn)(void *user, const void *send, void *recv, uint64_t bytes);
+#define VRHI_GROUP_MAX_WORLD 8
+VRHI_API int vrhi_group_create(vrhi_device dev, uint32_t world, uint32_t rank, vrhi_allgather_fn allgather, void *user,
+                               vrhi_group *out_group);
+/* Every rank calls it, once no rank uses the group any more: the ranks meet once inside (one round of
+ * the all-gather), because a rank's memory must outlive the other ranks' mappings of it.  The same
+ * holds for vrhi_exchange_destroy.  NULL is accepted. */
+VRHI_API int vrhi_group_destroy(vrhi_group group);
+VRHI_API int vrhi_group_info(vrhi_group group, uint32_t *out_world, uint32_t *out_rank);
+VRHI_API int vrhi_group_set_wait_ms(vrhi_group group, uint32_t wait_ms); /* limit of the device-side waits; 0 = 2000 */
+/* Sum of `n` floats (n <= 16384) at `offset` bytes of `buf` over all ranks, in place, enqueued on
+ * `stream`: the db row and the loss of a row-sharded backward, partial reductions.  Every rank adds
+ * the ranks' values in rank order: the same bits everywhere.  Calls of one rank must be ordered one
+ * behind the other on the GPU (one stream, or streams that wait for each other), and every rank
+ * makes the same calls in the same order.  A peer that does not arrive within the time limit
+ * leaves `buf` untouched; vrhi_stream_check(stream) then returns VRHI_ERR_TIMEOUT. */
+VRHI_API int vrhi_group_all_reduce_sum_f32(vrhi_group group, vrhi_buffer buf, uint64_t offset, uint64_t n, vrhi_stream stream);
+
+/* Gather of an escape-time image whose row chunks are dealt to the ranks round-robin
+ * (vrhi_partition_rows, VRHI_PART_CYCLIC): every rank ends every step with the whole uint32 image.
+ * `image` is this rank's full-size image [height][width]; height must be a whole number of chunks
+ * and the chunks must divide evenly over the ranks; width a multiple of 8.  Counts cross NVLink as
+ * uint16 (max_iter <= 65535): the exchange owns two uint16 wire images per rank, which alternate
+ * from step to step so that a fast rank never stores into rows a slower peer is still reading.
+ *
+ * One step on every rank:
+ *   vrhi_exchange_wire(ex, &wire);                     the wire image of this step
+ *   for each group of slabs (the same groups, in the same order, on every rank; a slab = `world`
+ *   consecutive chunks, one per rank):
+ *     vrhi_op_launch(compute_stream, escape_time, {image, wire}, params of the rank's chunks of the group);
+ *     vrhi_exchange_publish(ex, compute_stream, slab_first, slab_count, slab_stride);
+ *   vrhi_exchange_complete(ex, stream);
+ * publish, behind the work already enqueued on compute_stream, stores the rank's rows of those
+ * slabs into every peer's wire image and raises its sequence number there (on a stream of the
+ * exchange, so the next group's kernel is not held up), and enqueues the receiving side: a bounded
+ * wait for every peer's number, then the widening of their rows into `image`.  complete makes
+ * `stream` wait for all of the step's arrivals and for this rank's own stores, and switches to the
+ * other wire image; work enqueued on `stream` afterwards sees the whole image, and the next step's
+ * launches must be ordered behind it.  No host synchronisation anywhere in a step.
+ * vrhi_exchange_check synchronises the exchange's streams and returns VRHI_ERR_TIMEOUT if a peer
+ * failed to arrive in time (its rows are then missing from the image). */
+VRHI_API int vrhi_exchange_create(vrhi_group group, vrhi_buffer image, uint32_t width, uint32_t height, uint32_t chunk_rows,
+                                  vrhi_exchange *out_exchange);
+VRHI_API int vrhi_exchange_destroy(vrhi_exchange exchange); /* before the group; NULL is accepted */
+VRHI_API int vrhi_exchange_wire(vrhi_exchange exchange, vrhi_buffer *out_wire);
+VRHI_API int vrhi_exchange_publish(vrhi_exchange exchange, vrhi_stream compute_stream, uint32_t slab_first,
+                                   uint32_t slab_count, uint32_t slab_stride);
+VRHI_API int vrhi_exchange_complete(vrhi_exchange exchange, vrhi_stream stream);
+VRHI_API int vrhi_exchange_check(vrhi_exchange exchange);
+/* Kernels the exchange has launched on its own streams so far. */
+VRHI_API int vrhi_exchange_launch_count(vrhi_exchange exchange, uint64_t *out_count);
 
 /* ------------------------------------------------------------- execution graph ---------- */
 /* A small tensor graph over [rows][cols] float arrays, [cols] row vectors (broadcast down the

@@ -1,7 +1,8 @@
 """One rank of the multi-GPU gather test (launched by test_multi_gpu.py through torch.distributed.run).
 
 Every rank computes its comb of chunks of a small Julia image, the image is gathered with each
-exchange in turn, and every rank compares its whole image with the CPU oracle."""
+exchange in turn (the library's own first among them), and every rank compares its whole image with
+the CPU oracle."""
 import os
 import sys
 
@@ -72,19 +73,50 @@ def main() -> int:
     check("p2p")
     ex.close()
 
-    # uint16 on the wire, widened on arrival; two steps, so that stale wire rows would show
-    ex = partition.WireImageExchange(dev, image, plan, W)
-    for step in range(2):
-        ex.wire.fill(0xDD)
-        dev.synchronize()
-        dist.barrier()
+    # the library's own exchange (vrhi_exchange_*): uint16 rows stored into the peers, sequence flags, two wire
+    # images in turn.  Three steps with a different constant each, back to back: no host synchronisation and no
+    # barrier between them, every step's image downloaded behind it on the stream, so that a stale or an early
+    # row of a neighbouring step would show.
+    from vernondsl_b200 import group
+
+    grp = group.Group(dev, world, rank, group.torch_allgather())
+    ex = grp.image_exchange(image, W, H, chunk_rows)
+    constants = [0.156, 0.21, -0.09]
+    hosts = [vd.PinnedArray((H, W), np.uint32) for _ in constants]
+    for step, ci in enumerate(constants):
+        wire = ex.wire
         for g, p, comb in groups():
-            ops.escape_time(st, image, p, wire=ex.wire)
-            cstream.wait_stream(tstream)
-            ex.push(cst, comb)
-            ex.finish(cstream, cst, comb)
-        check(f"p2p16 step {step}")
+            p.ci = ci
+            ops.escape_time(st, image, p, wire=wire)
+            ex.publish(st, comb)
+        ex.complete(st)
+        image.download(hosts[step].array, stream=st)
+    st.synchronize()
+    ex.check()
+    for step, ci in enumerate(constants):
+        ref, _ = oracle.escape_time(oracle.JULIA, W, H, -1.6, -1.6, dx, dy, -0.8, ci, max_iter)
+        if not np.array_equal(hosts[step].array, ref):
+            failures.append(f"vrhi_exchange step {step}: {int((hosts[step].array != ref).sum())} pixels differ on rank {rank}")
+    # the library's all-reduce: the same bits on every rank, equal to the sum in rank order
+    vec = dev.from_numpy((np.arange(5000, dtype=np.float32) * np.float32(0.37) + np.float32(rank) / 8), L.STORAGE_BUFFER)
+    for _ in range(2):
+        vec.upload((np.arange(5000, dtype=np.float32) * np.float32(0.37) + np.float32(rank) / 8))
+        grp.all_reduce_sum(vec, 5000, st)
+        st.check()
+        expect = np.zeros(5000, np.float32)
+        for r in range(world):
+            expect = (expect + (np.arange(5000, dtype=np.float32) * np.float32(0.37) + np.float32(r) / 8)).astype(np.float32) if r else (np.arange(5000, dtype=np.float32) * np.float32(0.37) + np.float32(0) / 8)
+        if not np.array_equal(vec.download(dtype=np.float32, shape=(5000,)), expect):
+            failures.append(f"vrhi_group_all_reduce_sum_f32 differs from the rank-order sum on rank {rank}")
+    for h in hosts:
+        h.close()
+    vec.close()
+    dist.barrier()
     ex.close()
+    grp.close()
+    image.fill(0xEE)
+    dev.synchronize()
+    dist.barrier()
 
     # pull form: signals and bounded waits, two wire images alternating
     ex = partition.PullImageExchange(dev, image, plan, W, groups=G, wait_ms=5000)

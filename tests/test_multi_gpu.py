@@ -1,6 +1,7 @@
-"""GPU, two or more devices: every form of the image gather (NCCL all-gather, peer pushes of uint32
-rows, uint16 on the wire with widening, the pull form with signals and bounded waits) must leave the
-whole image, bit-exact against the CPU oracle, on every rank.  Skipped on a single-GPU box."""
+"""GPU, two or more devices: every form of the image gather (the library's own exchange over three
+back-to-back steps with changing data, NCCL all-gather, peer pushes of uint32 rows, the pull form
+with signals and bounded waits) must leave the whole image, bit-exact against the CPU oracle, on
+every rank, and the library's all-reduce must give the rank-order sum.  Skipped on a single-GPU box."""
 import os
 import subprocess
 import sys

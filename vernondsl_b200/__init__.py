@@ -2,7 +2,7 @@
 
 The product is ``libvrhi.so`` (CUDA kernels behind the C ABI of ``include/vrhi.h``); this package
 is the thin Python host layer over it: handles (:mod:`rhi`), operator launches (:mod:`ops`), the
-execution graph (:mod:`graph`), the multi-GPU partitioner (:mod:`partition`) and a small
+execution graph (:mod:`graph`), groups of GPUs (:mod:`group`, :mod:`partition`) and a small
 Taichi-style front end for programs written like the reference's fractal.py (:mod:`lang`).
 Nothing in the package computes on the CPU; without the built library it raises.
 """

@@ -15,11 +15,11 @@ LIB_PATH = os.path.join(_HERE, "libvrhi.so")
 CSRC = os.path.join(_HERE, "csrc")
 
 # status codes (include/vrhi.h: enum vrhi_status)
-OK, ERR_INVALID, ERR_CUDA, ERR_OOM, ERR_UNSUPPORTED, ERR_TIMEOUT, ERR_NOT_FOUND, ERR_SIZE, ERR_GRAPH = (
-    0, -1, -2, -3, -4, -5, -6, -7, -8)
+OK, ERR_INVALID, ERR_CUDA, ERR_OOM, ERR_UNSUPPORTED, ERR_TIMEOUT, ERR_NOT_FOUND, ERR_SIZE, ERR_GRAPH, ERR_PEER = (
+    0, -1, -2, -3, -4, -5, -6, -7, -8, -9)
 STATUS_NAMES = {0: "VRHI_OK", -1: "VRHI_ERR_INVALID", -2: "VRHI_ERR_CUDA", -3: "VRHI_ERR_OOM",
                 -4: "VRHI_ERR_UNSUPPORTED", -5: "VRHI_ERR_TIMEOUT", -6: "VRHI_ERR_NOT_FOUND",
-                -7: "VRHI_ERR_SIZE", -8: "VRHI_ERR_GRAPH"}
+                -7: "VRHI_ERR_SIZE", -8: "VRHI_ERR_GRAPH", -9: "VRHI_ERR_PEER"}
 
 # argument classes: the vernon.semantic vocabulary (VernonToSpirv.cpp:44-55, color.mlir:9,44)
 INPUT, OUTPUT, UNIFORM, UNIFORM_CONSTANT, STORAGE_BUFFER, IMAGE, VARYING = range(7)
@@ -124,6 +124,9 @@ class RowPartition(C.Structure):
 
 _vp, _i, _u64, _sz = C.c_void_p, C.c_int, C.c_uint64, C.c_size_t
 _P = C.POINTER
+_u32 = C.c_uint32
+# int (*vrhi_allgather_fn)(void *user, const void *send, void *recv, uint64_t bytes)
+ALLGATHER_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64)
 
 # name -> argtypes; every function returns int unless listed in _RESTYPES
 PROTOTYPES = {
@@ -180,6 +183,18 @@ PROTOTYPES = {
     "vrhi_col_sum_static_scratch": [_vp, _vp, _u64, _u64, _vp],
     "vrhi_partition_rows": [_u64, C.c_uint32, C.c_uint32, C.c_uint32, _i, _P(RowPartition)],
     "vrhi_partition_leading": [_u64, C.c_uint32, C.c_uint32, _P(_u64), _P(_u64)],
+    "vrhi_group_create": [_vp, _u32, _u32, ALLGATHER_FN, _vp, _P(_vp)],
+    "vrhi_group_destroy": [_vp],
+    "vrhi_group_info": [_vp, _P(_u32), _P(_u32)],
+    "vrhi_group_set_wait_ms": [_vp, _u32],
+    "vrhi_group_all_reduce_sum_f32": [_vp, _vp, _u64, _u64, _vp],
+    "vrhi_exchange_create": [_vp, _vp, _u32, _u32, _u32, _P(_vp)],
+    "vrhi_exchange_destroy": [_vp],
+    "vrhi_exchange_wire": [_vp, _P(_vp)],
+    "vrhi_exchange_publish": [_vp, _vp, _u32, _u32, _u32],
+    "vrhi_exchange_complete": [_vp, _vp],
+    "vrhi_exchange_check": [_vp],
+    "vrhi_exchange_launch_count": [_vp, _P(_u64)],
     "vrhi_graph_create": [_vp, _u64, _u64, _P(_vp)],
     "vrhi_graph_destroy": [_vp],
     "vrhi_graph_set_flags": [_vp, C.c_uint32],

@@ -72,6 +72,18 @@ __device__ __forceinline__ void store_count(void *image, size_t pix, uint32_t co
 // peers when the image is gathered; counts up to 65535 lose nothing).
 __device__ __forceinline__ void store_wire(uint16_t *wire, size_t pix, uint32_t count) { wire[pix] = (uint16_t)count; }
 
+// Order in which a launch visits its rows: from the middle outwards (k = 0 is the middle row).  The
+// expensive rows of these images lie around the middle and hold the pixels that run for thousands
+// of steps; a pixel started late is a tail nothing else covers (one warp, one dependent chain, tens
+// of microseconds), so those rows go first and the cheap outer rows, whose pixels end within a few
+// steps, go last.
+__device__ __forceinline__ uint32_t middle_out(uint32_t k, uint32_t rows) {
+  const uint32_t mid = rows >> 1, h = (k + 1u) >> 1;
+  // k odd: rows below the middle (mid-1, mid-2, ...); k even: the middle and above; past the shorter side the rest follows in order
+  if (k & 1u) return h <= mid ? mid - h : k;
+  return mid + h < rows ? mid + h : rows - 1u - k;
+}
+
 // Row of the image that owned row r maps to (rows are owned in chunks dealt round-robin).
 __device__ __forceinline__ uint32_t owned_row_to_image_row(const EscapeDev &p, uint32_t r) {
   uint32_t k = r / p.chunk_rows;

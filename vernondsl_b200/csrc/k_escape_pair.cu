@@ -150,8 +150,9 @@ __global__ void __launch_bounds__(256, 4) escape_pair_kernel(EscapeDev p, void *
       if (lane == 0) batch = atomicAdd(work_counter, 1u);
       batch = __shfl_sync(FULL, batch, 0);
       if (batch >= p.n_batches) { fresh = false; return; }
-      const uint32_t r = batch / p.batches_per_row;
-      tile = (batch - r * p.batches_per_row) * p.batch_tiles;
+      const uint32_t k = batch / p.batches_per_row;
+      tile = (batch - k * p.batches_per_row) * p.batch_tiles;
+      const uint32_t r = middle_out(k, p.rows_owned);  // expensive rows first: their long pixels end under cover of the rest
       tile_end = min(tile + p.batch_tiles, p.tiles_per_row);
       const uint32_t j = owned_row_to_image_row(p, r);
       row_y = __fadd_rn(p.y0, __fmul_rn((float)j, p.dy));

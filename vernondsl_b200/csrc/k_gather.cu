@@ -1,5 +1,7 @@
 // Receiving side of the image gather: counts arrive from the peers as uint16 (half the bytes on
 // NVLink) and are widened into the uint32 image here.
+#include <cstdlib>
+
 #include "vrhi_internal.h"
 
 namespace vrhi {
@@ -10,7 +12,10 @@ namespace vrhi {
 template <bool VEC>
 __global__ void __launch_bounds__(256) widen_rows_u16_kernel(const uint16_t *__restrict__ wire, uint32_t *__restrict__ image,
                                                              uint32_t width, uint32_t height, uint32_t chunk_rows, uint32_t world,
-                                                             uint32_t skip_rank, uint32_t slab_first, uint32_t slab_stride, uint32_t total_rows) {
+                                                             uint32_t skip_rank, uint32_t slab_first, uint32_t slab_stride, uint32_t total_rows,
+                                                             const uint32_t *ok = nullptr) {
+  // `ok` is the verdict of a bounded wait that ran before this kernel in the stream: 0 = it gave up, widen nothing
+  if (ok && *reinterpret_cast<const volatile uint32_t *>(ok) == 0u) return;
   const uint32_t nq = skip_rank < world ? world - 1 : world;
   const uint32_t rows_per_slab = nq * chunk_rows;
   for (uint32_t u = blockIdx.y; u < total_rows; u += gridDim.y) {
@@ -37,16 +42,10 @@ __global__ void __launch_bounds__(256) widen_rows_u16_kernel(const uint16_t *__r
   }
 }
 
-int launch_widen_rows_u16(vrhi_stream_t *st, const ArgView *args, int n_args, const void *params, size_t params_size) {
-  vrhi_widen_params q;
-  VRHI_TRY(read_params(params, params_size, &q));
-  if (n_args != 2) return fail(VRHI_ERR_INVALID, "widen_rows_u16 takes 2 arguments (wire, image), got %d", n_args);
-  if (!writable(args[1])) return fail(VRHI_ERR_INVALID, "widen_rows_u16: the image buffer is read-only (class %s)", vrhi_arg_class_name(args[1].buf_cls));
+// wire -> image for the given slabs; `ok` (optional) guards the launch, see the kernel
+int widen_rows_u16(vrhi_stream_t *st, const uint16_t *wire, uint32_t *image, const vrhi_widen_params &q, const uint32_t *ok) {
   if (q.width == 0 || q.height == 0) return fail(VRHI_ERR_SIZE, "widen_rows_u16: empty image");
   if (q.chunk_rows == 0 || q.world == 0) return fail(VRHI_ERR_INVALID, "widen_rows_u16: chunk_rows and world must be >= 1");
-  const uint64_t px = (uint64_t)q.width * q.height;
-  if (args[0].bytes < px * 2) return fail(VRHI_ERR_SIZE, "widen_rows_u16: the wire view holds %llu bytes, %llu needed", (unsigned long long)args[0].bytes, (unsigned long long)(px * 2));
-  if (args[1].bytes < px * 4) return fail(VRHI_ERR_SIZE, "widen_rows_u16: the image view holds %llu bytes, %llu needed", (unsigned long long)args[1].bytes, (unsigned long long)(px * 4));
   const uint64_t n_chunks = ((uint64_t)q.height + q.chunk_rows - 1) / q.chunk_rows;
   const uint64_t n_slabs = (n_chunks + q.world - 1) / q.world;
   const uint32_t stride = q.slab_stride ? q.slab_stride : 1u;
@@ -56,19 +55,28 @@ int launch_widen_rows_u16(vrhi_stream_t *st, const ArgView *args, int n_args, co
   const uint64_t total_rows = (uint64_t)q.slab_count * nq * q.chunk_rows;
   if (total_rows == 0) return VRHI_OK;  // nothing to widen (one rank, or an empty slab range)
   if (total_rows > 0xffffffffull) return fail(VRHI_ERR_UNSUPPORTED, "widen_rows_u16: too many rows");
-  const bool vec = q.width % 8 == 0 && ((uintptr_t)args[0].ptr % 16 == 0) && ((uintptr_t)args[1].ptr % 16 == 0);
+  const bool vec = q.width % 8 == 0 && ((uintptr_t)wire % 16 == 0) && ((uintptr_t)image % 16 == 0);
   dim3 grid;
   grid.y = (unsigned)(total_rows < 32768 ? total_rows : 32768);
   if (vec) {
     grid.x = (q.width / 8 + 255) / 256;
-    widen_rows_u16_kernel<true><<<grid, 256, 0, st->s>>>(reinterpret_cast<const uint16_t *>(args[0].ptr), reinterpret_cast<uint32_t *>(args[1].ptr),
-                                                         q.width, q.height, q.chunk_rows, q.world, q.skip_rank, q.slab_first, stride, (uint32_t)total_rows);
+    widen_rows_u16_kernel<true><<<grid, 256, 0, st->s>>>(wire, image, q.width, q.height, q.chunk_rows, q.world, q.skip_rank, q.slab_first, stride, (uint32_t)total_rows, ok);
   } else {
     grid.x = (q.width + 255) / 256 < 64 ? (q.width + 255) / 256 : 64;
-    widen_rows_u16_kernel<false><<<grid, 256, 0, st->s>>>(reinterpret_cast<const uint16_t *>(args[0].ptr), reinterpret_cast<uint32_t *>(args[1].ptr),
-                                                          q.width, q.height, q.chunk_rows, q.world, q.skip_rank, q.slab_first, stride, (uint32_t)total_rows);
+    widen_rows_u16_kernel<false><<<grid, 256, 0, st->s>>>(wire, image, q.width, q.height, q.chunk_rows, q.world, q.skip_rank, q.slab_first, stride, (uint32_t)total_rows, ok);
   }
   return post_launch(st, "widen_rows_u16");
+}
+
+int launch_widen_rows_u16(vrhi_stream_t *st, const ArgView *args, int n_args, const void *params, size_t params_size) {
+  vrhi_widen_params q;
+  VRHI_TRY(read_params(params, params_size, &q));
+  if (n_args != 2) return fail(VRHI_ERR_INVALID, "widen_rows_u16 takes 2 arguments (wire, image), got %d", n_args);
+  if (!writable(args[1])) return fail(VRHI_ERR_INVALID, "widen_rows_u16: the image buffer is read-only (class %s)", vrhi_arg_class_name(args[1].buf_cls));
+  const uint64_t px = (uint64_t)q.width * q.height;
+  if (args[0].bytes < px * 2) return fail(VRHI_ERR_SIZE, "widen_rows_u16: the wire view holds %llu bytes, %llu needed", (unsigned long long)args[0].bytes, (unsigned long long)(px * 2));
+  if (args[1].bytes < px * 4) return fail(VRHI_ERR_SIZE, "widen_rows_u16: the image view holds %llu bytes, %llu needed", (unsigned long long)args[1].bytes, (unsigned long long)(px * 4));
+  return widen_rows_u16(st, reinterpret_cast<const uint16_t *>(args[0].ptr), reinterpret_cast<uint32_t *>(args[1].ptr), q, nullptr);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -227,6 +235,129 @@ int launch_gather_pull_u16(vrhi_stream_t *st, const ArgView *args, int n_args, c
   gather_pull_u16_kernel<<<grid, 256, 0, st->s>>>(pp, ctrl + CTRL_WAIT_OK, reinterpret_cast<uint32_t *>(args[1].ptr),
                                                   q.width, q.height, q.chunk_rows, q.world, q.rank, q.slab_first, stride, (uint32_t)total_rows);
   return post_launch(st, "gather_pull_u16", 2);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Push form of the gather, the one vrhi_exchange_* uses: after computing a group of slabs a rank
+// copies its own uint16 rows out of its wire image into the same rows of every peer's wire image
+// with plain 16-byte stores over NVLink (one load, world-1 stores per thread and trip), then raises
+// its sequence number in every peer's flag array (gather_signal_kernel).  The kernel is built to
+// run BESIDE the escape-time kernel of the next group: blocks of 128 threads and few registers, so
+// that they fit into what four resident escape-time blocks leave of an SM, and a demand of a few
+// bytes per clock and SM, which the issue slots that kernel leaves free cover.
+struct PeerWires {
+  uint16_t *wire[VRHI_GATHER_MAX_WORLD];  // the world-1 peers, any order
+};
+
+constexpr int kPushRows = 4;  // rows in flight per thread
+
+__global__ void __launch_bounds__(128) gather_push_u16_kernel(PeerWires peers, uint32_t n_peers, const uint16_t *__restrict__ wire, uint32_t width,
+                                                              uint32_t height, uint32_t chunk_rows, uint32_t world, uint32_t rank,
+                                                              uint32_t slab_first, uint32_t slab_stride, uint32_t total_rows) {
+  const uint32_t v = blockIdx.x * 128u + threadIdx.x;
+  if (v * 8u >= width) return;
+  for (uint32_t u0 = blockIdx.y; u0 < total_rows; u0 += gridDim.y * kPushRows) {
+    uint4 in[kPushRows];
+    size_t at[kPushRows];
+    bool ok[kPushRows];
+#pragma unroll
+    for (int k = 0; k < kPushRows; ++k) {
+      const uint32_t u = u0 + (uint32_t)k * gridDim.y;
+      ok[k] = false;
+      if (u < total_rows) {
+        const uint32_t slab = u / chunk_rows, rr = u - slab * chunk_rows;
+        const uint64_t row = ((uint64_t)(slab_first + slab * slab_stride) * world + rank) * chunk_rows + rr;
+        if (row < height) {
+          ok[k] = true;
+          at[k] = (size_t)row * width / 8 + v;
+          in[k] = __ldcg(reinterpret_cast<const uint4 *>(wire) + at[k]);  // written by the escape-time kernel just before: L2
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < kPushRows; ++k)
+      if (ok[k])
+        for (uint32_t q = 0; q < n_peers; ++q) __stcg(reinterpret_cast<uint4 *>(peers.wire[q]) + at[k], in[k]);
+  }
+}
+
+int gather_push_u16(vrhi_stream_t *st, uint16_t *const *peer_wires, uint32_t n_peers, const uint16_t *wire, const vrhi_gather_params &q) {
+  if (n_peers == 0 || n_peers >= VRHI_GATHER_MAX_WORLD) return fail(VRHI_ERR_INVALID, "gather push: 1..%d peers", VRHI_GATHER_MAX_WORLD - 1);
+  if (q.width % 8 != 0) return fail(VRHI_ERR_UNSUPPORTED, "gather push: the width must be a multiple of 8 pixels (16-byte accesses)");
+  const uint32_t stride = q.slab_stride ? q.slab_stride : 1u;
+  const uint64_t total_rows = (uint64_t)q.slab_count * q.chunk_rows;
+  if (total_rows == 0) return VRHI_OK;
+  if (total_rows > 0xffffffffull) return fail(VRHI_ERR_UNSUPPORTED, "gather push: too many rows");
+  PeerWires pw{};
+  for (uint32_t k = 0; k < n_peers; ++k) pw.wire[k] = peer_wires[k];
+  dim3 grid;
+  grid.x = (q.width / 8 + 127) / 128;
+  // a few small blocks per SM: enough stores in flight for the link, little enough to sit beside another kernel
+  static const int per_sm = [] { const char *e = getenv("VRHI_PUSH_BLOCKS_PER_SM"); const int v = e ? atoi(e) : 0; return v >= 1 && v <= 16 ? v : 2; }();  // tuning aid
+  const uint64_t want_y = ((uint64_t)st->dev->prop.multiProcessorCount * per_sm + grid.x - 1) / grid.x;
+  const uint64_t max_y = (total_rows + kPushRows - 1) / kPushRows;
+  grid.y = (unsigned)(want_y < max_y ? want_y : max_y);
+  gather_push_u16_kernel<<<grid, 128, 0, st->s>>>(pw, n_peers, wire, q.width, q.height, q.chunk_rows, q.world, q.rank, q.slab_first, stride, (uint32_t)total_rows);
+  return post_launch(st, "gather_push_u16");
+}
+
+// stores `seq` into slot `slot` of each of the n flag arrays (the peers')
+int gather_signal(vrhi_stream_t *st, uint32_t *const *peer_flags, uint32_t n, uint32_t slot, uint32_t seq) {
+  if (n == 0 || n >= VRHI_GATHER_MAX_WORLD) return fail(VRHI_ERR_INVALID, "gather signal: 1..%d peers", VRHI_GATHER_MAX_WORLD - 1);
+  PeerFlags pf{};
+  for (uint32_t k = 0; k < n; ++k) pf.flags[k] = peer_flags[k];
+  gather_signal_kernel<<<1, 32, 0, st->s>>>(pf, n, slot, seq);
+  return post_launch(st, "gather_signal");
+}
+
+// bounded wait until every peer's slot of `flags` has reached `seq`; the verdict lands in the stream's
+// control block (CTRL_WAIT_OK, returned through *ok) for the kernel that follows
+int gather_wait(vrhi_stream_t *st, const uint32_t *flags, uint32_t world, uint32_t rank, uint32_t seq, uint32_t wait_ms, const uint32_t **ok) {
+  uint32_t *ctrl = nullptr;
+  VRHI_TRY(stream_arena(st, 0, &ctrl, nullptr));
+  const uint64_t wait_ns = (uint64_t)(wait_ms ? wait_ms : 2000u) * 1000000ull;
+  gather_wait_kernel<<<1, 32, 0, st->s>>>(flags, world, rank, seq, wait_ns, reinterpret_cast<int32_t *>(ctrl + CTRL_STATUS), ctrl + CTRL_WAIT_OK);
+  if (ok) *ok = ctrl + CTRL_WAIT_OK;
+  return post_launch(st, "gather_wait");
+}
+
+// ---------------------------------------------------------------------------------------------
+// Sum of small float arrays over the ranks (db and the loss of a row-sharded backward, reduction
+// partials): every rank stores its n values into its own slot of every rank's mailbox (its own
+// included), raises its sequence number, waits (bounded) for the others and adds the `world` slots
+// in rank order: the same bits on every rank, no atomics.
+struct PeerBoxes {
+  float *box[VRHI_GATHER_MAX_WORLD];  // mailbox of every rank, indexed by rank: [world][capacity] floats
+};
+
+__global__ void __launch_bounds__(256) box_scatter_kernel(PeerBoxes boxes, uint32_t world, uint32_t rank, const float *__restrict__ src, uint32_t n, uint32_t capacity) {
+  for (uint32_t i = blockIdx.x * 256u + threadIdx.x; i < n; i += gridDim.x * 256u) {
+    const float v = src[i];
+    for (uint32_t q = 0; q < world; ++q) __stcg(boxes.box[q] + (size_t)rank * capacity + i, v);
+  }
+}
+
+__global__ void __launch_bounds__(256) box_sum_kernel(const float *box, const uint32_t *ok, uint32_t world, float *__restrict__ dst, uint32_t n, uint32_t capacity) {
+  if (*reinterpret_cast<const volatile uint32_t *>(ok) == 0u) return;  // the wait gave up: leave dst alone; the host finds VRHI_ERR_TIMEOUT
+  for (uint32_t i = blockIdx.x * 256u + threadIdx.x; i < n; i += gridDim.x * 256u) {
+    float s = __ldcg(box + i);
+    for (uint32_t q = 1; q < world; ++q) s = __fadd_rn(s, __ldcg(box + (size_t)q * capacity + i));
+    dst[i] = s;
+  }
+}
+
+int box_scatter(vrhi_stream_t *st, float *const *boxes, uint32_t world, uint32_t rank, const float *src, uint32_t n, uint32_t capacity) {
+  PeerBoxes pb{};
+  for (uint32_t k = 0; k < world; ++k) pb.box[k] = boxes[k];
+  const unsigned blocks = (n + 255) / 256 < 64 ? (n + 255) / 256 : 64;
+  box_scatter_kernel<<<blocks, 256, 0, st->s>>>(pb, world, rank, src, n, capacity);
+  return post_launch(st, "all_reduce (scatter)");
+}
+
+int box_sum(vrhi_stream_t *st, const float *box, const uint32_t *ok, uint32_t world, float *dst, uint32_t n, uint32_t capacity) {
+  const unsigned blocks = (n + 255) / 256 < 64 ? (n + 255) / 256 : 64;
+  box_sum_kernel<<<blocks, 256, 0, st->s>>>(box, ok, world, dst, n, capacity);
+  return post_launch(st, "all_reduce (sum)");
 }
 
 }  // namespace vrhi

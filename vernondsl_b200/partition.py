@@ -1,18 +1,19 @@
-"""Single-box multi-GPU partitioner: one process per GPU, ``torch.distributed`` for the exchange.
+"""Single-box multi-GPU partitioner: one process per GPU.
 
 Work is split by the planner inside ``libvrhi.so`` (``vrhi_partition_rows`` /
-``vrhi_partition_leading``); this module adds the only exchange steps the path has:
+``vrhi_partition_leading``).  The exchange steps the path has, the gather of an escape-time
+image and the sum of ``db`` and the loss of a row-sharded backward, are the library's own
+(``vrhi_exchange_*`` and ``vrhi_group_all_reduce_sum_f32``, bound in :mod:`vernondsl_b200.group`).
+This module holds the planning helpers around them and three alternative forms of the image
+gather, kept for comparison; they run over ``torch.distributed``:
 
-* escape-time images: every rank computes its own row chunks into a full-size image at their
-  true position, then the chunks are gathered in place (no staging copy, no permutation), by one of
-  :class:`WireImageExchange` (uint16 counts pushed by the copy engines, widened on arrival),
-  :class:`PullImageExchange` (each rank reads its peers' uint16 rows over NVLink and widens them in
-  the same kernel), :class:`PeerImageExchange` (uint32 rows pushed) or :func:`all_gather_image` (NCCL);
-* the tanh-MSE backward: ``db`` and the loss are all-reduced (sum); ``dW`` and ``dx`` stay sharded.
+* :func:`all_gather_image`: in-place all-gather of the row chunks with the process group's
+  backend (NCCL on GPUs; gloo in the CPU tests of this logic);
+* :class:`PeerImageExchange`: uint32 rows pushed into the peers' images by the copy engines;
+* :class:`PullImageExchange`: each rank reads its peers' uint16 rows over NVLink and widens them
+  in the same kernel.
 
 Map and row operators need no exchange: each rank owns a slice of the leading axis.
-Collectives run on tensors that alias the library's buffers, on whatever backend the process
-group was created with (NCCL on GPUs; gloo in the CPU tests of this logic).
 """
 from __future__ import annotations
 
@@ -155,6 +156,12 @@ class PeerImageExchange:
 
     Needs an even cyclic plan (the in-place layout of :func:`all_gather_image`) and an image buffer
     allocated by the library (``Device.empty``); anything else should use :func:`all_gather_image`.
+
+    The pushes land in the peers' images themselves.  A rank must therefore not start the pushes of
+    a step before every peer is done reading the image of the step before: order them behind a
+    collective (or barrier) issued after those reads.  The library's own exchange
+    (:class:`vernondsl_b200.group.Exchange`) needs no such care: it sends through two alternating
+    wire images.
     """
 
     def __init__(self, dev, image, plan: ImagePlan, row_bytes: int, group=None):
@@ -202,41 +209,6 @@ class PeerImageExchange:
         for b in self.peers.values():
             b.close()
         self.peers = {}
-
-
-class WireImageExchange:
-    """The same gather with uint16 counts on the wire: half the bytes cross NVLink.
-
-    The escape-time kernel writes every count twice, as uint32 into the rank's image and as uint16
-    into a wire image of the same geometry (``ops.escape_time(..., wire=exchange.wire)``).  The wire
-    chunks are pushed into the peers' wire images by the copy engines (:class:`PeerImageExchange`);
-    ``finish`` orders the one-element all-reduce behind the pushes and then widens the peers' rows
-    from the local wire image into the uint32 image (``widen_rows_u16``, HBM-bound).  Needs
-    ``max_iter <= 65535``, so that nothing is lost.
-    """
-
-    def __init__(self, dev, image, plan: ImagePlan, width: int, group=None):
-        self.dev, self.image, self.plan, self.width = dev, image, plan, int(width)
-        self.wire = dev.empty((plan.height, self.width), np.uint16, L.IMAGE)
-        self.peer = PeerImageExchange(dev, self.wire, plan, self.width * 2, group)
-        self.n_slabs = self.peer.n_slabs
-
-    def push(self, stream, slabs=None) -> None:
-        self.peer.push(stream, slabs)
-
-    def finish(self, torch_stream, stream, slabs=None) -> None:
-        """``torch_stream`` and ``stream`` are the same CUDA stream (torch's handle for the collective,
-        the library's for the kernel), ordered behind this rank's pushes of ``slabs`` = (first, count,
-        stride), default all.  After this, stream-ordered, the uint32 image holds every rank's rows of
-        those slabs."""
-        self.peer.finish(torch_stream)
-        first, count, stride = slabs if slabs is not None else (0, self.n_slabs, 1)
-        p = self.plan
-        ops.widen_rows_u16(stream, self.wire, self.image, self.width, p.height, p.part.chunk_rows, p.world, p.rank, first, count, stride)
-
-    def close(self) -> None:
-        self.peer.close()
-        self.wire.close()
 
 
 class PullImageExchange:
@@ -291,7 +263,10 @@ class PullImageExchange:
         return self.step * self.groups + g + 1
 
     def signal(self, stream, g: int) -> None:
-        """Enqueue on ``stream`` (behind the kernels that computed group ``g``) the ready mark for the peers."""
+        """Enqueue on ``stream`` (behind the kernels that computed group ``g``) the ready mark for the peers.
+        Precondition: this rank's pulls of the step before the previous one are ordered before this call on the
+        GPU (the two wire images alternate, so the kernels of this step overwrite the rows the peers pulled two
+        steps ago; a peer can be at most one step behind, because this rank's pulls waited for its signals)."""
         ops.gather_signal(stream, self.peer_flags, self.plan.world, self.plan.rank, self._seq(g))
 
     def pull(self, stream, g: int, slabs) -> None:

@@ -133,3 +133,4 @@ def test_struct_layouts_match_the_header():
     assert C.sizeof(L.TapeInstr) == 12
     assert C.sizeof(L.TapeParams) == 4 * 4 + 16 + 12 + 16 + 12 * 64 + 4 + 4 + 4  # flags, colsum_mask, trailing pad to 8
     assert C.sizeof(L.RowPartition) == 24
+

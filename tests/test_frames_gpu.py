@@ -160,3 +160,36 @@ def test_a_recording_can_span_two_streams():
     seq.close()
     for s in (st, side, stray):
         s.close()
+
+
+def test_a_sequence_survives_the_growth_of_its_streams_scratch(dev, stream):
+    """A recorded sequence points into the stream's scratch of its time (the escape-time work counter
+    and the memset that clears it).  An operator that later needs more scratch than the stream holds
+    makes the stream allocate a larger block; the block the sequence points into must stay alive,
+    and both the sequence and the operator must keep giving right answers."""
+    W = H = 512
+    dx, dy = ops.grid_steps(-1.6, 1.6, -1.6, 1.6, W, H)
+    p = ops.escape_params(L.JULIA, W, H, -1.6, -1.6, dx, dy, cr=-0.8, ci=0.156, max_iter=300)
+    img = dev.empty((H, W), np.uint32, L.IMAGE)
+    ops.escape_time(stream, img, p)          # sizes the scratch (4 MiB at first use)
+    stream.check()
+    with stream.record() as seq:
+        ops.escape_time(stream, img, p)
+    want, _ = oracle.escape_time(oracle.JULIA, W, H, -1.6, -1.6, dx, dy, -0.8, 0.156, 300)
+    # column sums of [4096, 8192]: the partial rows need well over 4 MiB of scratch
+    rows, cols = 4096, 8192
+    m = np.random.default_rng(3).standard_normal((rows, cols)).astype(np.float32)
+    M, out = dev.from_numpy(m), dev.empty(cols, np.float32)
+    for _ in range(2):
+        img.fill(0)
+        seq.launch()
+        ops.col_sum(stream, M, out, rows, cols)
+        seq.launch()
+        stream.check()
+        assert np.array_equal(img.download(), want)
+        got = out.download()
+        ref = m.astype(np.float64).sum(axis=0)
+        assert np.abs(got - ref).max() <= 1e-5 * np.abs(m).astype(np.float64).sum(axis=0).max()
+    seq.close()
+    for b in (img, M, out):
+        b.close()

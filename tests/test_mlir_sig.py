@@ -50,10 +50,14 @@ def test_unknown_semantic_is_an_error():
     assert e.value.status == L.ERR_NOT_FOUND
 
 
-REFERENCE_FILE = "/root/reference/source/tests/integration/color.mlir"
+# where a checkout of the reference project lies, if anywhere: VERNON_REFERENCE_ROOT, else a `reference`
+# directory beside the repository; the test is skipped where there is none (a GPU box, for instance)
+_HERE = os.path.dirname(os.path.abspath(__file__))
+REFERENCE_ROOT = os.environ.get("VERNON_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+REFERENCE_FILE = os.path.join(REFERENCE_ROOT, "source", "tests", "integration", "color.mlir")
 
 
-@pytest.mark.skipif(not os.path.exists(REFERENCE_FILE), reason="the reference tree is not mounted here")
+@pytest.mark.skipif(not os.path.exists(REFERENCE_FILE), reason="no checkout of the reference project here")
 def test_reference_shader_file():
     """The reference's own input: vertex_main (color.mlir:4-9) and frag_main (:43-45)."""
     sigs = {s.name: s for s in mlir_sig.parse_signatures(open(REFERENCE_FILE).read())}

@@ -72,3 +72,32 @@ def test_wrapped_torch_tensor_and_stream(dev):
     assert view.data_ptr() == t.data_ptr() and torch.equal(view, t)
     s.close()
     img.close()
+
+
+def test_shapes_whose_byte_count_wraps_are_refused_before_any_launch(dev, stream):
+    """rows * cols * 4 wraps in 64 bits for shapes like 2^40 x 2^24 (2^66 bytes -> 0) and would then pass a
+    size check against a tiny buffer.  Every operator that takes a [rows][cols] shape must refuse such
+    a shape (VRHI_ERR_SIZE) before it launches anything."""
+    import vernondsl_b200 as vd
+    from vernondsl_b200 import ops
+
+    small = dev.empty(1024, np.float32)
+    vec = dev.empty(1024, np.float32)
+    before = stream.launch_count()
+    for rows, cols in ((1 << 40, 1 << 24), (1 << 39, 1 << 26)):
+        for call in (lambda: ops.row_sum(stream, small, vec, rows, cols),
+                     lambda: ops.row_softmax(stream, small, small, rows, cols),
+                     lambda: ops.col_sum(stream, small, vec, rows, cols),
+                     lambda: ops.mse_tanh_fwd(stream, small, small, vec, small, vec, rows, min(cols, 1 << 30)),
+                     lambda: ops.mse_tanh_bwd(stream, small, small, vec, small, small, small, vec, rows, min(cols, 1 << 30))):
+            with pytest.raises(vd.VrhiError) as err:
+                call()
+            assert err.value.status == L.ERR_SIZE
+        t = ops.Tape(1)
+        t.output(t.op("neg", t.input(0)))
+        with pytest.raises(vd.VrhiError) as err:
+            ops.map_tape(stream, t, [small], [small], rows, cols)
+        assert err.value.status == L.ERR_SIZE
+    assert stream.launch_count() == before
+    small.close()
+    vec.close()

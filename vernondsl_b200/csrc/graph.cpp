@@ -837,8 +837,8 @@ int vrhi_graph_create(vrhi_device dev, uint64_t rows, uint64_t cols, vrhi_graph 
   vrhi_graph_t *g = new (std::nothrow) vrhi_graph_t();
   if (!g) return fail(VRHI_ERR_OOM, "host allocation failed");
   g->dev = dev; g->rows = rows; g->cols = cols;
-  const char *e = getenv("VRHI_GRAPH_NO_SPECIALIZE");
-  if (e && *e && *e != '0') g->flags |= 1u;
+  static const bool no_specialize = [] { const char *e = getenv("VRHI_GRAPH_NO_SPECIALIZE"); return e && *e && *e != '0'; }();  // read once per process
+  if (no_specialize) g->flags |= 1u;
   *out_graph = g;
   return VRHI_OK;
 }

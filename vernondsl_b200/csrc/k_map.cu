@@ -82,10 +82,8 @@ int launch_fused_map(vrhi_stream_t *st, const ArgView *args, int n_args, const v
     resident = nb > 0 ? nb : 1;
   }
   uint64_t cap = (uint64_t)sms * resident;
-  if (const char *e = getenv("VRHI_MAP_BLOCKS_PER_SM")) {  // tuning aid
-    const int b = atoi(e);
-    if (b >= 1 && b <= 32) cap = (uint64_t)sms * b;
-  }
+  static const int env_blocks = env_int("VRHI_MAP_BLOCKS_PER_SM", 1, 32, 0);  // tuning aid
+  if (env_blocks) cap = (uint64_t)sms * env_blocks;
   unsigned grid = (unsigned)(want < cap ? (want ? want : 1) : cap);
   fused_map_kernel<2><<<grid, 256, 0, st->s>>>(
       (const float4 *)args[0].ptr, (const float4 *)args[1].ptr, (const float4 *)args[2].ptr, (float4 *)args[3].ptr, n4, q.n,
@@ -458,7 +456,8 @@ int launch_map_tape(vrhi_stream_t *st, const ArgView *args, int n_args, const vo
   if (q.n_inputs > VRHI_TAPE_MAX_INPUTS || q.n_outputs == 0 || q.n_outputs > VRHI_TAPE_MAX_OUTPUTS || q.n_instr > VRHI_TAPE_MAX_INSTR)
     return fail(VRHI_ERR_INVALID, "map_tape: %u inputs / %u outputs / %u instructions outside the limits (%d / 1..%d / %d)", q.n_inputs, q.n_outputs, q.n_instr, VRHI_TAPE_MAX_INPUTS, VRHI_TAPE_MAX_OUTPUTS, VRHI_TAPE_MAX_INSTR);
   if (n_args != (int)(q.n_inputs + q.n_outputs)) return fail(VRHI_ERR_INVALID, "map_tape: %d arguments passed, tape declares %u inputs + %u outputs", n_args, q.n_inputs, q.n_outputs);
-  const uint64_t n = q.rows * q.cols;
+  uint64_t n = 0;
+  VRHI_TRY(element_count(q.rows, q.cols, "map_tape", &n));
   if (n == 0) return VRHI_OK;
   if ((q.row_vector_mask & q.col_vector_mask) | (q.row_vector_mask & q.scalar_mask) | (q.col_vector_mask & q.scalar_mask))
     return fail(VRHI_ERR_INVALID, "map_tape: an input is marked with more than one broadcast shape");

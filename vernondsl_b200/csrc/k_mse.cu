@@ -59,7 +59,7 @@ __device__ __forceinline__ void bwd_one(float w, float x, float b, float t, floa
   lsum = fmaf(d, d, lsum);
 }
 
-template <bool VEC, bool PAIR = true>
+template <bool VEC>
 __global__ void __launch_bounds__(256) mse_bwd_kernel(const float *__restrict__ W, const float *__restrict__ X,
                                                       const float *__restrict__ B, const float *__restrict__ Tt,
                                                       float *__restrict__ dW, float *__restrict__ dX,
@@ -80,26 +80,7 @@ __global__ void __launch_bounds__(256) mse_bwd_kernel(const float *__restrict__ 
       float4 *dx4 = reinterpret_cast<float4 *>(dX) + cg;
       uint64_t r = blockIdx.y;
       const uint64_t step = gridDim.y;
-      // PAIR: two rows per trip, six independent 16-byte loads in flight per thread (kept for comparison;
-      // the launcher uses one row per trip, which needs fewer registers and measured faster)
-      for (; PAIR && r + step < rows; r += 2 * step) {
-        const uint64_t o0 = r * cols4, o1 = (r + step) * cols4;
-        const float4 wa = __ldcs(w4 + o0), xa = __ldcs(x4 + o0), ta = __ldcs(t4 + o0);
-        const float4 wb = __ldcs(w4 + o1), xb = __ldcs(x4 + o1), tb = __ldcs(t4 + o1);
-        float4 ow, ox;
-        bwd_one(wa.x, xa.x, b.x, ta.x, inv, ow.x, ox.x, g.x, lsum);
-        bwd_one(wa.y, xa.y, b.y, ta.y, inv, ow.y, ox.y, g.y, lsum);
-        bwd_one(wa.z, xa.z, b.z, ta.z, inv, ow.z, ox.z, g.z, lsum);
-        bwd_one(wa.w, xa.w, b.w, ta.w, inv, ow.w, ox.w, g.w, lsum);
-        __stcs(dw4 + o0, ow);
-        __stcs(dx4 + o0, ox);
-        bwd_one(wb.x, xb.x, b.x, tb.x, inv, ow.x, ox.x, g.x, lsum);
-        bwd_one(wb.y, xb.y, b.y, tb.y, inv, ow.y, ox.y, g.y, lsum);
-        bwd_one(wb.z, xb.z, b.z, tb.z, inv, ow.z, ox.z, g.z, lsum);
-        bwd_one(wb.w, xb.w, b.w, tb.w, inv, ow.w, ox.w, g.w, lsum);
-        __stcs(dw4 + o1, ow);
-        __stcs(dx4 + o1, ox);
-      }
+      // one row per trip: 48 registers; two rows per trip (63 registers) measured slower, 0.464 ms against 0.419 ms on [32768,4096]
       for (; r < rows; r += step) {
         const uint64_t o0 = r * cols4;
         const float4 wa = __ldcs(w4 + o0), xa = __ldcs(x4 + o0), ta = __ldcs(t4 + o0);
@@ -203,7 +184,9 @@ struct MsePlan {
 static int mse_plan(vrhi_stream_t *st, const ArgView *args, int n_in_out, const vrhi_mse_params &q, const char *name, MsePlan *pl) {
   if (q.cols == 0 || q.rows == 0) return fail(VRHI_ERR_SIZE, "%s: empty problem", name);
   if (q.rows > (1ull << 40) || q.cols > (1ull << 31)) return fail(VRHI_ERR_SIZE, "%s: shape out of range", name);
-  const uint64_t full = q.rows * q.cols * 4;
+  uint64_t elements = 0;
+  VRHI_TRY(element_count(q.rows, q.cols, name, &elements));
+  const uint64_t full = elements * 4;
   const uint64_t want[8] = {full, full, q.cols * 4, full, 0, 0, 0, 0};
   for (int k = 0; k < 4; ++k)
     if (args[k].bytes < want[k]) return fail(VRHI_ERR_SIZE, "%s: argument %d holds %llu bytes, %llu needed", name, k, (unsigned long long)args[k].bytes, (unsigned long long)want[k]);
@@ -215,11 +198,8 @@ static int mse_plan(vrhi_stream_t *st, const ArgView *args, int n_in_out, const 
   const uint64_t gx = (q.cols + 1023) / 1024;
   // four 256-thread CTAs are resident per SM at this kernel's register count: one full wave,
   // and as few partial rows for the finalize kernels as that allows
-  uint64_t per_sm = 4;
-  if (const char *e = getenv("VRHI_MSE_BLOCKS_PER_SM")) {  // tuning aid
-    const int b = atoi(e);
-    if (b >= 1 && b <= 8) per_sm = (uint64_t)b;
-  }
+  static const int env_blocks = env_int("VRHI_MSE_BLOCKS_PER_SM", 1, 8, 4);  // tuning aid
+  const uint64_t per_sm = (uint64_t)env_blocks;
   uint64_t gy = ((uint64_t)sms * per_sm + gx - 1) / gx;
   if (gy > q.rows) gy = q.rows;
   if (gy > 4096) gy = 4096;
@@ -267,10 +247,7 @@ int launch_mse_tanh_bwd(vrhi_stream_t *st, const ArgView *args, int n_args, cons
   dim3 grid(pl.gx, pl.gy);
   const float *W = (const float *)args[0].ptr, *X = (const float *)args[1].ptr, *B = (const float *)args[2].ptr, *T = (const float *)args[3].ptr;
   const float inv = (float)(2.0 / pl.denom);
-  // One row per trip (48 registers) measured faster than two (63): 0.419 ms against 0.464 ms on [32768,4096].
-  const char *pair = getenv("VRHI_MSE_ROW_PAIRS");  // tuning aid: 1 selects two rows per trip
-  if (pl.vec && !(pair && atoi(pair) == 1)) mse_bwd_kernel<true, false><<<grid, 256, 0, st->s>>>(W, X, B, T, (float *)args[4].ptr, (float *)args[5].ptr, db_partial, loss_partial, pl.rows, pl.cols, inv);
-  else if (pl.vec) mse_bwd_kernel<true><<<grid, 256, 0, st->s>>>(W, X, B, T, (float *)args[4].ptr, (float *)args[5].ptr, db_partial, loss_partial, pl.rows, pl.cols, inv);
+  if (pl.vec) mse_bwd_kernel<true><<<grid, 256, 0, st->s>>>(W, X, B, T, (float *)args[4].ptr, (float *)args[5].ptr, db_partial, loss_partial, pl.rows, pl.cols, inv);
   else mse_bwd_kernel<false><<<grid, 256, 0, st->s>>>(W, X, B, T, (float *)args[4].ptr, (float *)args[5].ptr, db_partial, loss_partial, pl.rows, pl.cols, inv);
   VRHI_TRY(post_launch(st, "mse_tanh_bwd"));
   VRHI_TRY(col_finalize(st, db_partial, (float *)args[6].ptr, pl.gy, pl.cols, 1.0f));

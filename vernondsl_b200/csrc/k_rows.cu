@@ -286,7 +286,9 @@ static int rows_common(const ArgView *args, int n_args, int want_args, const voi
   if (n_args != want_args) return fail(VRHI_ERR_INVALID, "%s takes %d arguments, got %d", name, want_args, n_args);
   if (q->cols == 0 && q->rows != 0) return fail(VRHI_ERR_SIZE, "%s: rows of zero length", name);
   if (q->rows > (1ull << 40) || q->cols > (1ull << 32)) return fail(VRHI_ERR_SIZE, "%s: shape out of range", name);
-  if (args[0].bytes < q->rows * q->cols * 4) return fail(VRHI_ERR_SIZE, "%s: input holds %llu bytes, %llu needed", name, (unsigned long long)args[0].bytes, (unsigned long long)(q->rows * q->cols * 4));
+  uint64_t elements = 0;
+  VRHI_TRY(element_count(q->rows, q->cols, name, &elements));
+  if (args[0].bytes < elements * 4) return fail(VRHI_ERR_SIZE, "%s: input holds %llu bytes, %llu needed", name, (unsigned long long)args[0].bytes, (unsigned long long)(q->rows * q->cols * 4));
   for (int k = 1; k < n_args; ++k)
     if (!writable(args[k])) return fail(VRHI_ERR_INVALID, "%s: argument %d is read-only (class %s)", name, k, vrhi_arg_class_name(args[k].buf_cls));
   return VRHI_OK;

@@ -303,11 +303,15 @@ int compile(vrhi_device_t *dev, const std::string &src, CUfunction *out) {
 // Returns VRHI_OK when the compiled kernel was launched, 1 when this tape or shape is left to the
 // interpreter (no NVRTC, switched off, columns not a multiple of 4, unaligned pointers), and an
 // error code when compilation or the launch failed.
+// VRHI_TAPE_JIT=0 in the environment selects the interpreting kernel for every tape; read once per process
+static bool jit_enabled() {
+  static const bool on = env_int("VRHI_TAPE_JIT", 0, 1, 1) != 0;
+  return on;
+}
+
 int tape_jit_launch(vrhi_stream_t *st, const vrhi_tape_params &q, const float *const *in, float *const *out) {
   if (q.flags & VRHI_TAPE_FLAG_INTERPRET) return 1;
-  if (const char *e = getenv("VRHI_TAPE_JIT")) {
-    if (atoi(e) == 0) return 1;
-  }
+  if (!jit_enabled()) return 1;
   if (q.cols % 4 != 0) return 1;
   for (uint32_t k = 0; k < q.n_inputs; ++k)
     if (!((q.col_vector_mask >> k) & 1u) && !((q.scalar_mask >> k) & 1u) && ((uintptr_t)in[k] % 16)) return 1;
@@ -325,14 +329,9 @@ int tape_jit_launch(vrhi_stream_t *st, const vrhi_tape_params &q, const float *c
   for (uint32_t k = 0; k < q.n_inputs; ++k)
     if (!(((q.row_vector_mask | q.col_vector_mask | q.scalar_mask) >> k) & 1u)) ++full_inputs;
   int unroll = full_inputs >= 3 ? 1 : full_inputs == 2 ? 2 : 3, blocks_per_sm = 0;  // 0: what is resident at once, at most 6
-  if (const char *e = getenv("VRHI_TAPE_UNROLL")) {  // tuning aids
-    const int u = atoi(e);
-    if (u >= 1 && u <= 8) unroll = u;
-  }
-  if (const char *e = getenv("VRHI_TAPE_BLOCKS_PER_SM")) {
-    const int b = atoi(e);
-    if (b >= 1 && b <= 32) blocks_per_sm = b;
-  }
+  static const int env_unroll = env_int("VRHI_TAPE_UNROLL", 1, 8, 0), env_blocks = env_int("VRHI_TAPE_BLOCKS_PER_SM", 1, 32, 0);  // tuning aids
+  if (env_unroll) unroll = env_unroll;
+  if (env_blocks) blocks_per_sm = env_blocks;
   // cache key: everything the generated text depends on, as raw bytes (the text itself is only built on a miss)
   std::string key;
   {
@@ -409,9 +408,7 @@ int tape_jit_launch(vrhi_stream_t *st, const vrhi_tape_params &q, const float *c
 }
 
 bool tape_jit_available() {
-  if (const char *e = getenv("VRHI_TAPE_JIT")) {
-    if (atoi(e) == 0) return false;
-  }
+  if (!jit_enabled()) return false;
   std::lock_guard<std::mutex> lock(g_mu);
   load_once();
   return g_nvrtc.ok && g_driver.ok;

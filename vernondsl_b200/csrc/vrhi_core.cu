@@ -34,16 +34,22 @@ int stream_arena(vrhi_stream_t *st, size_t payload, uint32_t **ctrl, char **payl
     VRHI_CUDA(cudaStreamIsCapturing(st->s, &cap));
     if (cap != cudaStreamCaptureStatusNone)
       return fail(VRHI_ERR_INVALID, "this launch needs %zu bytes of stream scratch that do not exist yet; run the operator once on the stream before recording it", payload);
+    // at least twice the old size, so that a stream outgrows its arena a bounded number of times
     size_t want = payload < (size_t(4) << 20) ? (size_t(4) << 20) : payload;
-    if (st->arena) {
-      VRHI_CUDA(cudaStreamSynchronize(st->s));
-      VRHI_CUDA(cudaFree(st->arena));
-      st->arena = nullptr;
-      st->arena_payload = 0;
-    }
+    if (st->arena && want < 2 * st->arena_payload) want = 2 * st->arena_payload;
+    if (st->arena && st->n_retired >= (int)(sizeof st->retired / sizeof st->retired[0]))
+      return fail(VRHI_ERR_OOM, "the stream's scratch has been regrown too often");
     void *p = nullptr;
     VRHI_CUDA(cudaMalloc(&p, kCtrlBytes + want));
-    VRHI_CUDA(cudaMemsetAsync(p, 0, kCtrlBytes, st->s));
+    if (st->arena) {
+      // The control block moves with the stream: a status a kernel has recorded (or is about to, the copy
+      // is ordered behind it) is not lost.  The old arena is retired, not freed: recorded sequences still point into it.
+      VRHI_CUDA(cudaMemcpyAsync(p, st->arena, kCtrlBytes, cudaMemcpyDeviceToDevice, st->s));
+      VRHI_CUDA(cudaMemsetAsync(st->arena, 0, sizeof(uint32_t), st->s));  // the status word went along: report it once
+      st->retired[st->n_retired++] = st->arena;
+    } else {
+      VRHI_CUDA(cudaMemsetAsync(p, 0, kCtrlBytes, st->s));
+    }
     st->arena = static_cast<char *>(p);
     st->arena_payload = want;
   }
@@ -164,6 +170,7 @@ int vrhi_device_destroy(vrhi_device dev) {
     if (dev->default_stream->arena) {
       cudaSetDevice(dev->ordinal);
       cudaFree(dev->default_stream->arena);
+      for (int k = 0; k < dev->default_stream->n_retired; ++k) cudaFree(dev->default_stream->retired[k]);
     }
     delete dev->default_stream;
   }
@@ -440,6 +447,7 @@ int vrhi_stream_destroy(vrhi_stream stream) {
   if (stream->arena) {
     cudaStreamSynchronize(stream->s);
     cudaFree(stream->arena);
+    for (int k = 0; k < stream->n_retired; ++k) cudaFree(stream->retired[k]);
   }
   if (stream->fork_event) cudaEventDestroy(stream->fork_event);
   if (stream->owned) {
@@ -461,11 +469,15 @@ int vrhi_stream_check(vrhi_stream stream) {
   if (!stream) return fail(VRHI_ERR_INVALID, "NULL stream");
   VRHI_TRY(vrhi_stream_synchronize(stream));
   if (!stream->arena) return VRHI_OK;
-  int32_t status = 0;
-  VRHI_CUDA(cudaMemcpy(&status, stream->arena, sizeof status, cudaMemcpyDeviceToHost));
-  if (status != 0) {
-    VRHI_CUDA(cudaMemset(stream->arena, 0, sizeof status));
-    return fail(status, "a kernel on this stream recorded device status %d", status);
+  // the current arena, then the retired ones: kernels of a sequence recorded before the scratch grew report there
+  for (int k = -1; k < stream->n_retired; ++k) {
+    char *arena = k < 0 ? stream->arena : stream->retired[k];
+    int32_t status = 0;
+    VRHI_CUDA(cudaMemcpy(&status, arena, sizeof status, cudaMemcpyDeviceToHost));
+    if (status != 0) {
+      VRHI_CUDA(cudaMemset(arena, 0, sizeof status));
+      return fail(status, "a kernel on this stream recorded device status %d", status);
+    }
   }
   return VRHI_OK;
 }

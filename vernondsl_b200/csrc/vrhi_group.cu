@@ -55,6 +55,10 @@ struct vrhi_exchange_t {
   uint32_t width, height, chunk_rows, n_slabs;
   vrhi_buffer_t *wire[2];               // own wire images (uint16 [height][width]); two alternate from step to step
   uint16_t *peer_wire[2][kMaxWorld];    // the world-1 peers', starting with rank+1
+  // squeezed transfer (see k_gather.cu): counts cross as bytes, granules with large counts in full
+  bool squeeze;
+  uint8_t *bytes[2];                    // own byte planes [height][width], alternating like the wire images
+  uint8_t *peer_bytes[2][kMaxWorld];
   uint32_t *flags;                      // own flag array [world]
   uint32_t *peer_flags[kMaxWorld];
   vrhi_stream_t *push[kMaxWorld], *arrive;  // internal streams: one per peer for the transfers to it; waits and widening
@@ -121,6 +125,16 @@ int share(vrhi_group_t *g, void *local, void **by_rank, std::vector<void *> *ope
 bool use_copy_engines() {
   static const bool v = [] { const char *e = getenv("VRHI_PUSH_COPY_ENGINE"); return !e || atoi(e) != 0; }();
   return v;
+}
+
+// Whether the counts cross NVLink squeezed to bytes.  It pays where the step is bound by the transfer,
+// not by the arithmetic: from five ranks on by default (at eight ranks each GPU takes in 7/8 of the
+// image every step); VRHI_EXCHANGE_SQUEEZE=0/1 overrides.  The squeezing push is a kernel, so it
+// replaces the copy engines where it is on.
+bool use_squeeze(uint32_t world, uint32_t width) {
+  static const int v = env_int("VRHI_EXCHANGE_SQUEEZE", 0, 1, -1);
+  if (width % 16) return false;
+  return v < 0 ? world >= 5 : v == 1;
 }
 
 // Ranks meet here: one round of the caller's all-gather.
@@ -275,7 +289,17 @@ int vrhi_exchange_create(vrhi_group g, vrhi_buffer image, uint32_t width, uint32
     ex->flags = static_cast<uint32_t *>(p);
     if (cudaMemset(p, 0, 2u << 20) != cudaSuccess) return cleanup(fail(VRHI_ERR_CUDA, "cudaMemset failed"));
   }
+  ex->squeeze = g->world > 1 && use_squeeze(g->world, width);
   void *by_rank[kMaxWorld];
+  for (int b = 0; b < 2 && ex->squeeze; ++b) {
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, px);
+    if (e != cudaSuccess) { (void)cudaGetLastError(); return cleanup(fail(VRHI_ERR_OOM, "cudaMalloc of the exchange's byte plane failed: %s", cudaGetErrorString(e))); }
+    ex->bytes[b] = static_cast<uint8_t *>(p);
+    int rc = share(g, p, by_rank, ex->opened);
+    if (rc != VRHI_OK) return cleanup(rc);
+    for (uint32_t k = 0; k + 1 < g->world; ++k) ex->peer_bytes[b][k] = static_cast<uint8_t *>(by_rank[(g->rank + 1 + k) % g->world]);
+  }
   for (int b = 0; b < 2; ++b) {
     int rc = share(g, ex->wire[b]->ptr, by_rank, ex->opened);
     if (rc != VRHI_OK) return cleanup(rc);
@@ -290,7 +314,7 @@ int vrhi_exchange_create(vrhi_group g, vrhi_buffer image, uint32_t width, uint32
   // copy engines: a stream per peer, so that the transfers to different peers run on different engines at once;
   // the storing kernel serves all peers from one launch and needs one stream
   static const bool one_stream = [] { const char *e = getenv("VRHI_PUSH_STREAMS"); return e && atoi(e) == 1; }();  // comparison aid
-  ex->n_push = use_copy_engines() && g->world > 2 && !one_stream ? g->world - 1 : 1;
+  ex->n_push = use_copy_engines() && !ex->squeeze && g->world > 2 && !one_stream ? g->world - 1 : 1;
   int rc = VRHI_OK;
   for (uint32_t k = 0; k < ex->n_push && rc == VRHI_OK; ++k) rc = make_stream(g->dev, &ex->push[k]);
   if (rc == VRHI_OK) rc = make_stream(g->dev, &ex->arrive);
@@ -328,6 +352,8 @@ int vrhi_exchange_destroy(vrhi_exchange ex) {
   // a rank's wire images must outlive every other rank's mapping of them
   int rc = ex->ready ? meet(ex->grp) : VRHI_OK;
   for (int b = 0; b < 2; ++b) vrhi_buffer_destroy(ex->wire[b]);
+  for (int b = 0; b < 2; ++b)
+    if (ex->bytes[b]) cudaFree(ex->bytes[b]);
   if (ex->flags) cudaFree(ex->flags);
   delete ex;
   return rc;
@@ -355,7 +381,10 @@ int vrhi_exchange_publish(vrhi_exchange ex, vrhi_stream compute, uint32_t slab_f
   // sending side, behind the launches that computed these slabs
   VRHI_CUDA(cudaEventRecord(ex->ev_compute, compute->s));
   for (uint32_t k = 0; k < ex->n_push; ++k) VRHI_CUDA(cudaStreamWaitEvent(ex->push[k]->s, ex->ev_compute, 0));
-  if (use_copy_engines()) {
+  if (ex->squeeze) {
+    VRHI_TRY(gather_push_squeezed(ex->push[0], ex->peer_bytes[ex->cur], ex->peer_wire[ex->cur], g->world - 1, static_cast<const uint16_t *>(ex->wire[ex->cur]->ptr), q));
+    VRHI_TRY(gather_signal(ex->push[0], ex->peer_flags, g->world - 1, g->rank, seq));
+  } else if (use_copy_engines()) {
     // one strided device-to-device copy per peer, then that peer's flag, each peer on its own stream where there are several
     const uint64_t chunk_bytes = (uint64_t)ex->chunk_rows * ex->width * 2;
     const uint64_t offset = ((uint64_t)slab_first * g->world + g->rank) * chunk_bytes, pitch = (uint64_t)g->world * stride * chunk_bytes;
@@ -379,7 +408,8 @@ int vrhi_exchange_publish(vrhi_exchange ex, vrhi_stream compute, uint32_t slab_f
   vrhi_widen_params w{};
   w.size = sizeof w; w.width = ex->width; w.height = ex->height; w.chunk_rows = ex->chunk_rows; w.world = g->world; w.skip_rank = g->rank;
   w.slab_first = slab_first; w.slab_count = slab_count; w.slab_stride = stride;
-  VRHI_TRY(widen_rows_u16(ex->arrive, static_cast<const uint16_t *>(ex->wire[ex->cur]->ptr), static_cast<uint32_t *>(ex->image->ptr), w, ok));
+  if (ex->squeeze) VRHI_TRY(widen_rows_squeezed(ex->arrive, ex->bytes[ex->cur], static_cast<const uint16_t *>(ex->wire[ex->cur]->ptr), static_cast<uint32_t *>(ex->image->ptr), w, ok));
+  else VRHI_TRY(widen_rows_u16(ex->arrive, static_cast<const uint16_t *>(ex->wire[ex->cur]->ptr), static_cast<uint32_t *>(ex->image->ptr), w, ok));
   return VRHI_OK;
 }
 

@@ -6,6 +6,7 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <string>
 
 struct vrhi_stream_t;
@@ -44,6 +45,11 @@ struct vrhi_stream_t {
   vrhi_stream_t *record_sides[4];
   int n_record_sides;
   cudaEvent_t fork_event;      // created on first use, reused
+  // Arenas this stream has outgrown.  They stay allocated until the stream is destroyed: a recorded
+  // sequence keeps raw pointers into the arena of its time (work counters, partial sums, the wait
+  // verdict), and must find them intact however much the stream's scratch has grown since.
+  char *retired[24];
+  int n_retired;
 };
 
 struct vrhi_sequence_t {
@@ -124,6 +130,9 @@ int launch_gather_pull_u16(vrhi_stream_t *, const ArgView *, int, const void *, 
 // Pieces of the image gather and of the small all-reduce (k_gather.cu), used by vrhi_group.cu.
 int widen_rows_u16(vrhi_stream_t *st, const uint16_t *wire, uint32_t *image, const vrhi_widen_params &q, const uint32_t *ok);
 int gather_push_u16(vrhi_stream_t *st, uint16_t *const *peer_wires, uint32_t n_peers, const uint16_t *wire, const vrhi_gather_params &q);
+int gather_push_squeezed(vrhi_stream_t *st, uint8_t *const *peer_bytes, uint16_t *const *peer_wide, uint32_t n_peers, const uint16_t *wire,
+                         const vrhi_gather_params &q);
+int widen_rows_squeezed(vrhi_stream_t *st, const uint8_t *bytes, const uint16_t *wide, uint32_t *image, const vrhi_widen_params &q, const uint32_t *ok);
 int gather_signal(vrhi_stream_t *st, uint32_t *const *peer_flags, uint32_t n, uint32_t slot, uint32_t seq);
 int gather_wait(vrhi_stream_t *st, const uint32_t *flags, uint32_t world, uint32_t rank, uint32_t seq, uint32_t wait_ms, const uint32_t **ok);
 int box_scatter(vrhi_stream_t *st, float *const *boxes, uint32_t world, uint32_t rank, const float *src, uint32_t n, uint32_t capacity);
@@ -157,6 +166,26 @@ int read_params(const void *params, size_t params_size, P *out) {
   if (declared > params_size) return fail(VRHI_ERR_SIZE, "parameter block declares %u bytes but %zu were passed", declared, params_size);
   size_t n = declared < sizeof(P) ? declared : sizeof(P);
   memcpy(out, params, n);
+  return VRHI_OK;
+}
+
+// An integer from the environment, or `fallback` when the variable is unset or outside [lo, hi].  The
+// tuning and behaviour switches of this library are read ONCE per process, by callers of the form
+//   static const int v = env_int("NAME", lo, hi, fallback);
+// so that nothing on a launch path calls getenv.
+inline int env_int(const char *name, int lo, int hi, int fallback) {
+  const char *e = getenv(name);
+  if (!e || !*e) return fallback;
+  const int v = atoi(e);
+  return v >= lo && v <= hi ? v : fallback;
+}
+
+// rows * cols as an element count, refused (VRHI_ERR_SIZE) beyond 2^40 elements: checked before any
+// byte count is formed, so that a product that wraps in 64 bits can never pass a size check.
+inline int element_count(uint64_t rows, uint64_t cols, const char *name, uint64_t *out) {
+  constexpr uint64_t kMax = 1ull << 40;
+  if (rows != 0 && cols > kMax / rows) return fail(VRHI_ERR_SIZE, "%s: %llu x %llu elements are out of range (at most 2^40)", name, (unsigned long long)rows, (unsigned long long)cols);
+  *out = rows * cols;
   return VRHI_OK;
 }
 

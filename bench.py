@@ -562,7 +562,16 @@ def run_only(args):
     rn = lambda *shape: torch.randn(shape, generator=gen, device=device, dtype=torch.float32)
     name, it = args.only, args.iters
     res = {"only": name, "scale": args.scale}
-    if name in ("escape_julia", "escape_mandelbrot"):
+    if name == "fp32_probe":
+        # what the FP32 pipe and the issue port do with scalar and with packed fma, alone and with integer work beside
+        out = dev.empty(4, np.float32)
+        per_thread, threads = 64 * 4000, dev.sm_count * 2048
+        for variant, label in enumerate(("scalar fma", "packed fma.f32x2", "packed fma + 1 integer add each", "scalar fma + 1 integer add each")):
+            ms = min(time_launches(dev, st, lambda: ops.fp32_probe(st, out, per_thread, threads, variant), 3, warmup=1) for _ in range(3))
+            lane_fma = per_thread * threads * (2 if variant in (1, 2) else 1)
+            res[label] = {"ms": ms, "T_lane_fma_per_s": lane_fma / (ms * 1e-3) / 1e12,
+                          "instructions_per_clk_per_subpartition": per_thread * threads * (2 if variant >= 2 else 1) / 32 / (ms * 1e-3 * dev.sm_clock_khz * 1e3) / (dev.sm_count * 4)}
+    elif name in ("escape_julia", "escape_mandelbrot"):
         side = max(256, int(16384 * args.scale) // 128 * 128)
         if name == "escape_julia":
             W = H = side
@@ -575,6 +584,16 @@ def run_only(args):
         img = dev.empty((H, W), np.uint32, L.IMAGE)
         res["ms"] = time_launches(dev, st, lambda: ops.escape_time(st, img, p), it, warmup=1)
         res["shape"] = [H, W]
+    elif name == "widen":
+        # the receiving side of the image gather alone: uint16 rows of the peers -> the uint32 image, for a world of --world ranks
+        W = H = max(2048, int(16384 * args.scale) // 2048 * 2048)
+        world = max(2, args.world)
+        wire, img = dev.empty((H, W), np.uint16, L.IMAGE), dev.empty((H, W), np.uint32, L.IMAGE)
+        wire.fill(1)
+        n_slabs = H // 128 // world
+        res["ms"] = time_launches(dev, st, lambda: ops.widen_rows_u16(st, wire, img, W, H, 128, world, 0, 0, n_slabs), it, warmup=2)
+        moved = (world - 1) * n_slabs * 128 * W * 6
+        res["world"], res["gbs"] = world, moved / res["ms"] / 1e6
     elif name in ("escape_split", "escape_beside"):
         from vernondsl_b200 import partition
 
@@ -932,6 +951,8 @@ def main():
     launches0 = count_launches()
     total_ms = timed(step, args.steps)
     launches = count_launches() - launches0
+    if native:
+        exchange.check()   # raises if a device-side wait gave up (a peer never arrived); with VRHI_EXCHANGE_TRACE=1 prints the last step's timeline
     if world > 1 and os.environ.get("VRHI_BENCH_TRACE"):
         barrier()
         TRACING[0] = True

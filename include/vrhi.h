@@ -386,12 +386,14 @@ typedef struct vrhi_mse_params {
  *   flat_color (color.mlir:43-59): args [0] color UNIFORM f32[3], [1] fragments IMAGE f32[n][4],
  *     every fragment = (c0,c1,c2,1). */
 
-/* op "fp32_probe": dependent-free FFMA chains, for measuring the FP32 issue peak the
- * escape-time kernel is bounded by.  args [0] OUTPUT (>= 4 bytes).  Executes
- * `ffma_per_thread` FFMAs in each of `threads` threads. */
+/* op "fp32_probe": dependent-free fma chains, for measuring the FP32 issue peak the escape-time
+ * kernel is bounded by.  args [0] OUTPUT (>= 4 bytes).  Executes `ffma_per_thread` fma instructions
+ * in each of `threads` threads.  variant 0: scalar fma.rn.f32 (the roofline's denominator);
+ * 1: packed fma.rn.f32x2, two lane-FMAs per instruction; 2: packed with one integer add per fma;
+ * 3: scalar with one integer add per fma. */
 typedef struct vrhi_probe_params {
   uint32_t size;
-  uint32_t reserved;
+  uint32_t variant;
   uint64_t ffma_per_thread;
   uint64_t threads; /* 0 = fill the device */
 } vrhi_probe_params;

@@ -113,7 +113,7 @@ class MseParams(C.Structure):
 
 
 class ProbeParams(C.Structure):
-    _fields_ = [("size", C.c_uint32), ("reserved", C.c_uint32), ("ffma_per_thread", C.c_uint64),
+    _fields_ = [("size", C.c_uint32), ("variant", C.c_uint32), ("ffma_per_thread", C.c_uint64),
                 ("threads", C.c_uint64)]
 
 

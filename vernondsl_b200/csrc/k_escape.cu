@@ -208,31 +208,62 @@ int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const
 
 // ---------------------------------------------------------------------------------------------
 // FP32 issue-rate probe: independent FFMA chains, 8 per thread, nothing else in the loop body.
-__global__ void __launch_bounds__(256) fp32_probe_kernel(float *out, uint64_t iters, float seed) {
-  float v0 = seed + threadIdx.x, v1 = v0 + 1.f, v2 = v0 + 2.f, v3 = v0 + 3.f;
-  float v4 = v0 + 4.f, v5 = v0 + 5.f, v6 = v0 + 6.f, v7 = v0 + 7.f;
+// Variants (vrhi_probe_params.variant) measure what the two-pixels-per-lane kernel relies on:
+//   0  scalar fma.rn.f32                       the denominator of the escape-time roofline
+//   1  packed fma.rn.f32x2                     the same lane-FMA rate from half the instructions
+//   2  packed, one integer add per packed fma  the integer adds issue in the gaps: same time as 1
+//   3  scalar, one integer add per fma         every integer add costs an issue slot: slower than 0
+template <int VARIANT>
+__global__ void __launch_bounds__(256) fp32_probe_kernel(float *out, uint64_t iters, float seed, uint32_t step) {
+  constexpr bool PACKED = VARIANT == 1 || VARIANT == 2, WITH_INT = VARIANT >= 2;
+  float v[8], w[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { v[i] = seed + threadIdx.x + i; w[i] = v[i] * 0.5f; }
+  uint32_t x[4] = {threadIdx.x, threadIdx.x + 1u, threadIdx.x + 2u, threadIdx.x + 3u};
   const float m = 0.999f, c = 0.001f;
   for (uint64_t k = 0; k < iters; ++k) {
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
-      v0 = fmaf(v0, m, c); v1 = fmaf(v1, m, c); v2 = fmaf(v2, m, c); v3 = fmaf(v3, m, c);
-      v4 = fmaf(v4, m, c); v5 = fmaf(v5, m, c); v6 = fmaf(v6, m, c); v7 = fmaf(v7, m, c);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (PACKED) {
+          // one instruction for the pair (v[i], w[i])
+          unsigned long long p, pm, pc;
+          asm("mov.b64 %0, {%1, %2};" : "=l"(p) : "f"(v[i]), "f"(w[i]));
+          asm("mov.b64 %0, {%1, %1};" : "=l"(pm) : "f"(m));
+          asm("mov.b64 %0, {%1, %1};" : "=l"(pc) : "f"(c));
+          asm volatile("fma.rn.f32x2 %0, %0, %1, %2;" : "+l"(p) : "l"(pm), "l"(pc));
+          asm("mov.b64 {%0, %1}, %2;" : "=f"(v[i]), "=f"(w[i]) : "l"(p));
+        } else {
+          v[i] = fmaf(v[i], m, c);
+        }
+        if (WITH_INT) asm volatile("add.u32 %0, %0, %1;" : "+r"(x[i & 3]) : "r"(step));
+      }
     }
   }
-  float r = ((v0 + v1) + (v2 + v3)) + ((v4 + v5) + (v6 + v7));
-  if (r == 12345.678f) out[0] = r;  // keeps the chains alive without memory traffic
+  float r = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) r += v[i] + (PACKED ? w[i] : 0.f);
+  if (r == 12345.678f || (x[0] ^ x[1] ^ x[2] ^ x[3]) == 0x12345u) out[0] = r;  // keeps the chains alive without memory traffic
 }
 
 int launch_fp32_probe(vrhi_stream_t *st, const ArgView *args, int n_args, const void *params, size_t params_size) {
   vrhi_probe_params q;
   VRHI_TRY(read_params(params, params_size, &q));
   if (n_args != 1 || args[0].bytes < 4 || !writable(args[0])) return fail(VRHI_ERR_INVALID, "fp32_probe takes one writable argument of at least 4 bytes");
+  if (q.variant > 3) return fail(VRHI_ERR_INVALID, "fp32_probe: variant %u out of range", q.variant);
   const int sms = st->dev->prop.multiProcessorCount;
   uint64_t threads = q.threads ? q.threads : (uint64_t)sms * 2048;
   uint64_t blocks = (threads + 255) / 256;
   if (blocks == 0 || blocks > 0x7fffffffull) return fail(VRHI_ERR_SIZE, "fp32_probe: thread count out of range");
-  uint64_t iters = q.ffma_per_thread / 64;  // 64 FFMAs per loop trip
-  fp32_probe_kernel<<<(unsigned)blocks, 256, 0, st->s>>>(reinterpret_cast<float *>(args[0].ptr), iters, 1.0f);
+  uint64_t iters = q.ffma_per_thread / 64;  // 64 fma instructions per loop trip (128 lane-FMAs when packed)
+  float *o = reinterpret_cast<float *>(args[0].ptr);
+  switch (q.variant) {
+    case 0: fp32_probe_kernel<0><<<(unsigned)blocks, 256, 0, st->s>>>(o, iters, 1.0f, 7u); break;
+    case 1: fp32_probe_kernel<1><<<(unsigned)blocks, 256, 0, st->s>>>(o, iters, 1.0f, 7u); break;
+    case 2: fp32_probe_kernel<2><<<(unsigned)blocks, 256, 0, st->s>>>(o, iters, 1.0f, 7u); break;
+    default: fp32_probe_kernel<3><<<(unsigned)blocks, 256, 0, st->s>>>(o, iters, 1.0f, 7u); break;
+  }
   return post_launch(st, "fp32_probe");
 }
 

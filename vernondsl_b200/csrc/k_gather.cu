@@ -6,9 +6,12 @@
 
 namespace vrhi {
 
-// One block row of 256 threads widens 2048 pixels of one image row: a 16-byte load of eight
-// counts, two 16-byte stores.  Rows are enumerated slab by slab over the chunks the skipped rank
-// does not own.  HBM-bound: 2 B read + 4 B written per pixel.
+// A block widens whole image rows, one after the other (grid-stride over the rows to do): every
+// thread keeps four 16-byte loads of eight counts in flight and writes two 16-byte stores for each.
+// Rows are enumerated slab by slab over the chunks the skipped rank does not own.  HBM-bound: 2 B
+// read + 4 B written per pixel.  (A first form with one short-lived block per 2048 pixels reached
+// 2.1 TB/s; at four and eight ranks the widening of 3/4 and 7/8 of the image was then the longest
+// part of a step.)
 template <bool VEC>
 __global__ void __launch_bounds__(256) widen_rows_u16_kernel(const uint16_t *__restrict__ wire, uint32_t *__restrict__ image,
                                                              uint32_t width, uint32_t height, uint32_t chunk_rows, uint32_t world,
@@ -18,7 +21,7 @@ __global__ void __launch_bounds__(256) widen_rows_u16_kernel(const uint16_t *__r
   if (ok && *reinterpret_cast<const volatile uint32_t *>(ok) == 0u) return;
   const uint32_t nq = skip_rank < world ? world - 1 : world;
   const uint32_t rows_per_slab = nq * chunk_rows;
-  for (uint32_t u = blockIdx.y; u < total_rows; u += gridDim.y) {
+  for (uint32_t u = blockIdx.x; u < total_rows; u += gridDim.x) {
     const uint32_t slab = u / rows_per_slab, rem = u - slab * rows_per_slab;
     const uint32_t qq = rem / chunk_rows, rr = rem - qq * chunk_rows;
     const uint32_t q = qq + (qq >= skip_rank ? 1u : 0u);
@@ -26,18 +29,25 @@ __global__ void __launch_bounds__(256) widen_rows_u16_kernel(const uint16_t *__r
     if (row >= height) continue;
     const size_t base = (size_t)row * width;
     if (VEC) {
-      const uint32_t v = blockIdx.x * 256u + threadIdx.x;
-      if (v * 8u < width) {
-        const uint4 in = __ldcs(reinterpret_cast<const uint4 *>(wire + base) + v);
-        uint4 lo, hi;
-        lo.x = in.x & 0xffffu; lo.y = in.x >> 16; lo.z = in.y & 0xffffu; lo.w = in.y >> 16;
-        hi.x = in.z & 0xffffu; hi.y = in.z >> 16; hi.z = in.w & 0xffffu; hi.w = in.w >> 16;
-        uint4 *out = reinterpret_cast<uint4 *>(image + base) + 2 * (size_t)v;
-        __stcs(out, lo);
-        __stcs(out + 1, hi);
+      const uint32_t segs = width / 8u;
+      const uint4 *src = reinterpret_cast<const uint4 *>(wire + base);
+      uint4 *dst = reinterpret_cast<uint4 *>(image + base);
+      for (uint32_t v0 = threadIdx.x; v0 < segs; v0 += 1024u) {
+        uint4 in[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (v0 + j * 256u < segs) in[j] = __ldcs(src + v0 + j * 256u);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t v = v0 + j * 256u;
+          if (v < segs) {
+            __stcs(dst + 2 * (size_t)v, make_uint4(in[j].x & 0xffffu, in[j].x >> 16, in[j].y & 0xffffu, in[j].y >> 16));
+            __stcs(dst + 2 * (size_t)v + 1, make_uint4(in[j].z & 0xffffu, in[j].z >> 16, in[j].w & 0xffffu, in[j].w >> 16));
+          }
+        }
       }
     } else {
-      for (uint32_t i = blockIdx.x * 256u + threadIdx.x; i < width; i += gridDim.x * 256u) image[base + i] = wire[base + i];
+      for (uint32_t i = threadIdx.x; i < width; i += 256u) image[base + i] = wire[base + i];
     }
   }
 }
@@ -56,15 +66,12 @@ int widen_rows_u16(vrhi_stream_t *st, const uint16_t *wire, uint32_t *image, con
   if (total_rows == 0) return VRHI_OK;  // nothing to widen (one rank, or an empty slab range)
   if (total_rows > 0xffffffffull) return fail(VRHI_ERR_UNSUPPORTED, "widen_rows_u16: too many rows");
   const bool vec = q.width % 8 == 0 && ((uintptr_t)wire % 16 == 0) && ((uintptr_t)image % 16 == 0);
-  dim3 grid;
-  grid.y = (unsigned)(total_rows < 32768 ? total_rows : 32768);
-  if (vec) {
-    grid.x = (q.width / 8 + 255) / 256;
+  const uint64_t cap = (uint64_t)st->dev->prop.multiProcessorCount * 8;  // resident at once: a persistent grid over the rows
+  const unsigned grid = (unsigned)(total_rows < cap ? total_rows : cap);
+  if (vec)
     widen_rows_u16_kernel<true><<<grid, 256, 0, st->s>>>(wire, image, q.width, q.height, q.chunk_rows, q.world, q.skip_rank, q.slab_first, stride, (uint32_t)total_rows, ok);
-  } else {
-    grid.x = (q.width + 255) / 256 < 64 ? (q.width + 255) / 256 : 64;
+  else
     widen_rows_u16_kernel<false><<<grid, 256, 0, st->s>>>(wire, image, q.width, q.height, q.chunk_rows, q.world, q.skip_rank, q.slab_first, stride, (uint32_t)total_rows, ok);
-  }
   return post_launch(st, "widen_rows_u16");
 }
 
@@ -370,7 +377,7 @@ __global__ void __launch_bounds__(128) gather_push_squeezed_kernel(PeerPlanes pe
 }
 
 // The receiving side of the squeezed push: byte plane -> uint32 image, granules with a byte of 255 from
-// the uint16 wire image.  Rows are enumerated as in widen_rows_u16_kernel.
+// the uint16 wire image.  Rows and blocks as in widen_rows_u16_kernel; a granule is 16 pixels.
 __global__ void __launch_bounds__(256) widen_rows_squeezed_kernel(const uint8_t *__restrict__ bytes, const uint16_t *__restrict__ wide,
                                                                   uint32_t *__restrict__ image, uint32_t width, uint32_t height,
                                                                   uint32_t chunk_rows, uint32_t world, uint32_t skip_rank, uint32_t slab_first,
@@ -378,29 +385,40 @@ __global__ void __launch_bounds__(256) widen_rows_squeezed_kernel(const uint8_t 
   if (ok && *reinterpret_cast<const volatile uint32_t *>(ok) == 0u) return;
   const uint32_t nq = skip_rank < world ? world - 1 : world;
   const uint32_t rows_per_slab = nq * chunk_rows;
-  const uint32_t v = blockIdx.x * 256u + threadIdx.x;
-  if (v * 16u >= width) return;
-  for (uint32_t u = blockIdx.y; u < total_rows; u += gridDim.y) {
+  const uint32_t segs = width / 16u;
+  for (uint32_t u = blockIdx.x; u < total_rows; u += gridDim.x) {
     const uint32_t slab = u / rows_per_slab, rem = u - slab * rows_per_slab;
     const uint32_t qq = rem / chunk_rows, rr = rem - qq * chunk_rows;
     const uint32_t q = qq + (qq >= skip_rank ? 1u : 0u);
     const uint64_t row = ((uint64_t)(slab_first + slab * slab_stride) * world + q) * chunk_rows + rr;
     if (row >= height) continue;
-    const size_t at = (size_t)row * width / 16 + v;
-    const uint4 sq = __ldcs(reinterpret_cast<const uint4 *>(bytes) + at);
-    uint4 *out = reinterpret_cast<uint4 *>(image) + 4 * at;
-    if (has_ff(sq.x) || has_ff(sq.y) || has_ff(sq.z) || has_ff(sq.w)) {
-      const uint4 *src = reinterpret_cast<const uint4 *>(wide) + 2 * at;
-      const uint4 a = __ldcs(src), b = __ldcs(src + 1);
-      __stcs(out, make_uint4(a.x & 0xffffu, a.x >> 16, a.y & 0xffffu, a.y >> 16));
-      __stcs(out + 1, make_uint4(a.z & 0xffffu, a.z >> 16, a.w & 0xffffu, a.w >> 16));
-      __stcs(out + 2, make_uint4(b.x & 0xffffu, b.x >> 16, b.y & 0xffffu, b.y >> 16));
-      __stcs(out + 3, make_uint4(b.z & 0xffffu, b.z >> 16, b.w & 0xffffu, b.w >> 16));
-    } else {
-      __stcs(out, make_uint4(sq.x & 0xffu, (sq.x >> 8) & 0xffu, (sq.x >> 16) & 0xffu, sq.x >> 24));
-      __stcs(out + 1, make_uint4(sq.y & 0xffu, (sq.y >> 8) & 0xffu, (sq.y >> 16) & 0xffu, sq.y >> 24));
-      __stcs(out + 2, make_uint4(sq.z & 0xffu, (sq.z >> 8) & 0xffu, (sq.z >> 16) & 0xffu, sq.z >> 24));
-      __stcs(out + 3, make_uint4(sq.w & 0xffu, (sq.w >> 8) & 0xffu, (sq.w >> 16) & 0xffu, sq.w >> 24));
+    const size_t g0 = (size_t)row * segs;
+    for (uint32_t v0 = threadIdx.x; v0 < segs; v0 += 1024u) {
+      uint4 in[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (v0 + j * 256u < segs) in[j] = __ldcs(reinterpret_cast<const uint4 *>(bytes) + g0 + v0 + j * 256u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t v = v0 + j * 256u;
+        if (v >= segs) continue;
+        const size_t at = g0 + v;
+        const uint4 sq = in[j];
+        uint4 *out = reinterpret_cast<uint4 *>(image) + 4 * at;
+        if (has_ff(sq.x) || has_ff(sq.y) || has_ff(sq.z) || has_ff(sq.w)) {
+          const uint4 *src = reinterpret_cast<const uint4 *>(wide) + 2 * at;
+          const uint4 a = __ldcs(src), b = __ldcs(src + 1);
+          __stcs(out, make_uint4(a.x & 0xffffu, a.x >> 16, a.y & 0xffffu, a.y >> 16));
+          __stcs(out + 1, make_uint4(a.z & 0xffffu, a.z >> 16, a.w & 0xffffu, a.w >> 16));
+          __stcs(out + 2, make_uint4(b.x & 0xffffu, b.x >> 16, b.y & 0xffffu, b.y >> 16));
+          __stcs(out + 3, make_uint4(b.z & 0xffffu, b.z >> 16, b.w & 0xffffu, b.w >> 16));
+        } else {
+          __stcs(out, make_uint4(sq.x & 0xffu, (sq.x >> 8) & 0xffu, (sq.x >> 16) & 0xffu, sq.x >> 24));
+          __stcs(out + 1, make_uint4(sq.y & 0xffu, (sq.y >> 8) & 0xffu, (sq.y >> 16) & 0xffu, sq.y >> 24));
+          __stcs(out + 2, make_uint4(sq.z & 0xffu, (sq.z >> 8) & 0xffu, (sq.z >> 16) & 0xffu, sq.z >> 24));
+          __stcs(out + 3, make_uint4(sq.w & 0xffu, (sq.w >> 8) & 0xffu, (sq.w >> 16) & 0xffu, sq.w >> 24));
+        }
+      }
     }
   }
 }
@@ -432,9 +450,8 @@ int widen_rows_squeezed(vrhi_stream_t *st, const uint8_t *bytes, const uint16_t 
   const uint64_t total_rows = (uint64_t)q.slab_count * nq * q.chunk_rows;
   if (total_rows == 0) return VRHI_OK;
   if (total_rows > 0xffffffffull) return fail(VRHI_ERR_UNSUPPORTED, "widen: too many rows");
-  dim3 grid;
-  grid.x = (q.width / 16 + 255) / 256;
-  grid.y = (unsigned)(total_rows < 32768 ? total_rows : 32768);
+  const uint64_t cap = (uint64_t)st->dev->prop.multiProcessorCount * 8;
+  const unsigned grid = (unsigned)(total_rows < cap ? total_rows : cap);
   widen_rows_squeezed_kernel<<<grid, 256, 0, st->s>>>(bytes, wide, image, q.width, q.height, q.chunk_rows, q.world, q.skip_rank, q.slab_first, stride, (uint32_t)total_rows, ok);
   return post_launch(st, "widen_rows_squeezed");
 }

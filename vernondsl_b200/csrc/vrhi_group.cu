@@ -68,6 +68,11 @@ struct vrhi_exchange_t {
   uint64_t steps;
   std::vector<void *> *opened;          // IPC mappings of the peers' wire images and flags
   bool ready;
+  // VRHI_EXCHANGE_TRACE=1: timed events behind each group's transfer and widening, printed by vrhi_exchange_check
+  bool trace;
+  uint32_t n_marks;                     // publishes of the current step
+  cudaEvent_t t_computed[16], t_pushed[16], t_widened[16], t_done;
+  uint32_t last_marks;
 };
 
 namespace {
@@ -290,6 +295,11 @@ int vrhi_exchange_create(vrhi_group g, vrhi_buffer image, uint32_t width, uint32
     if (cudaMemset(p, 0, 2u << 20) != cudaSuccess) return cleanup(fail(VRHI_ERR_CUDA, "cudaMemset failed"));
   }
   ex->squeeze = g->world > 1 && use_squeeze(g->world, width);
+  ex->trace = g->world > 1 && env_int("VRHI_EXCHANGE_TRACE", 0, 1, 0) == 1;
+  if (ex->trace) {
+    cudaEventCreate(&ex->t_done);
+    for (int k = 0; k < 16; ++k) { cudaEventCreate(&ex->t_computed[k]); cudaEventCreate(&ex->t_pushed[k]); cudaEventCreate(&ex->t_widened[k]); }
+  }
   void *by_rank[kMaxWorld];
   for (int b = 0; b < 2 && ex->squeeze; ++b) {
     void *p = nullptr;
@@ -346,6 +356,10 @@ int vrhi_exchange_destroy(vrhi_exchange ex) {
   for (uint32_t k = 0; k < kMaxWorld; ++k)
     if (ex->ev_push[k]) cudaEventDestroy(ex->ev_push[k]);
   if (ex->ev_arrive) cudaEventDestroy(ex->ev_arrive);
+  if (ex->trace) {
+    cudaEventDestroy(ex->t_done);
+    for (int k = 0; k < 16; ++k) { cudaEventDestroy(ex->t_computed[k]); cudaEventDestroy(ex->t_pushed[k]); cudaEventDestroy(ex->t_widened[k]); }
+  }
   if (ex->opened)
     for (void *p : *ex->opened) cudaIpcCloseMemHandle(p);
   delete ex->opened;
@@ -378,6 +392,8 @@ int vrhi_exchange_publish(vrhi_exchange ex, vrhi_stream compute, uint32_t slab_f
   vrhi_gather_params q{};
   q.size = sizeof q; q.width = ex->width; q.height = ex->height; q.chunk_rows = ex->chunk_rows; q.world = g->world; q.rank = g->rank;
   q.slab_first = slab_first; q.slab_count = slab_count; q.slab_stride = stride; q.seq = seq; q.wait_ms = g->wait_ms;
+  const bool mark = ex->trace && ex->n_marks < 16;
+  if (mark) VRHI_CUDA(cudaEventRecord(ex->t_computed[ex->n_marks], compute->s));
   // sending side, behind the launches that computed these slabs
   VRHI_CUDA(cudaEventRecord(ex->ev_compute, compute->s));
   for (uint32_t k = 0; k < ex->n_push; ++k) VRHI_CUDA(cudaStreamWaitEvent(ex->push[k]->s, ex->ev_compute, 0));
@@ -399,6 +415,7 @@ int vrhi_exchange_publish(vrhi_exchange ex, vrhi_stream compute, uint32_t slab_f
     VRHI_TRY(gather_push_u16(ex->push[0], ex->peer_wire[ex->cur], g->world - 1, static_cast<const uint16_t *>(ex->wire[ex->cur]->ptr), q));
     VRHI_TRY(gather_signal(ex->push[0], ex->peer_flags, g->world - 1, g->rank, seq));
   }
+  if (mark) VRHI_CUDA(cudaEventRecord(ex->t_pushed[ex->n_marks], ex->push[ex->n_push - 1]->s));
   // receiving side: when every peer's rows of this group have landed, widen them into the image; ordered
   // behind the caller's stream as well, so that what it enqueued before this call (a download of the
   // previous step's image, say) is done with the image before a fast peer's rows are widened into it
@@ -410,6 +427,7 @@ int vrhi_exchange_publish(vrhi_exchange ex, vrhi_stream compute, uint32_t slab_f
   w.slab_first = slab_first; w.slab_count = slab_count; w.slab_stride = stride;
   if (ex->squeeze) VRHI_TRY(widen_rows_squeezed(ex->arrive, ex->bytes[ex->cur], static_cast<const uint16_t *>(ex->wire[ex->cur]->ptr), static_cast<uint32_t *>(ex->image->ptr), w, ok));
   else VRHI_TRY(widen_rows_u16(ex->arrive, static_cast<const uint16_t *>(ex->wire[ex->cur]->ptr), static_cast<uint32_t *>(ex->image->ptr), w, ok));
+  if (mark) VRHI_CUDA(cudaEventRecord(ex->t_widened[ex->n_marks++], ex->arrive->s));
   return VRHI_OK;
 }
 
@@ -426,6 +444,11 @@ int vrhi_exchange_complete(vrhi_exchange ex, vrhi_stream stream) {
     VRHI_CUDA(cudaStreamWaitEvent(stream->s, ex->ev_push[k], 0));
   }
   ex->cur ^= 1u;
+  if (ex->trace) {
+    VRHI_CUDA(cudaEventRecord(ex->t_done, stream->s));
+    ex->last_marks = ex->n_marks;
+    ex->n_marks = 0;
+  }
   return VRHI_OK;
 }
 
@@ -433,7 +456,22 @@ int vrhi_exchange_check(vrhi_exchange ex) {
   if (!ex) return fail(VRHI_ERR_INVALID, "NULL exchange");
   if (ex->grp->world == 1) return VRHI_OK;
   for (uint32_t k = 0; k < ex->n_push; ++k) VRHI_TRY(vrhi_stream_synchronize(ex->push[k]));
-  return vrhi_stream_check(ex->arrive);
+  int rc = vrhi_stream_check(ex->arrive);
+  if (ex->trace && ex->last_marks && cudaEventSynchronize(ex->t_done) == cudaSuccess) {
+    // the last completed step, milliseconds after its first group was computed
+    fprintf(stderr, "vrhi_exchange rank %u, last step:", ex->grp->rank);
+    for (uint32_t k = 0; k < ex->last_marks; ++k) {
+      float c = 0.f, p = 0.f, w = 0.f;
+      cudaEventElapsedTime(&c, ex->t_computed[0], ex->t_computed[k]);
+      cudaEventElapsedTime(&p, ex->t_computed[0], ex->t_pushed[k]);
+      cudaEventElapsedTime(&w, ex->t_computed[0], ex->t_widened[k]);
+      fprintf(stderr, " [group %u computed %.3f sent %.3f widened %.3f]", k, c, p, w);
+    }
+    float d = 0.f;
+    cudaEventElapsedTime(&d, ex->t_computed[0], ex->t_done);
+    fprintf(stderr, " complete %.3f\n", d);
+  }
+  return rc;
 }
 
 int vrhi_exchange_launch_count(vrhi_exchange ex, uint64_t *out_count) {

@@ -268,9 +268,10 @@ def flat_color(stream: Stream, color: Buffer, fragments: Buffer, n: int) -> None
     launch(stream, "flat_color", [color.arg(L.UNIFORM), fragments.arg(L.IMAGE)], p)
 
 
-def fp32_probe(stream: Stream, out: Buffer, ffma_per_thread: int, threads: int = 0) -> None:
+def fp32_probe(stream: Stream, out: Buffer, ffma_per_thread: int, threads: int = 0, variant: int = 0) -> None:
+    """``variant``: 0 scalar fma, 1 packed fma.rn.f32x2, 2 packed with an integer add per fma, 3 scalar with one."""
     p = L.ProbeParams()
-    p.size, p.ffma_per_thread, p.threads = C.sizeof(L.ProbeParams), int(ffma_per_thread), int(threads)
+    p.size, p.ffma_per_thread, p.threads, p.variant = C.sizeof(L.ProbeParams), int(ffma_per_thread), int(threads), int(variant)
     launch(stream, "fp32_probe", [out.arg(L.OUTPUT)], p)
 
 

@@ -378,9 +378,16 @@ def hbm_workloads(dev, st, torch, rank, world, hbm_peak, peak_kind, grp=None, gr
     bW, bx, bb, bt_, bdW, bdx, bdb, bl = (dev.wrap_tensor(t) for t in (sW, sx, bt, stt, dWt, dxt, dbt, lt))
     bsmall = dev.wrap_tensor(small)
 
+    tstream = None
+    if world > 1 and grp is None:   # no peer mapping on this box: the process group's all-reduce on the same stream
+        tstream = torch.cuda.ExternalStream(st.cuda_stream, device=device)
+
     def reduce_small():
-        if world > 1:
+        if world > 1 and grp is not None:
             grp.all_reduce_sum(bsmall, Cc + 1, st)   # db and the loss: one call of the library's own all-reduce
+        elif world > 1:
+            with torch.cuda.stream(tstream):
+                dist.all_reduce(small)
 
     def fwd():
         ops.mse_tanh_fwd(st, bW, bx, bb, bt_, bl, cnt, Cc, denom)
@@ -389,7 +396,7 @@ def hbm_workloads(dev, st, torch, rank, world, hbm_peak, peak_kind, grp=None, gr
     ms = timed(fwd)
     st.check()
     small.zero_(); torch.cuda.synchronize(); fwd(); st.check()
-    line("tanh-MSE loss [32768,4096]", "mse_tanh_fwd" + (" + all-reduce" if world > 1 else ""), ms, 12 * R * Cc,
+    line("tanh-MSE loss [32768,4096]", "mse_tanh_fwd" + (" + vrhi all-reduce" if world > 1 and grp is not None else " + all-reduce" if world > 1 else ""), ms, 12 * R * Cc,
          check_mse(Wt, xt, bt, tt, denom, loss=lt.item()) if rank == 0 else (True, 0.0))
 
     def bwd(reduce=True):
@@ -405,7 +412,7 @@ def hbm_workloads(dev, st, torch, rank, world, hbm_peak, peak_kind, grp=None, gr
     small.zero_(); torch.cuda.synchronize(); bwd(); st.check()
     ok_rows = check_mse(Wt, xt, bt, tt, denom, dWt, dxt, lo)
     ok_sum = check_mse(Wt, xt, bt, tt, denom, db=dbt, loss=lt.item()) if rank == 0 else (True, 0.0)
-    line("tanh-MSE backward dW,dx,db,loss [32768,4096]", "mse_tanh_bwd" + (" + all-reduce of db and loss" if world > 1 else ""), ms,
+    line("tanh-MSE backward dW,dx,db,loss [32768,4096]", "mse_tanh_bwd" + (" + vrhi all-reduce of db and loss" if world > 1 and grp is not None else " + all-reduce of db and loss" if world > 1 else ""), ms,
          20 * R * Cc + 8 * Cc, (ok_rows[0] and ok_sum[0], max(ok_rows[1], ok_sum[1])), **extra)
     if graphs and world == 1:
         # The same gradients through the generic path: the execution graph differentiates the loss and fuses the
@@ -805,8 +812,12 @@ def main():
             comm_stream2 = torch.cuda.Stream(device=local)
             comm_st2 = dev.wrap_stream(comm_stream2.cuda_stream)
         exchange = None
-        grp = group.Group(dev, world, rank, group.torch_allgather())   # bootstrap over the process group; the data path is the library's
-        if args.gather != "nccl":
+        try:
+            grp = group.Group(dev, world, rank, group.torch_allgather())   # bootstrap over the process group; the data path is the library's
+        except Exception as exc:  # no peer mapping on this box
+            print(f"vrhi_group unavailable ({exc}); using torch.distributed for the exchange steps", file=sys.stderr)
+            grp = None
+        if args.gather != "nccl" and grp is not None:
             try:
                 if args.gather == "push16":
                     exchange = grp.image_exchange(image, W, H, 128)

@@ -108,7 +108,9 @@ class Device:
         """Adopt an existing CUDA stream handle, e.g. ``torch.cuda.current_stream().cuda_stream``."""
         h = C.c_void_p()
         check(lib().vrhi_stream_wrap(self._h, C.c_void_p(int(cuda_stream)), C.byref(h)))
-        return Stream(self, h)
+        s = Stream(self, h)
+        s.cuda_stream = int(cuda_stream)
+        return s
 
     def event(self) -> "Event":
         h = C.c_void_p()
@@ -197,6 +199,7 @@ class Stream:
 
     def __init__(self, dev: Device, handle):
         self.dev, self._h = dev, handle
+        self.cuda_stream = None   # the adopted CUDA stream handle, where this stream wraps one
 
     def close(self) -> None:
         if self._h:

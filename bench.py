@@ -853,12 +853,12 @@ def main():
         mark("start", tstream)
         if native:
             # the whole exchange is the library's: publish after each group's launch, complete at the end of the step
-            wire = exchange.wire
+            wire, byte_plane = exchange.planes
             if TWO_COMPUTE_STREAMS:
                 tstream2.wait_stream(tstream)
             for gi, (gp, slabs) in enumerate(zip(group_params, group_slabs)):
                 cs_t, cs = (tstream2, st2) if (TWO_COMPUTE_STREAMS and gi % 2) else (tstream, st)
-                ops.escape_time(cs, image, gp, wire=wire)
+                ops.escape_time(cs, image, gp, wire=wire, byte_plane=byte_plane)
                 mark(f"computed {gi}", cs_t)
                 exchange.publish(cs, slabs)
             if TWO_COMPUTE_STREAMS:
@@ -916,8 +916,9 @@ def main():
                     w.wait()   # the compute stream waits for the gathers: the step is complete after this
 
     EXCHANGE_NOTE = ("none" if world == 1 else
-                     "vrhi_exchange (C ABI, no collective library): every rank stores its uint16 rows into its peers' wire images over NVLink from a "
-                     "small kernel beside the next group's compute, sequence flags with bounded device waits, widened on arrival" if native else
+                     "vrhi_exchange (C ABI, no collective library): the copy engines move every rank's rows into its peers while the next group "
+                     "computes (uint16 counts at 2 ranks; from 3 ranks on a byte plane, counts of 255 and more fetched from the owner), "
+                     "sequence flags with bounded device waits, widened on arrival" if native else
                      "no collective: each rank reads its peers' rows as uint16 out of their memory over NVLink and widens them into "
                      "its uint32 image in one kernel, group by group while later groups compute; readiness flags with bounded device waits" if pulling else
                      "image chunks pushed into every peer's image by strided peer copies (copy engines over NVLink), overlapped with "

@@ -253,13 +253,19 @@ typedef struct vrhi_escape_params {
 /* op "escape_time", optional second argument: a uint16 image of the same [height][width]
  * geometry that receives every count a second time (uint32 counts only, max_iter <= 65535).
  * It is the form in which a rank sends its rows to its peers when the image is gathered over
- * NVLink: half the bytes, nothing lost.
+ * NVLink: half the bytes, nothing lost.  Optional third argument: a plane of bytes of the same
+ * geometry that receives min(count, 255): a quarter of the bytes; a byte of 255 sends the reader
+ * to the uint16 image (vrhi_exchange_* moves this plane where it pays and fetches the rest).
  *
  * op "widen_rows_u16" -- the receiving side: copies uint16 counts into the uint32 image for the
  * rows of slabs slab_first .. slab_first+slab_count-1 (a slab = `world` consecutive chunks of
  * chunk_rows rows), leaving out the chunks of `skip_rank` (the caller's own, already present in
  * full width); skip_rank >= world widens every chunk.
  * args: [0] wire (uint16 [height][width]), [1] image (uint32 [height][width], writable).
+ * op "widen_rows_u8" -- the same from a plane of bytes min(count, 255): args [0] bytes (uint8
+ * [height][width]), [1] image, [2..] the uint16 wire images of ranks 0..world-1 (mapped peer memory
+ * or local); a 16-pixel granule that shows a byte of 255 is taken from the wire image of the rank
+ * that owns the row.  width a multiple of 16.
  * Reference counterpart: none (the reference runs on one device). */
 typedef struct vrhi_widen_params {
   uint32_t size;
@@ -468,26 +474,34 @@ VRHI_API int vrhi_group_all_reduce_sum_f32(vrhi_group group, vrhi_buffer buf, ui
  * uint16 (max_iter <= 65535): the exchange owns two uint16 wire images per rank, which alternate
  * from step to step so that a fast rank never stores into rows a slower peer is still reading.
  *
+ * From three ranks on the exchange by default squeezes the counts further: the kernel also writes a
+ * plane of bytes min(count, 255) (a third argument), that plane is what the copy engines move, and
+ * the receiving kernel fetches the 16-pixel granules that show a byte of 255 from the owner's uint16
+ * wire image over NVLink.  Lossless whatever the image; VRHI_EXCHANGE_SQUEEZE=0/1 overrides.
+ *
  * One step on every rank:
- *   vrhi_exchange_wire(ex, &wire);                     the wire image of this step
+ *   vrhi_exchange_planes(ex, &wire, &bytes);           this step's wire image and byte plane (bytes == NULL: not squeezing)
  *   for each group of slabs (the same groups, in the same order, on every rank; a slab = `world`
  *   consecutive chunks, one per rank):
- *     vrhi_op_launch(compute_stream, escape_time, {image, wire}, params of the rank's chunks of the group);
+ *     vrhi_op_launch(compute_stream, escape_time, {image, wire[, bytes]}, params of the rank's chunks of the group);
  *     vrhi_exchange_publish(ex, compute_stream, slab_first, slab_count, slab_stride);
  *   vrhi_exchange_complete(ex, stream);
- * publish, behind the work already enqueued on compute_stream, stores the rank's rows of those
- * slabs into every peer's wire image and raises its sequence number there (on a stream of the
- * exchange, so the next group's kernel is not held up), and enqueues the receiving side: a bounded
- * wait for every peer's number, then the widening of their rows into `image`.  complete makes
- * `stream` wait for all of the step's arrivals and for this rank's own stores, and switches to the
- * other wire image; work enqueued on `stream` afterwards sees the whole image, and the next step's
- * launches must be ordered behind it.  No host synchronisation anywhere in a step.
+ * publish marks the point of compute_stream behind which the rank's rows of those slabs are ready; it
+ * costs one event record, so that the caller's next launch is not held up.  The transfer of every
+ * published group is enqueued, in order, by the next call that is not a publish (complete or check;
+ * after 16 groups at the latest): behind that point, on streams of the exchange, the copy engines send
+ * the rank's rows into every peer's wire image (or byte plane) and the rank's sequence number is
+ * raised there; on another stream a bounded wait for every peer's number is followed by the widening of
+ * their rows into `image`.  complete makes `stream` wait for all of the step's arrivals and for this
+ * rank's own transfers, and switches to the other wire image; work enqueued on `stream` afterwards
+ * sees the whole image, and the next step's launches must be ordered behind it.  No host
+ * synchronisation anywhere in a step.
  * vrhi_exchange_check synchronises the exchange's streams and returns VRHI_ERR_TIMEOUT if a peer
  * failed to arrive in time (its rows are then missing from the image). */
 VRHI_API int vrhi_exchange_create(vrhi_group group, vrhi_buffer image, uint32_t width, uint32_t height, uint32_t chunk_rows,
                                   vrhi_exchange *out_exchange);
 VRHI_API int vrhi_exchange_destroy(vrhi_exchange exchange); /* before the group; NULL is accepted */
-VRHI_API int vrhi_exchange_wire(vrhi_exchange exchange, vrhi_buffer *out_wire);
+VRHI_API int vrhi_exchange_planes(vrhi_exchange exchange, vrhi_buffer *out_wire, vrhi_buffer *out_bytes);
 VRHI_API int vrhi_exchange_publish(vrhi_exchange exchange, vrhi_stream compute_stream, uint32_t slab_first,
                                    uint32_t slab_count, uint32_t slab_stride);
 VRHI_API int vrhi_exchange_complete(vrhi_exchange exchange, vrhi_stream stream);

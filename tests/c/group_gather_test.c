@@ -92,16 +92,16 @@ static int run_rank(shared_t *sh, int world, int rank) {
 
   const float ci[STEPS] = {0.156f, 0.2f, -0.11f};
   for (int s = 0; s < STEPS; ++s) {  /* no host synchronisation and no barrier inside this loop */
-    vrhi_buffer wire;
-    OK(vrhi_exchange_wire(ex, &wire));
+    vrhi_buffer wire, bytes;
+    OK(vrhi_exchange_planes(ex, &wire, &bytes));  /* bytes == NULL where the exchange does not squeeze the counts */
     for (int g = 0; g < GROUPS; ++g) {
       vrhi_escape_params p;
       julia(&p, ci[s]);
       const uint32_t count = (part.chunk_count - g + GROUPS - 1) / GROUPS;  /* slabs g, g+GROUPS, ... */
       p.chunk_rows = part.chunk_rows; p.chunk_first = part.chunk_first + g * part.chunk_step;
       p.chunk_step = part.chunk_step * GROUPS; p.chunk_count = count;
-      vrhi_arg args[2] = {{image, 0, 0, VRHI_IMAGE, 0}, {wire, 0, 0, VRHI_IMAGE, 0}};
-      OK(vrhi_op_launch(st, op, args, 2, &p, sizeof p));
+      vrhi_arg args[3] = {{image, 0, 0, VRHI_IMAGE, 0}, {wire, 0, 0, VRHI_IMAGE, 0}, {bytes, 0, 0, VRHI_IMAGE, 0}};
+      OK(vrhi_op_launch(st, op, args, bytes ? 3 : 2, &p, sizeof p));
       OK(vrhi_exchange_publish(ex, st, (uint32_t)g, count, GROUPS));
     }
     OK(vrhi_exchange_complete(ex, st));

@@ -84,10 +84,10 @@ def main() -> int:
     constants = [0.156, 0.21, -0.09]
     hosts = [vd.PinnedArray((H, W), np.uint32) for _ in constants]
     for step, ci in enumerate(constants):
-        wire = ex.wire
+        wire, byte_plane = ex.planes
         for g, p, comb in groups():
             p.ci = ci
-            ops.escape_time(st, image, p, wire=wire)
+            ops.escape_time(st, image, p, wire=wire, byte_plane=byte_plane)
             ex.publish(st, comb)
         ex.complete(st)
         image.download(hosts[step].array, stream=st)

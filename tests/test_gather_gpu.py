@@ -95,6 +95,50 @@ def test_gather_with_uint16_on_the_wire_rebuilds_the_whole_image(W, world):
     st.close()
 
 
+@pytest.mark.parametrize("world,max_iter", [(2, 400), (4, 400), (4, 200)])
+def test_gather_with_a_byte_plane_rebuilds_the_whole_image(world, max_iter):
+    """The squeezed form of the gather, ranks played one after the other on one GPU: the kernel writes
+    min(count, 255) into a byte plane beside the uint16 wire image, only the byte plane is pushed,
+    and the widening kernel fetches the granules that show a byte of 255 from the owner's wire image
+    (here: another buffer on the same GPU).  max_iter 200 leaves no count above 254: nothing is fetched."""
+    dev = vd.Device(0)
+    st = dev.stream()
+    W, chunk_rows, slabs = 512, 8, 3
+    H = chunk_rows * world * slabs
+    dx, dy, want = _julia(W, H, max_iter)
+    assert (want >= 255).any() == (max_iter > 254)
+    images = [dev.empty((H, W), np.uint32, L.IMAGE) for _ in range(world)]
+    wires = [dev.empty((H, W), np.uint16, L.IMAGE) for _ in range(world)]
+    planes = [dev.empty((H, W), np.uint8, L.IMAGE) for _ in range(world)]
+    for r in range(world):
+        images[r].fill(0xEE, stream=st)
+        wires[r].fill(0xDD, stream=st)
+        planes[r].fill(0xCC, stream=st)
+        part = ops.partition_rows(H, world, r, L.PART_CYCLIC, chunk_rows)
+        p = ops.escape_params(L.JULIA, W, H, J["x0"], J["y0"], dx, dy, cr=J["cr"], ci=J["ci"], max_iter=max_iter, partition=part)
+        ops.escape_time(st, images[r], p, wire=wires[r], byte_plane=planes[r])
+    st.check()
+    # the byte plane of a rank holds min(count, 255) on the rank's own rows
+    own0 = np.zeros(H, bool)
+    for k in range(slabs):
+        own0[(k * world) * chunk_rows:(k * world + 1) * chunk_rows] = True
+    got = planes[0].download(dtype=np.uint8, shape=(H, W))
+    assert np.array_equal(got[own0], np.minimum(want[own0], 255).astype(np.uint8))
+    # the push: rank r's chunks of the BYTE plane into every peer's byte plane; the wire images stay where they are
+    chunk_bytes = chunk_rows * W
+    for r in range(world):
+        for q in range(world):
+            if q != r:
+                planes[r].copy_2d_to(planes[q], r * chunk_bytes, world * chunk_bytes, r * chunk_bytes, world * chunk_bytes, chunk_bytes, slabs, st)
+    for r in range(world):
+        ops.widen_rows_u8(st, planes[r], images[r], wires, W, H, chunk_rows, world, r, 0, 2, 2)
+        ops.widen_rows_u8(st, planes[r], images[r], wires, W, H, chunk_rows, world, r, 1, 1, 2)
+    st.check()
+    for r in range(world):
+        assert np.array_equal(images[r].download(dtype=np.uint32, shape=(H, W)), want), r
+    st.close()
+
+
 def test_pull_gather_reads_the_peers_rows_and_widens_them():
     dev = vd.Device(0)
     st = dev.stream()

@@ -190,7 +190,7 @@ PROTOTYPES = {
     "vrhi_group_all_reduce_sum_f32": [_vp, _vp, _u64, _u64, _vp],
     "vrhi_exchange_create": [_vp, _vp, _u32, _u32, _u32, _P(_vp)],
     "vrhi_exchange_destroy": [_vp],
-    "vrhi_exchange_wire": [_vp, _P(_vp)],
+    "vrhi_exchange_planes": [_vp, _P(_vp), _P(_vp)],
     "vrhi_exchange_publish": [_vp, _vp, _u32, _u32, _u32],
     "vrhi_exchange_complete": [_vp, _vp],
     "vrhi_exchange_check": [_vp],

@@ -22,6 +22,7 @@ struct EscapeDev {
   uint32_t n_batches;
   uint32_t transposed;       // 1: the row coordinate is the real part and the column coordinate the imaginary part
   float neg_zero;            // -0.0f, set by the host: an addend the assembler cannot fold (k_escape_pair.cu)
+  uint8_t *bytes;            // optional third copy of every count, min(count, 255), at the same pixel index (nullptr: none)
 };
 
 // Step primitives.  EXACT keeps a = zr*zr and b = zi*zi alongside z so that one update costs six
@@ -70,7 +71,12 @@ __device__ __forceinline__ void store_count(void *image, size_t pix, uint32_t co
 
 // Second copy of a count as uint16 at the same pixel index (the compact form a rank sends to its
 // peers when the image is gathered; counts up to 65535 lose nothing).
-__device__ __forceinline__ void store_wire(uint16_t *wire, size_t pix, uint32_t count) { wire[pix] = (uint16_t)count; }
+// With `bytes` also min(count, 255) as one byte: the plane that crosses NVLink where the counts are squeezed
+// (a byte of 255 tells the receiving side to fetch the uint16 count).
+__device__ __forceinline__ void store_wire(uint16_t *wire, uint8_t *bytes, size_t pix, uint32_t count) {
+  wire[pix] = (uint16_t)count;
+  if (bytes) bytes[pix] = (uint8_t)min(count, 255u);
+}
 
 // Order in which a launch visits its rows: from the middle outwards (k = 0 is the middle row).  The
 // expensive rows of these images lie around the middle and hold the pixels that run for thousands

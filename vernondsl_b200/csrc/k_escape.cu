@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(256) escape_checked_kernel(EscapeDev p, void *
         ++count;
       }
       store_count<OUT>(image, row_base + i, count, p.color_scale);
-      if (wire) store_wire(wire, row_base + i, count);
+      if (wire) store_wire(wire, p.bytes, row_base + i, count);
     }
   }
 }
@@ -89,15 +89,21 @@ static void launch_checked_test(int test, int out, int grid, cudaStream_t s, con
 int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const void *params, size_t params_size) {
   vrhi_escape_params q;
   VRHI_TRY(read_params(params, params_size, &q));
-  if (n_args != 1 && n_args != 2) return fail(VRHI_ERR_INVALID, "escape_time takes the image and, optionally, a uint16 wire copy; got %d arguments", n_args);
+  if (n_args < 1 || n_args > 3) return fail(VRHI_ERR_INVALID, "escape_time takes the image and, optionally, a uint16 wire copy and a byte plane; got %d arguments", n_args);
   if (!writable(args[0])) return fail(VRHI_ERR_INVALID, "escape_time: the image buffer is read-only (class %s)", vrhi_arg_class_name(args[0].buf_cls));
   uint16_t *wire = nullptr;
-  if (n_args == 2) {
+  uint8_t *byte_plane = nullptr;
+  if (n_args >= 2) {
     if (q.output != VRHI_OUT_COUNT_U32) return fail(VRHI_ERR_INVALID, "escape_time: the uint16 wire copy goes with uint32 counts only");
     if (q.max_iter > 65535u) return fail(VRHI_ERR_UNSUPPORTED, "escape_time: a uint16 wire copy needs max_iter <= 65535");
     if (!writable(args[1])) return fail(VRHI_ERR_INVALID, "escape_time: the wire buffer is read-only (class %s)", vrhi_arg_class_name(args[1].buf_cls));
     if (args[1].bytes < (uint64_t)q.width * q.height * 2) return fail(VRHI_ERR_SIZE, "escape_time: the wire view holds %llu bytes, %llu needed", (unsigned long long)args[1].bytes, (unsigned long long)q.width * q.height * 2);
     wire = reinterpret_cast<uint16_t *>(args[1].ptr);
+    if (n_args == 3) {
+      if (!writable(args[2])) return fail(VRHI_ERR_INVALID, "escape_time: the byte plane is read-only (class %s)", vrhi_arg_class_name(args[2].buf_cls));
+      if (args[2].bytes < (uint64_t)q.width * q.height) return fail(VRHI_ERR_SIZE, "escape_time: the byte plane holds %llu bytes, %llu needed", (unsigned long long)args[2].bytes, (unsigned long long)q.width * q.height);
+      byte_plane = reinterpret_cast<uint8_t *>(args[2].ptr);
+    }
   }
   if (q.kind > VRHI_ESCAPE_JULIA || q.mode > VRHI_ESCAPE_FAST || q.test > VRHI_TEST_NORM_GE || q.output > VRHI_OUT_COLOR_F32)
     return fail(VRHI_ERR_INVALID, "escape_time: kind/mode/test/output out of range");
@@ -134,6 +140,7 @@ int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const
   }
   if (p.rows_owned == 0) return VRHI_OK;  // an empty band is not an error
   p.neg_zero = -0.0f;
+  p.bytes = byte_plane;
   // tuning aids, read once per process
   static const int env_batch = [] { const char *e = getenv("VRHI_ESCAPE_BATCH"); return e ? atoi(e) : 0; }();
   static const int env_per_sm = [] { const char *e = getenv("VRHI_ESCAPE_CTAS_PER_SM"); return e ? atoi(e) : 0; }();

@@ -141,7 +141,7 @@ __global__ void __launch_bounds__(256, 4) escape_pair_kernel(EscapeDev p, void *
 
   auto finish = [&](uint32_t pix, uint32_t count) {
     store_count<OUT>(image, (size_t)pix, count, color_scale);
-    if (WIRE) store_wire(wire, (size_t)pix, count);
+    if (WIRE) store_wire(wire, p.bytes, (size_t)pix, count);
   };
 
   auto intake = [&]() {

@@ -7,11 +7,18 @@
 namespace vrhi {
 
 // A block widens whole image rows, one after the other (grid-stride over the rows to do): every
-// thread keeps four 16-byte loads of eight counts in flight and writes two 16-byte stores for each.
+// thread keeps kWidenInFlight 16-byte loads in flight and writes two 16-byte stores for each.  The grid is
+// kWidenBlocksPerSm blocks per SM and no more: the kernel runs beside the escape-time launches of
+// the following groups, and a grid that filled every thread slot (8 blocks of 256 per SM, as a
+// first form did, on a high-priority stream) kept those launches off the SMs until it was through
+// (measured at 8 ranks: the four groups of a step computed in 0.9 ms instead of 0.4 ms).
 // Rows are enumerated slab by slab over the chunks the skipped rank does not own.  HBM-bound: 2 B
 // read + 4 B written per pixel.  (A first form with one short-lived block per 2048 pixels reached
 // 2.1 TB/s; at four and eight ranks the widening of 3/4 and 7/8 of the image was then the longest
 // part of a step.)
+constexpr int kWidenInFlight = 8;
+constexpr int kWidenBlocksPerSm = 2;
+
 template <bool VEC>
 __global__ void __launch_bounds__(256) widen_rows_u16_kernel(const uint16_t *__restrict__ wire, uint32_t *__restrict__ image,
                                                              uint32_t width, uint32_t height, uint32_t chunk_rows, uint32_t world,
@@ -32,13 +39,13 @@ __global__ void __launch_bounds__(256) widen_rows_u16_kernel(const uint16_t *__r
       const uint32_t segs = width / 8u;
       const uint4 *src = reinterpret_cast<const uint4 *>(wire + base);
       uint4 *dst = reinterpret_cast<uint4 *>(image + base);
-      for (uint32_t v0 = threadIdx.x; v0 < segs; v0 += 1024u) {
-        uint4 in[4];
+      for (uint32_t v0 = threadIdx.x; v0 < segs; v0 += 256u * kWidenInFlight) {
+        uint4 in[kWidenInFlight];
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int j = 0; j < kWidenInFlight; ++j)
           if (v0 + j * 256u < segs) in[j] = __ldcs(src + v0 + j * 256u);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < kWidenInFlight; ++j) {
           const uint32_t v = v0 + j * 256u;
           if (v < segs) {
             __stcs(dst + 2 * (size_t)v, make_uint4(in[j].x & 0xffffu, in[j].x >> 16, in[j].y & 0xffffu, in[j].y >> 16));
@@ -66,7 +73,7 @@ int widen_rows_u16(vrhi_stream_t *st, const uint16_t *wire, uint32_t *image, con
   if (total_rows == 0) return VRHI_OK;  // nothing to widen (one rank, or an empty slab range)
   if (total_rows > 0xffffffffull) return fail(VRHI_ERR_UNSUPPORTED, "widen_rows_u16: too many rows");
   const bool vec = q.width % 8 == 0 && ((uintptr_t)wire % 16 == 0) && ((uintptr_t)image % 16 == 0);
-  const uint64_t cap = (uint64_t)st->dev->prop.multiProcessorCount * 8;  // resident at once: a persistent grid over the rows
+  const uint64_t cap = (uint64_t)st->dev->prop.multiProcessorCount * kWidenBlocksPerSm;  // a persistent grid over the rows
   const unsigned grid = (unsigned)(total_rows < cap ? total_rows : cap);
   if (vec)
     widen_rows_u16_kernel<true><<<grid, 256, 0, st->s>>>(wire, image, q.width, q.height, q.chunk_rows, q.world, q.skip_rank, q.slab_first, stride, (uint32_t)total_rows, ok);
@@ -309,76 +316,25 @@ int gather_push_u16(vrhi_stream_t *st, uint16_t *const *peer_wires, uint32_t n_p
 }
 
 // ---------------------------------------------------------------------------------------------
-// The same push with the counts squeezed to one byte where that loses nothing.  Far from the set
-// almost every count is small (on the 16384^2 Julia image 97 % are below 255), so the rows cross
-// NVLink as a plane of bytes, min(count, 255), and only the 16-pixel granules that hold a count of
-// 255 or more are sent in full, as uint16, into the same place of the peer's uint16 wire image.
-// The receiving side reads the byte plane and, where a granule shows a byte of 255, takes that
-// granule from the uint16 wire image instead (it was stored there in this very step, by the same
-// thread, before the rank raised its sequence number).  No lists, no counters, no capacity to
-// overflow: an image of nothing but large counts costs 1.5 times the plain uint16 push, the usual
-// image a little over half of it.
-struct PeerPlanes {
-  uint8_t *bytes[VRHI_GATHER_MAX_WORLD];   // the peers' byte planes [height][width]
-  uint16_t *wide[VRHI_GATHER_MAX_WORLD];   // the peers' uint16 wire images
+// The counts squeezed to one byte where that loses nothing.  Far from the set almost every count is
+// small (on the 16384^2 Julia image 97 % are below 255).  The escape-time kernel therefore writes,
+// beside the uint32 image and the uint16 wire image, a plane of bytes min(count, 255) (its optional
+// third argument); the copy engines move a rank's rows of that plane to the peers, half the bytes of
+// the uint16 rows, and the receiving kernel below takes every 16-pixel granule from the byte plane
+// unless the granule shows a byte of 255: then it fetches the granule's uint16 counts from the
+// OWNER's wire image with two 16-byte loads over NVLink (6 % of the granules of that image).  No
+// sending kernel, no lists, no counters, no capacity to overflow: an image of nothing but large
+// counts costs 1.5 times the plain uint16 transfer, the usual image a little over half of it.
+// The owner's wire image of a step stays untouched until two steps later (two images alternate),
+// and a rank cannot run two steps ahead of a peer whose rows it needs: what is fetched is this step's.
+struct OwnerWires {
+  const uint16_t *wire[VRHI_GATHER_MAX_WORLD];  // every rank's uint16 wire image of this step, by rank (the caller's own is unused)
 };
 
-__device__ __forceinline__ uint32_t squeeze4(uint32_t lo, uint32_t hi) {
-  // four uint16 counts (two per word) -> four bytes min(count, 255)
-  const uint32_t a = min(lo & 0xffffu, 255u), b = min(lo >> 16, 255u), c = min(hi & 0xffffu, 255u), d = min(hi >> 16, 255u);
-  return a | (b << 8) | (c << 16) | (d << 24);
-}
 __device__ __forceinline__ bool has_ff(uint32_t w) { return __vcmpeq4(w, 0xffffffffu) != 0u; }
 
-constexpr int kSqueezeRows = 2;  // rows in flight per thread (two 16-byte loads each)
-
-__global__ void __launch_bounds__(128) gather_push_squeezed_kernel(PeerPlanes peers, uint32_t n_peers, const uint16_t *__restrict__ wire, uint32_t width,
-                                                                   uint32_t height, uint32_t chunk_rows, uint32_t world, uint32_t rank,
-                                                                   uint32_t slab_first, uint32_t slab_stride, uint32_t total_rows) {
-  const uint32_t v = blockIdx.x * 128u + threadIdx.x;   // granule of 16 pixels within the row
-  if (v * 16u >= width) return;
-  for (uint32_t u0 = blockIdx.y; u0 < total_rows; u0 += gridDim.y * kSqueezeRows) {
-    uint4 a[kSqueezeRows], b[kSqueezeRows];
-    size_t at[kSqueezeRows];
-    bool ok[kSqueezeRows];
-#pragma unroll
-    for (int k = 0; k < kSqueezeRows; ++k) {
-      const uint32_t u = u0 + (uint32_t)k * gridDim.y;
-      ok[k] = false;
-      if (u < total_rows) {
-        const uint32_t slab = u / chunk_rows, rr = u - slab * chunk_rows;
-        const uint64_t row = ((uint64_t)(slab_first + slab * slab_stride) * world + rank) * chunk_rows + rr;
-        if (row < height) {
-          ok[k] = true;
-          at[k] = (size_t)row * width / 16 + v;
-          const uint4 *src = reinterpret_cast<const uint4 *>(wire) + 2 * at[k];
-          a[k] = __ldcg(src);
-          b[k] = __ldcg(src + 1);
-        }
-      }
-    }
-#pragma unroll
-    for (int k = 0; k < kSqueezeRows; ++k) {
-      if (!ok[k]) continue;
-      uint4 sq;
-      sq.x = squeeze4(a[k].x, a[k].y); sq.y = squeeze4(a[k].z, a[k].w);
-      sq.z = squeeze4(b[k].x, b[k].y); sq.w = squeeze4(b[k].z, b[k].w);
-      const bool big = has_ff(sq.x) || has_ff(sq.y) || has_ff(sq.z) || has_ff(sq.w);
-      for (uint32_t q = 0; q < n_peers; ++q) {
-        if (big) {
-          uint4 *dst = reinterpret_cast<uint4 *>(peers.wide[q]) + 2 * at[k];
-          __stcg(dst, a[k]);
-          __stcg(dst + 1, b[k]);
-        }
-        __stcg(reinterpret_cast<uint4 *>(peers.bytes[q]) + at[k], sq);
-      }
-    }
-  }
-}
-
-// The receiving side of the squeezed push: byte plane -> uint32 image, granules with a byte of 255 from
-// the uint16 wire image.  Rows and blocks as in widen_rows_u16_kernel; a granule is 16 pixels.
-__global__ void __launch_bounds__(256) widen_rows_squeezed_kernel(const uint8_t *__restrict__ bytes, const uint16_t *__restrict__ wide,
+// Byte plane -> uint32 image.  Rows and blocks as in widen_rows_u16_kernel; a granule is 16 pixels.
+__global__ void __launch_bounds__(256) widen_rows_squeezed_kernel(const uint8_t *__restrict__ bytes, OwnerWires owners,
                                                                   uint32_t *__restrict__ image, uint32_t width, uint32_t height,
                                                                   uint32_t chunk_rows, uint32_t world, uint32_t skip_rank, uint32_t slab_first,
                                                                   uint32_t slab_stride, uint32_t total_rows, const uint32_t *ok) {
@@ -393,21 +349,21 @@ __global__ void __launch_bounds__(256) widen_rows_squeezed_kernel(const uint8_t 
     const uint64_t row = ((uint64_t)(slab_first + slab * slab_stride) * world + q) * chunk_rows + rr;
     if (row >= height) continue;
     const size_t g0 = (size_t)row * segs;
-    for (uint32_t v0 = threadIdx.x; v0 < segs; v0 += 1024u) {
-      uint4 in[4];
+    for (uint32_t v0 = threadIdx.x; v0 < segs; v0 += 256u * kWidenInFlight) {
+      uint4 in[kWidenInFlight];
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
+      for (int j = 0; j < kWidenInFlight; ++j)
         if (v0 + j * 256u < segs) in[j] = __ldcs(reinterpret_cast<const uint4 *>(bytes) + g0 + v0 + j * 256u);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < kWidenInFlight; ++j) {
         const uint32_t v = v0 + j * 256u;
         if (v >= segs) continue;
         const size_t at = g0 + v;
         const uint4 sq = in[j];
         uint4 *out = reinterpret_cast<uint4 *>(image) + 4 * at;
         if (has_ff(sq.x) || has_ff(sq.y) || has_ff(sq.z) || has_ff(sq.w)) {
-          const uint4 *src = reinterpret_cast<const uint4 *>(wide) + 2 * at;
-          const uint4 a = __ldcs(src), b = __ldcs(src + 1);
+          const uint4 *src = reinterpret_cast<const uint4 *>(owners.wire[q]) + 2 * at;   // rank q computed this row
+          const uint4 a = __ldcg(src), b = __ldcg(src + 1);                                 // L2 only: never a stale L1 line
           __stcs(out, make_uint4(a.x & 0xffffu, a.x >> 16, a.y & 0xffffu, a.y >> 16));
           __stcs(out + 1, make_uint4(a.z & 0xffffu, a.z >> 16, a.w & 0xffffu, a.w >> 16));
           __stcs(out + 2, make_uint4(b.x & 0xffffu, b.x >> 16, b.y & 0xffffu, b.y >> 16));
@@ -423,37 +379,42 @@ __global__ void __launch_bounds__(256) widen_rows_squeezed_kernel(const uint8_t 
   }
 }
 
-int gather_push_squeezed(vrhi_stream_t *st, uint8_t *const *peer_bytes, uint16_t *const *peer_wide, uint32_t n_peers, const uint16_t *wire,
-                         const vrhi_gather_params &q) {
-  if (n_peers == 0 || n_peers >= VRHI_GATHER_MAX_WORLD) return fail(VRHI_ERR_INVALID, "gather push: 1..%d peers", VRHI_GATHER_MAX_WORLD - 1);
-  if (q.width % 16 != 0) return fail(VRHI_ERR_UNSUPPORTED, "gather push (squeezed): the width must be a multiple of 16 pixels");
-  const uint32_t stride = q.slab_stride ? q.slab_stride : 1u;
-  const uint64_t total_rows = (uint64_t)q.slab_count * q.chunk_rows;
-  if (total_rows == 0) return VRHI_OK;
-  if (total_rows > 0xffffffffull) return fail(VRHI_ERR_UNSUPPORTED, "gather push: too many rows");
-  PeerPlanes pp{};
-  for (uint32_t k = 0; k < n_peers; ++k) { pp.bytes[k] = peer_bytes[k]; pp.wide[k] = peer_wide[k]; }
-  dim3 grid;
-  grid.x = (q.width / 16 + 127) / 128;
-  static const int per_sm = env_int("VRHI_PUSH_BLOCKS_PER_SM", 1, 16, 8);  // tuning aid
-  const uint64_t want_y = ((uint64_t)st->dev->prop.multiProcessorCount * per_sm + grid.x - 1) / grid.x;
-  const uint64_t max_y = (total_rows + kSqueezeRows - 1) / kSqueezeRows;
-  grid.y = (unsigned)(want_y < max_y ? want_y : max_y);
-  gather_push_squeezed_kernel<<<grid, 128, 0, st->s>>>(pp, n_peers, wire, q.width, q.height, q.chunk_rows, q.world, q.rank, q.slab_first, stride, (uint32_t)total_rows);
-  return post_launch(st, "gather_push_squeezed");
-}
-
-int widen_rows_squeezed(vrhi_stream_t *st, const uint8_t *bytes, const uint16_t *wide, uint32_t *image, const vrhi_widen_params &q, const uint32_t *ok) {
+int widen_rows_squeezed(vrhi_stream_t *st, const uint8_t *bytes, const uint16_t *const *wire_by_rank, uint32_t *image, const vrhi_widen_params &q, const uint32_t *ok) {
+  if (q.world > VRHI_GATHER_MAX_WORLD) return fail(VRHI_ERR_INVALID, "widen (squeezed): at most %d ranks", VRHI_GATHER_MAX_WORLD);
+  OwnerWires ow{};
+  for (uint32_t r = 0; r < q.world; ++r) ow.wire[r] = wire_by_rank[r];
   if (q.width % 16 != 0) return fail(VRHI_ERR_UNSUPPORTED, "widen (squeezed): the width must be a multiple of 16 pixels");
   const uint32_t stride = q.slab_stride ? q.slab_stride : 1u;
   const uint32_t nq = q.skip_rank < q.world ? q.world - 1 : q.world;
   const uint64_t total_rows = (uint64_t)q.slab_count * nq * q.chunk_rows;
   if (total_rows == 0) return VRHI_OK;
   if (total_rows > 0xffffffffull) return fail(VRHI_ERR_UNSUPPORTED, "widen: too many rows");
-  const uint64_t cap = (uint64_t)st->dev->prop.multiProcessorCount * 8;
+  const uint64_t cap = (uint64_t)st->dev->prop.multiProcessorCount * kWidenBlocksPerSm;
   const unsigned grid = (unsigned)(total_rows < cap ? total_rows : cap);
-  widen_rows_squeezed_kernel<<<grid, 256, 0, st->s>>>(bytes, wide, image, q.width, q.height, q.chunk_rows, q.world, q.skip_rank, q.slab_first, stride, (uint32_t)total_rows, ok);
+  widen_rows_squeezed_kernel<<<grid, 256, 0, st->s>>>(bytes, ow, image, q.width, q.height, q.chunk_rows, q.world, q.skip_rank, q.slab_first, stride, (uint32_t)total_rows, ok);
   return post_launch(st, "widen_rows_squeezed");
+}
+
+int launch_widen_rows_u8(vrhi_stream_t *st, const ArgView *args, int n_args, const void *params, size_t params_size) {
+  vrhi_widen_params q;
+  VRHI_TRY(read_params(params, params_size, &q));
+  if (q.world == 0 || q.world > VRHI_GATHER_MAX_WORLD) return fail(VRHI_ERR_INVALID, "widen_rows_u8: world must be 1..%d, got %u", VRHI_GATHER_MAX_WORLD, q.world);
+  if (n_args != (int)q.world + 2) return fail(VRHI_ERR_INVALID, "widen_rows_u8 takes the byte plane, the image and the %u ranks' wire images (%u arguments), got %d", q.world, q.world + 2, n_args);
+  if (!writable(args[1])) return fail(VRHI_ERR_INVALID, "widen_rows_u8: the image buffer is read-only (class %s)", vrhi_arg_class_name(args[1].buf_cls));
+  if (q.width == 0 || q.height == 0 || q.chunk_rows == 0) return fail(VRHI_ERR_SIZE, "widen_rows_u8: empty image or chunk");
+  const uint64_t px = (uint64_t)q.width * q.height;
+  if (args[0].bytes < px) return fail(VRHI_ERR_SIZE, "widen_rows_u8: the byte plane holds %llu bytes, %llu needed", (unsigned long long)args[0].bytes, (unsigned long long)px);
+  if (args[1].bytes < px * 4) return fail(VRHI_ERR_SIZE, "widen_rows_u8: the image view holds %llu bytes, %llu needed", (unsigned long long)args[1].bytes, (unsigned long long)(px * 4));
+  const uint16_t *by_rank[VRHI_GATHER_MAX_WORLD] = {};
+  for (uint32_t r = 0; r < q.world; ++r) {
+    if (args[2 + r].bytes < px * 2) return fail(VRHI_ERR_SIZE, "widen_rows_u8: the wire image of rank %u holds %llu bytes, %llu needed", r, (unsigned long long)args[2 + r].bytes, (unsigned long long)(px * 2));
+    by_rank[r] = reinterpret_cast<const uint16_t *>(args[2 + r].ptr);
+  }
+  const uint64_t n_chunks = ((uint64_t)q.height + q.chunk_rows - 1) / q.chunk_rows;
+  const uint64_t n_slabs = (n_chunks + q.world - 1) / q.world;
+  const uint32_t stride = q.slab_stride ? q.slab_stride : 1u;
+  if (q.slab_count && (uint64_t)q.slab_first + (uint64_t)(q.slab_count - 1) * stride >= n_slabs) return fail(VRHI_ERR_SIZE, "widen_rows_u8: slabs beyond the image");
+  return widen_rows_squeezed(st, reinterpret_cast<const uint8_t *>(args[0].ptr), by_rank, reinterpret_cast<uint32_t *>(args[1].ptr), q, nullptr);
 }
 
 // stores `seq` into slot `slot` of each of the n flag arrays (the peers')

@@ -59,7 +59,7 @@ int stream_arena(vrhi_stream_t *st, size_t payload, uint32_t **ctrl, char **payl
 }
 
 static const OpDef kOps[] = {
-    {"escape_time", "args: image(OUTPUT|IMAGE u32/u16/f32 [height][width])[, wire(OUTPUT|IMAGE u16 [height][width])]; params: vrhi_escape_params",
+    {"escape_time", "args: image(OUTPUT|IMAGE u32/u16/f32 [height][width])[, wire(OUTPUT|IMAGE u16 [height][width])[, bytes(OUTPUT|IMAGE u8 [height][width])]]; params: vrhi_escape_params",
      launch_escape_time},
     {"fused_map", "args: a,x,y(INPUT f32[n]), out(OUTPUT f32[n]); params: vrhi_map_params", launch_fused_map},
     {"map_tape", "args: inputs..., outputs...; params: vrhi_tape_params", launch_map_tape},
@@ -83,6 +83,8 @@ static const OpDef kOps[] = {
     {"flat_color", "args: color(UNIFORM f32[3]), fragments(IMAGE f32[n][4]); params: vrhi_map_params", launch_flat_color},
     {"widen_rows_u16", "args: wire(u16 [height][width]), image(OUTPUT|IMAGE u32 [height][width]); params: vrhi_widen_params",
      launch_widen_rows_u16},
+    {"widen_rows_u8", "args: bytes(u8 [height][width]), image(OUTPUT|IMAGE u32 [height][width]), the ranks' wire images (u16 [height][width]) in rank order; params: vrhi_widen_params",
+     launch_widen_rows_u8},
     {"gather_signal", "args: the peers' flag arrays (u32[world]); params: vrhi_gather_params", launch_gather_signal},
     {"gather_pull_u16", "args: flags(u32[world]), image(u32 [height][width]), the peers' wire images (u16 [height][width]) in rank order; params: vrhi_gather_params",
      launch_gather_pull_u16},

@@ -49,16 +49,22 @@ struct vrhi_group_t {
   bool ready;  // creation got as far as the ranks' first meeting: destruction meets again
 };
 
+constexpr uint32_t kMaxPending = 16;
+struct Pending {  // a published group whose transfer has not been enqueued yet
+  uint32_t slab_first, slab_count, stride, seq;
+};
+
 struct vrhi_exchange_t {
   vrhi_group_t *grp;
   vrhi_buffer_t *image;
   uint32_t width, height, chunk_rows, n_slabs;
   vrhi_buffer_t *wire[2];               // own wire images (uint16 [height][width]); two alternate from step to step
   uint16_t *peer_wire[2][kMaxWorld];    // the world-1 peers', starting with rank+1
-  // squeezed transfer (see k_gather.cu): counts cross as bytes, granules with large counts in full
+  // squeezed transfer (see k_gather.cu): counts cross as bytes, granules with large counts are fetched in full
   bool squeeze;
-  uint8_t *bytes[2];                    // own byte planes [height][width], alternating like the wire images
-  uint8_t *peer_bytes[2][kMaxWorld];
+  vrhi_buffer_t *bytes[2];              // own byte planes [height][width], alternating like the wire images
+  uint8_t *peer_bytes[2][kMaxWorld];    // the world-1 peers', starting with rank+1
+  const uint16_t *wire_by_rank[2][kMaxWorld];  // every rank's wire images, indexed by rank
   uint32_t *flags;                      // own flag array [world]
   uint32_t *peer_flags[kMaxWorld];
   vrhi_stream_t *push[kMaxWorld], *arrive;  // internal streams: one per peer for the transfers to it; waits and widening
@@ -66,6 +72,9 @@ struct vrhi_exchange_t {
   cudaEvent_t ev_compute, ev_push[kMaxWorld], ev_arrive;
   uint32_t cur, seq;
   uint64_t steps;
+  Pending pending[kMaxPending];
+  cudaEvent_t ev_group[kMaxPending];    // the point of the compute stream each pending group was published at
+  uint32_t n_pending;
   std::vector<void *> *opened;          // IPC mappings of the peers' wire images and flags
   bool ready;
   // VRHI_EXCHANGE_TRACE=1: timed events behind each group's transfer and widening, printed by vrhi_exchange_check
@@ -132,14 +141,14 @@ bool use_copy_engines() {
   return v;
 }
 
-// Whether the counts cross NVLink squeezed to bytes.  It pays where the step is bound by the transfer,
-// not by the arithmetic: from five ranks on by default (at eight ranks each GPU takes in 7/8 of the
-// image every step); VRHI_EXCHANGE_SQUEEZE=0/1 overrides.  The squeezing push is a kernel, so it
-// replaces the copy engines where it is on.
+// Whether the counts cross NVLink squeezed to bytes (see k_gather.cu): half the bytes for the copy engines
+// to move, one more store per pixel for the escape-time kernel.  On by default from three ranks on,
+// where the transfer is as long as the arithmetic or longer (at eight ranks each GPU takes in 7/8 of
+// the image every step); VRHI_EXCHANGE_SQUEEZE=0/1 overrides.
 bool use_squeeze(uint32_t world, uint32_t width) {
   static const int v = env_int("VRHI_EXCHANGE_SQUEEZE", 0, 1, -1);
   if (width % 16) return false;
-  return v < 0 ? world >= 5 : v == 1;
+  return v < 0 ? world >= 3 : v == 1;
 }
 
 // Ranks meet here: one round of the caller's all-gather.
@@ -151,11 +160,13 @@ int meet(vrhi_group_t *g) {
   return VRHI_OK;
 }
 
-int make_stream(vrhi_device_t *dev, vrhi_stream_t **out) {
+// high_priority: blocks of the stream go first when an SM has room (the one-warp flag kernels behind the
+// transfers); the widening kernels run at normal priority, behind the escape-time launches they share the GPU with
+int make_stream(vrhi_device_t *dev, vrhi_stream_t **out, bool high_priority) {
   int lo = 0, hi = 0;
   VRHI_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
   cudaStream_t s;
-  VRHI_CUDA(cudaStreamCreateWithPriority(&s, cudaStreamNonBlocking, hi));  // blocks of these streams go first when an SM has room
+  VRHI_CUDA(cudaStreamCreateWithPriority(&s, cudaStreamNonBlocking, high_priority ? hi : lo));
   vrhi_stream_t *st = new (std::nothrow) vrhi_stream_t{dev, s, true, nullptr, 0, 0};
   if (!st) {
     cudaStreamDestroy(s);
@@ -302,11 +313,9 @@ int vrhi_exchange_create(vrhi_group g, vrhi_buffer image, uint32_t width, uint32
   }
   void *by_rank[kMaxWorld];
   for (int b = 0; b < 2 && ex->squeeze; ++b) {
-    void *p = nullptr;
-    cudaError_t e = cudaMalloc(&p, px);
-    if (e != cudaSuccess) { (void)cudaGetLastError(); return cleanup(fail(VRHI_ERR_OOM, "cudaMalloc of the exchange's byte plane failed: %s", cudaGetErrorString(e))); }
-    ex->bytes[b] = static_cast<uint8_t *>(p);
-    int rc = share(g, p, by_rank, ex->opened);
+    int rc = vrhi_buffer_create(g->dev, px, VRHI_IMAGE, &ex->bytes[b]);
+    if (rc != VRHI_OK) return cleanup(rc);
+    rc = share(g, ex->bytes[b]->ptr, by_rank, ex->opened);
     if (rc != VRHI_OK) return cleanup(rc);
     for (uint32_t k = 0; k + 1 < g->world; ++k) ex->peer_bytes[b][k] = static_cast<uint8_t *>(by_rank[(g->rank + 1 + k) % g->world]);
   }
@@ -315,6 +324,7 @@ int vrhi_exchange_create(vrhi_group g, vrhi_buffer image, uint32_t width, uint32
     if (rc != VRHI_OK) return cleanup(rc);
     // start with the next rank so that, at any moment, the ranks store to different peers
     for (uint32_t k = 0; k + 1 < g->world; ++k) ex->peer_wire[b][k] = static_cast<uint16_t *>(by_rank[(g->rank + 1 + k) % g->world]);
+    for (uint32_t r = 0; r < g->world; ++r) ex->wire_by_rank[b][r] = static_cast<const uint16_t *>(by_rank[r]);
   }
   {
     int rc = share(g, ex->flags, by_rank, ex->opened);
@@ -323,11 +333,14 @@ int vrhi_exchange_create(vrhi_group g, vrhi_buffer image, uint32_t width, uint32
   }
   // copy engines: a stream per peer, so that the transfers to different peers run on different engines at once;
   // the storing kernel serves all peers from one launch and needs one stream
-  static const bool one_stream = [] { const char *e = getenv("VRHI_PUSH_STREAMS"); return e && atoi(e) == 1; }();  // comparison aid
-  ex->n_push = use_copy_engines() && !ex->squeeze && g->world > 2 && !one_stream ? g->world - 1 : 1;
+  // One stream carries the copies to all peers, one after the other (every rank starts with its next neighbour, so at
+  // any moment the ranks send to different peers).  A stream per peer (VRHI_PUSH_STREAMS=0) measured the same at four
+  // ranks and costs three times the driver calls.
+  static const bool per_peer = env_int("VRHI_PUSH_STREAMS", 0, 1, 1) == 0;  // comparison aid
+  ex->n_push = per_peer && g->world > 2 ? g->world - 1 : 1;
   int rc = VRHI_OK;
-  for (uint32_t k = 0; k < ex->n_push && rc == VRHI_OK; ++k) rc = make_stream(g->dev, &ex->push[k]);
-  if (rc == VRHI_OK) rc = make_stream(g->dev, &ex->arrive);
+  for (uint32_t k = 0; k < ex->n_push && rc == VRHI_OK; ++k) rc = make_stream(g->dev, &ex->push[k], true);
+  if (rc == VRHI_OK) rc = make_stream(g->dev, &ex->arrive, false);
   if (rc != VRHI_OK) return cleanup(rc);
   uint32_t *ctrl = nullptr;
   rc = stream_arena(ex->arrive, 0, &ctrl, nullptr);  // the waits' status word: allocate now, not inside a step
@@ -337,6 +350,8 @@ int vrhi_exchange_create(vrhi_group g, vrhi_buffer image, uint32_t width, uint32
     return cleanup(fail(VRHI_ERR_CUDA, "cudaEventCreate failed"));
   for (uint32_t k = 0; k < ex->n_push; ++k)
     if (cudaEventCreateWithFlags(&ex->ev_push[k], cudaEventDisableTiming) != cudaSuccess) return cleanup(fail(VRHI_ERR_CUDA, "cudaEventCreate failed"));
+  for (uint32_t k = 0; k < kMaxPending; ++k)
+    if (cudaEventCreateWithFlags(&ex->ev_group[k], cudaEventDisableTiming) != cudaSuccess) return cleanup(fail(VRHI_ERR_CUDA, "cudaEventCreate failed"));
   if (cudaDeviceSynchronize() != cudaSuccess) return cleanup(fail(VRHI_ERR_CUDA, "cudaDeviceSynchronize failed"));
   ex->ready = true;
   rc = meet(g);  // every rank has zeroed its flags before anybody raises one
@@ -355,6 +370,8 @@ int vrhi_exchange_destroy(vrhi_exchange ex) {
   if (ex->ev_compute) cudaEventDestroy(ex->ev_compute);
   for (uint32_t k = 0; k < kMaxWorld; ++k)
     if (ex->ev_push[k]) cudaEventDestroy(ex->ev_push[k]);
+  for (uint32_t k = 0; k < kMaxPending; ++k)
+    if (ex->ev_group[k]) cudaEventDestroy(ex->ev_group[k]);
   if (ex->ev_arrive) cudaEventDestroy(ex->ev_arrive);
   if (ex->trace) {
     cudaEventDestroy(ex->t_done);
@@ -366,18 +383,75 @@ int vrhi_exchange_destroy(vrhi_exchange ex) {
   // a rank's wire images must outlive every other rank's mapping of them
   int rc = ex->ready ? meet(ex->grp) : VRHI_OK;
   for (int b = 0; b < 2; ++b) vrhi_buffer_destroy(ex->wire[b]);
-  for (int b = 0; b < 2; ++b)
-    if (ex->bytes[b]) cudaFree(ex->bytes[b]);
+  for (int b = 0; b < 2; ++b) vrhi_buffer_destroy(ex->bytes[b]);
   if (ex->flags) cudaFree(ex->flags);
   delete ex;
   return rc;
 }
 
-int vrhi_exchange_wire(vrhi_exchange ex, vrhi_buffer *out_wire) {
-  if (!ex || !out_wire) return fail(VRHI_ERR_INVALID, "NULL argument");
+int vrhi_exchange_planes(vrhi_exchange ex, vrhi_buffer *out_wire, vrhi_buffer *out_bytes) {
+  if (!ex || !out_wire || !out_bytes) return fail(VRHI_ERR_INVALID, "NULL argument");
   *out_wire = ex->wire[ex->cur];
+  *out_bytes = ex->squeeze ? ex->bytes[ex->cur] : nullptr;
   return VRHI_OK;
 }
+
+}  // extern "C" (reopened below)
+
+namespace {
+
+// Enqueue the transfer and the arrival of every group published since the last flush, in order.
+int flush_pending(vrhi_exchange_t *ex) {
+  vrhi_group_t *g = ex->grp;
+  for (uint32_t i = 0; i < ex->n_pending; ++i) {
+    const Pending &pd = ex->pending[i];
+    const uint32_t slab_first = pd.slab_first, slab_count = pd.slab_count, stride = pd.stride, seq = pd.seq;
+    cudaEvent_t ev = ex->ev_group[i];
+    const bool mark = ex->trace && ex->n_marks < 16;
+    // sending side, behind the launches that computed these slabs
+    for (uint32_t k = 0; k < ex->n_push; ++k) VRHI_CUDA(cudaStreamWaitEvent(ex->push[k]->s, ev, 0));
+    if (ex->squeeze || use_copy_engines()) {
+      // the rank's rows by the copy engines, one strided copy per peer, and the peers' flags behind them.  Squeezing:
+      // rows of the byte plane (the receiving side fetches what a byte cannot hold from this rank's uint16 wire image)
+      const uint64_t elem = ex->squeeze ? 1 : 2;
+      const uint64_t chunk_bytes = (uint64_t)ex->chunk_rows * ex->width * elem;
+      const uint64_t offset = ((uint64_t)slab_first * g->world + g->rank) * chunk_bytes, pitch = (uint64_t)g->world * stride * chunk_bytes;
+      const char *src = static_cast<const char *>(ex->squeeze ? ex->bytes[ex->cur]->ptr : ex->wire[ex->cur]->ptr) + offset;
+      for (uint32_t k = 0; k + 1 < g->world; ++k) {
+        vrhi_stream_t *ps = ex->push[ex->n_push > 1 ? k : 0];
+        char *dst = (ex->squeeze ? reinterpret_cast<char *>(ex->peer_bytes[ex->cur][k]) : reinterpret_cast<char *>(ex->peer_wire[ex->cur][k])) + offset;
+        VRHI_CUDA(cudaMemcpy2DAsync(dst, pitch, src, pitch, chunk_bytes, slab_count, cudaMemcpyDeviceToDevice, ps->s));
+        if (ex->n_push > 1) VRHI_TRY(gather_signal(ps, &ex->peer_flags[k], 1, g->rank, seq));
+      }
+      if (ex->n_push == 1) VRHI_TRY(gather_signal(ex->push[0], ex->peer_flags, g->world - 1, g->rank, seq));
+    } else {
+      vrhi_gather_params q{};
+      q.size = sizeof q; q.width = ex->width; q.height = ex->height; q.chunk_rows = ex->chunk_rows; q.world = g->world; q.rank = g->rank;
+      q.slab_first = slab_first; q.slab_count = slab_count; q.slab_stride = stride; q.seq = seq; q.wait_ms = g->wait_ms;
+      VRHI_TRY(gather_push_u16(ex->push[0], ex->peer_wire[ex->cur], g->world - 1, static_cast<const uint16_t *>(ex->wire[ex->cur]->ptr), q));
+      VRHI_TRY(gather_signal(ex->push[0], ex->peer_flags, g->world - 1, g->rank, seq));
+    }
+    if (mark) VRHI_CUDA(cudaEventRecord(ex->t_pushed[ex->n_marks], ex->push[ex->n_push - 1]->s));
+    // receiving side: when every peer's rows of this group have landed, widen them into the image; ordered
+    // behind the caller's stream as well, so that what it enqueued before the publish (a download of the
+    // previous step's image, say) is done with the image before a fast peer's rows are widened into it
+    VRHI_CUDA(cudaStreamWaitEvent(ex->arrive->s, ev, 0));
+    const uint32_t *ok = nullptr;
+    VRHI_TRY(gather_wait(ex->arrive, ex->flags, g->world, g->rank, seq, g->wait_ms, &ok));
+    vrhi_widen_params w{};
+    w.size = sizeof w; w.width = ex->width; w.height = ex->height; w.chunk_rows = ex->chunk_rows; w.world = g->world; w.skip_rank = g->rank;
+    w.slab_first = slab_first; w.slab_count = slab_count; w.slab_stride = stride;
+    if (ex->squeeze) VRHI_TRY(widen_rows_squeezed(ex->arrive, static_cast<const uint8_t *>(ex->bytes[ex->cur]->ptr), ex->wire_by_rank[ex->cur], static_cast<uint32_t *>(ex->image->ptr), w, ok));
+    else VRHI_TRY(widen_rows_u16(ex->arrive, static_cast<const uint16_t *>(ex->wire[ex->cur]->ptr), static_cast<uint32_t *>(ex->image->ptr), w, ok));
+    if (mark) VRHI_CUDA(cudaEventRecord(ex->t_widened[ex->n_marks++], ex->arrive->s));
+  }
+  ex->n_pending = 0;
+  return VRHI_OK;
+}
+
+}  // namespace
+
+extern "C" {
 
 int vrhi_exchange_publish(vrhi_exchange ex, vrhi_stream compute, uint32_t slab_first, uint32_t slab_count, uint32_t slab_stride) {
   if (!ex || !compute) return fail(VRHI_ERR_INVALID, "NULL argument");
@@ -388,46 +462,16 @@ int vrhi_exchange_publish(vrhi_exchange ex, vrhi_stream compute, uint32_t slab_f
   if ((uint64_t)slab_first + (uint64_t)(slab_count - 1) * stride >= ex->n_slabs) return fail(VRHI_ERR_SIZE, "slabs %u + k*%u, k < %u, reach beyond the image's %u", slab_first, stride, slab_count, ex->n_slabs);
   if (g->world == 1) return VRHI_OK;
   VRHI_TRY(set_dev(g->dev));
-  const uint32_t seq = ++ex->seq;
-  vrhi_gather_params q{};
-  q.size = sizeof q; q.width = ex->width; q.height = ex->height; q.chunk_rows = ex->chunk_rows; q.world = g->world; q.rank = g->rank;
-  q.slab_first = slab_first; q.slab_count = slab_count; q.slab_stride = stride; q.seq = seq; q.wait_ms = g->wait_ms;
-  const bool mark = ex->trace && ex->n_marks < 16;
-  if (mark) VRHI_CUDA(cudaEventRecord(ex->t_computed[ex->n_marks], compute->s));
-  // sending side, behind the launches that computed these slabs
-  VRHI_CUDA(cudaEventRecord(ex->ev_compute, compute->s));
-  for (uint32_t k = 0; k < ex->n_push; ++k) VRHI_CUDA(cudaStreamWaitEvent(ex->push[k]->s, ex->ev_compute, 0));
-  if (ex->squeeze) {
-    VRHI_TRY(gather_push_squeezed(ex->push[0], ex->peer_bytes[ex->cur], ex->peer_wire[ex->cur], g->world - 1, static_cast<const uint16_t *>(ex->wire[ex->cur]->ptr), q));
-    VRHI_TRY(gather_signal(ex->push[0], ex->peer_flags, g->world - 1, g->rank, seq));
-  } else if (use_copy_engines()) {
-    // one strided device-to-device copy per peer, then that peer's flag, each peer on its own stream where there are several
-    const uint64_t chunk_bytes = (uint64_t)ex->chunk_rows * ex->width * 2;
-    const uint64_t offset = ((uint64_t)slab_first * g->world + g->rank) * chunk_bytes, pitch = (uint64_t)g->world * stride * chunk_bytes;
-    const char *src = static_cast<const char *>(ex->wire[ex->cur]->ptr) + offset;
-    for (uint32_t k = 0; k + 1 < g->world; ++k) {
-      vrhi_stream_t *ps = ex->push[ex->n_push > 1 ? k : 0];
-      VRHI_CUDA(cudaMemcpy2DAsync(reinterpret_cast<char *>(ex->peer_wire[ex->cur][k]) + offset, pitch, src, pitch, chunk_bytes, slab_count, cudaMemcpyDeviceToDevice, ps->s));
-      if (ex->n_push > 1) VRHI_TRY(gather_signal(ps, &ex->peer_flags[k], 1, g->rank, seq));
-    }
-    if (ex->n_push == 1) VRHI_TRY(gather_signal(ex->push[0], ex->peer_flags, g->world - 1, g->rank, seq));
-  } else {
-    VRHI_TRY(gather_push_u16(ex->push[0], ex->peer_wire[ex->cur], g->world - 1, static_cast<const uint16_t *>(ex->wire[ex->cur]->ptr), q));
-    VRHI_TRY(gather_signal(ex->push[0], ex->peer_flags, g->world - 1, g->rank, seq));
-  }
-  if (mark) VRHI_CUDA(cudaEventRecord(ex->t_pushed[ex->n_marks], ex->push[ex->n_push - 1]->s));
-  // receiving side: when every peer's rows of this group have landed, widen them into the image; ordered
-  // behind the caller's stream as well, so that what it enqueued before this call (a download of the
-  // previous step's image, say) is done with the image before a fast peer's rows are widened into it
-  VRHI_CUDA(cudaStreamWaitEvent(ex->arrive->s, ex->ev_compute, 0));
-  const uint32_t *ok = nullptr;
-  VRHI_TRY(gather_wait(ex->arrive, ex->flags, g->world, g->rank, seq, g->wait_ms, &ok));
-  vrhi_widen_params w{};
-  w.size = sizeof w; w.width = ex->width; w.height = ex->height; w.chunk_rows = ex->chunk_rows; w.world = g->world; w.skip_rank = g->rank;
-  w.slab_first = slab_first; w.slab_count = slab_count; w.slab_stride = stride;
-  if (ex->squeeze) VRHI_TRY(widen_rows_squeezed(ex->arrive, ex->bytes[ex->cur], static_cast<const uint16_t *>(ex->wire[ex->cur]->ptr), static_cast<uint32_t *>(ex->image->ptr), w, ok));
-  else VRHI_TRY(widen_rows_u16(ex->arrive, static_cast<const uint16_t *>(ex->wire[ex->cur]->ptr), static_cast<uint32_t *>(ex->image->ptr), w, ok));
-  if (mark) VRHI_CUDA(cudaEventRecord(ex->t_widened[ex->n_marks++], ex->arrive->s));
+  // Only the point of the compute stream is recorded here, so that the caller's next launch is not held
+  // up by the dozen driver calls a group's transfer takes (with seven peers they cost more host time than a
+  // group of an eighth of the image takes to compute); the transfer itself is enqueued by the next call that
+  // is not a publish (complete, check, destroy), or when kMaxPending groups have gathered.
+  if (ex->n_pending == kMaxPending) VRHI_TRY(flush_pending(ex));
+  Pending &pd = ex->pending[ex->n_pending];
+  VRHI_CUDA(cudaEventRecord(ex->ev_group[ex->n_pending], compute->s));
+  pd.slab_first = slab_first; pd.slab_count = slab_count; pd.stride = stride; pd.seq = ++ex->seq;
+  if (ex->trace && ex->n_marks + ex->n_pending < 16) VRHI_CUDA(cudaEventRecord(ex->t_computed[ex->n_marks + ex->n_pending], compute->s));
+  ++ex->n_pending;
   return VRHI_OK;
 }
 
@@ -437,6 +481,7 @@ int vrhi_exchange_complete(vrhi_exchange ex, vrhi_stream stream) {
   ex->steps++;
   if (ex->grp->world == 1) return VRHI_OK;
   VRHI_TRY(set_dev(ex->grp->dev));
+  VRHI_TRY(flush_pending(ex));
   VRHI_CUDA(cudaEventRecord(ex->ev_arrive, ex->arrive->s));
   VRHI_CUDA(cudaStreamWaitEvent(stream->s, ex->ev_arrive, 0));
   for (uint32_t k = 0; k < ex->n_push; ++k) {
@@ -455,6 +500,8 @@ int vrhi_exchange_complete(vrhi_exchange ex, vrhi_stream stream) {
 int vrhi_exchange_check(vrhi_exchange ex) {
   if (!ex) return fail(VRHI_ERR_INVALID, "NULL exchange");
   if (ex->grp->world == 1) return VRHI_OK;
+  VRHI_TRY(set_dev(ex->grp->dev));
+  VRHI_TRY(flush_pending(ex));
   for (uint32_t k = 0; k < ex->n_push; ++k) VRHI_TRY(vrhi_stream_synchronize(ex->push[k]));
   int rc = vrhi_stream_check(ex->arrive);
   if (ex->trace && ex->last_marks && cudaEventSynchronize(ex->t_done) == cudaSuccess) {

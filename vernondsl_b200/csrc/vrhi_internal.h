@@ -124,15 +124,14 @@ int launch_fp32_probe(vrhi_stream_t *, const ArgView *, int, const void *, size_
 int launch_vertex_transform(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
 int launch_flat_color(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
 int launch_widen_rows_u16(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
+int launch_widen_rows_u8(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
 int launch_gather_signal(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
 int launch_gather_pull_u16(vrhi_stream_t *, const ArgView *, int, const void *, size_t);
 
 // Pieces of the image gather and of the small all-reduce (k_gather.cu), used by vrhi_group.cu.
 int widen_rows_u16(vrhi_stream_t *st, const uint16_t *wire, uint32_t *image, const vrhi_widen_params &q, const uint32_t *ok);
 int gather_push_u16(vrhi_stream_t *st, uint16_t *const *peer_wires, uint32_t n_peers, const uint16_t *wire, const vrhi_gather_params &q);
-int gather_push_squeezed(vrhi_stream_t *st, uint8_t *const *peer_bytes, uint16_t *const *peer_wide, uint32_t n_peers, const uint16_t *wire,
-                         const vrhi_gather_params &q);
-int widen_rows_squeezed(vrhi_stream_t *st, const uint8_t *bytes, const uint16_t *wide, uint32_t *image, const vrhi_widen_params &q, const uint32_t *ok);
+int widen_rows_squeezed(vrhi_stream_t *st, const uint8_t *bytes, const uint16_t *const *wire_by_rank, uint32_t *image, const vrhi_widen_params &q, const uint32_t *ok);
 int gather_signal(vrhi_stream_t *st, uint32_t *const *peer_flags, uint32_t n, uint32_t slot, uint32_t seq);
 int gather_wait(vrhi_stream_t *st, const uint32_t *flags, uint32_t world, uint32_t rank, uint32_t seq, uint32_t wait_ms, const uint32_t **ok);
 int box_scatter(vrhi_stream_t *st, float *const *boxes, uint32_t world, uint32_t rank, const float *src, uint32_t n, uint32_t capacity);

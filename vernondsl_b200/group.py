@@ -92,11 +92,14 @@ class Exchange:
         self._h = h
 
     @property
-    def wire(self) -> Buffer:
-        """The uint16 wire image this step's ``escape_time`` launches write beside the image."""
-        h = C.c_void_p()
-        check(lib().vrhi_exchange_wire(self._h, C.byref(h)))
-        return _Borrowed(self.group.dev, h, self.width * self.height * 2, L.IMAGE)
+    def planes(self):
+        """``(wire, bytes)``: the uint16 wire image and the byte plane this step's ``escape_time`` launches write
+        beside the image (``ops.escape_time(..., wire=wire, byte_plane=bytes)``); ``bytes`` is None where the
+        exchange does not squeeze the counts."""
+        w, b = C.c_void_p(), C.c_void_p()
+        check(lib().vrhi_exchange_planes(self._h, C.byref(w), C.byref(b)))
+        n = self.width * self.height
+        return (_Borrowed(self.group.dev, w, 2 * n, L.IMAGE), _Borrowed(self.group.dev, b, n, L.IMAGE) if b.value else None)
 
     def publish(self, compute_stream: Stream, slabs) -> None:
         """``slabs`` = (first, count, stride): the slabs the launches enqueued on ``compute_stream`` computed."""

@@ -68,12 +68,16 @@ def escape_params(kind: int, width: int, height: int, x0: float, y0: float, dx: 
     return p
 
 
-def escape_time(stream: Stream, image: Buffer, params: L.EscapeParams, wire: Optional[Buffer] = None) -> None:
+def escape_time(stream: Stream, image: Buffer, params: L.EscapeParams, wire: Optional[Buffer] = None,
+                byte_plane: Optional[Buffer] = None) -> None:
     """Launch the escape-time map (the per-pixel loop of fractal.py:18-25) into ``image``.  ``wire``,
-    a uint16 image of the same geometry, receives every count a second time (the form sent to peers)."""
+    a uint16 image of the same geometry, receives every count a second time (the form sent to peers);
+    ``byte_plane`` (with ``wire``), a uint8 plane, receives min(count, 255)."""
     args = [image.arg(L.IMAGE if image.arg_class == L.IMAGE else L.OUTPUT)]
     if wire is not None:
         args.append(wire.arg(L.IMAGE if wire.arg_class == L.IMAGE else L.OUTPUT))
+        if byte_plane is not None:
+            args.append(byte_plane.arg(L.IMAGE if byte_plane.arg_class == L.IMAGE else L.OUTPUT))
     launch(stream, "escape_time", args, params)
 
 
@@ -86,6 +90,17 @@ def widen_rows_u16(stream: Stream, wire: Buffer, image: Buffer, width: int, heig
     p.width, p.height, p.chunk_rows, p.world = int(width), int(height), int(chunk_rows), int(world)
     p.skip_rank, p.slab_first, p.slab_count, p.slab_stride = int(skip_rank), int(slab_first), int(slab_count), int(slab_stride)
     launch(stream, "widen_rows_u16", [wire.arg(), image.arg(L.IMAGE if image.arg_class == L.IMAGE else L.OUTPUT)], p)
+
+
+def widen_rows_u8(stream: Stream, byte_plane: Buffer, image: Buffer, wires: Sequence[Buffer], width: int, height: int, chunk_rows: int,
+                  world: int, skip_rank: int, slab_first: int, slab_count: int, slab_stride: int = 1) -> None:
+    """Byte plane -> uint32 image for the given slabs; granules showing a byte of 255 come from ``wires[owner]``."""
+    p = L.WidenParams()
+    p.size = C.sizeof(L.WidenParams)
+    p.width, p.height, p.chunk_rows, p.world, p.skip_rank = int(width), int(height), int(chunk_rows), int(world), int(skip_rank)
+    p.slab_first, p.slab_count, p.slab_stride = int(slab_first), int(slab_count), int(slab_stride)
+    launch(stream, "widen_rows_u8", [byte_plane.arg(L.INPUT), image.arg(L.IMAGE if image.arg_class == L.IMAGE else L.OUTPUT)] +
+           [w.arg(L.INPUT) for w in wires], p)
 
 
 def gather_signal(stream: Stream, peer_flags: Sequence[Buffer], world: int, rank: int, seq: int) -> None:

@@ -793,7 +793,9 @@ def main():
     # launch computes.  The step ends when the last gather has finished.
     # launches per step; finished slabs are exchanged while the next launch computes.  More groups shorten the last,
     # exposed push; every launch adds ramp-up and drain, most of which the two alternating compute streams hide.
-    GROUPS = int(os.environ.get("VRHI_BENCH_GROUPS", "4"))
+    # measured on B200 (ms per step): 2 ranks 1.35 with 6 groups (1.36 with 4); 4 ranks 1.02 with 4 (1.03 with 6, 1.05 with 3);
+    # 8 ranks 1.11 with 2 (1.17 with 4): with seven peers a group's seven copies want to be large
+    GROUPS = int(os.environ.get("VRHI_BENCH_GROUPS", "6" if world <= 2 else "4" if world <= 4 else "2"))
     COMM_STREAMS = 2 if (os.environ.get("VRHI_BENCH_COMM_STREAMS", "1") == "2" and world > 2) else 1   # pushes to odd and even peers on two streams
     # Group g takes slabs g, g+GROUPS, g+2*GROUPS, ...: every group is a thin comb over the whole image, so the
     # groups cost the same although the rows near the set cost far more than the rows at the edges.

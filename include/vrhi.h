@@ -448,7 +448,9 @@ VRHI_API int vrhi_partition_leading(uint64_t n, uint32_t world, uint32_t rank, u
  *
  * vrhi_allgather_fn: `send` holds `bytes` bytes of this rank; on return `recv` holds world*bytes
  * bytes, rank r's record at offset r*bytes.  Returns 0 on success.  Every rank calls the creating
- * functions in the same order, so the all-gathers match up. */
+ * (and destroying) functions in the same order, so the all-gathers match up; it should carry a time
+ * limit of its own, because a rank whose creation fails half way (VRHI_ERR_PEER: a peer's memory
+ * cannot be mapped) leaves the others waiting in it. */
 typedef int (*vrhi_allgather_fn)(void *user, const void *send, void *recv, uint64_t bytes);
 #define VRHI_GROUP_MAX_WORLD 8
 VRHI_API int vrhi_group_create(vrhi_device dev, uint32_t world, uint32_t rank, vrhi_allgather_fn allgather, void *user,

@@ -69,7 +69,7 @@ struct vrhi_exchange_t {
   uint32_t *peer_flags[kMaxWorld];
   vrhi_stream_t *push[kMaxWorld], *arrive;  // internal streams: one per peer for the transfers to it; waits and widening
   uint32_t n_push;
-  cudaEvent_t ev_compute, ev_push[kMaxWorld], ev_arrive;
+  cudaEvent_t ev_push[kMaxWorld], ev_arrive;
   uint32_t cur, seq;
   uint64_t steps;
   Pending pending[kMaxPending];
@@ -133,9 +133,10 @@ int share(vrhi_group_t *g, void *local, void **by_rank, std::vector<void *> *ope
   return VRHI_OK;
 }
 
-// How a rank's rows reach its peers: by the copy engines (default: they move the data without
-// occupying SMs; measured at two ranks on the 16384^2 Julia image, 1.39 ms per step against 1.48 ms)
-// or, with VRHI_PUSH_COPY_ENGINE=0, by a small storing kernel beside the next group's compute.
+// How a rank's uint16 rows reach its peers where the counts are not squeezed: by the copy engines
+// (default: they move the data without occupying SMs; measured at two ranks on the 16384^2 Julia
+// image, 1.39 ms per step against 1.48 ms) or, with VRHI_PUSH_COPY_ENGINE=0, by a small storing
+// kernel beside the next group's compute (kept for comparison).
 bool use_copy_engines() {
   static const bool v = [] { const char *e = getenv("VRHI_PUSH_COPY_ENGINE"); return !e || atoi(e) != 0; }();
   return v;
@@ -345,8 +346,7 @@ int vrhi_exchange_create(vrhi_group g, vrhi_buffer image, uint32_t width, uint32
   uint32_t *ctrl = nullptr;
   rc = stream_arena(ex->arrive, 0, &ctrl, nullptr);  // the waits' status word: allocate now, not inside a step
   if (rc != VRHI_OK) return cleanup(rc);
-  if (cudaEventCreateWithFlags(&ex->ev_compute, cudaEventDisableTiming) != cudaSuccess ||
-      cudaEventCreateWithFlags(&ex->ev_arrive, cudaEventDisableTiming) != cudaSuccess)
+  if (cudaEventCreateWithFlags(&ex->ev_arrive, cudaEventDisableTiming) != cudaSuccess)
     return cleanup(fail(VRHI_ERR_CUDA, "cudaEventCreate failed"));
   for (uint32_t k = 0; k < ex->n_push; ++k)
     if (cudaEventCreateWithFlags(&ex->ev_push[k], cudaEventDisableTiming) != cudaSuccess) return cleanup(fail(VRHI_ERR_CUDA, "cudaEventCreate failed"));
@@ -367,7 +367,6 @@ int vrhi_exchange_destroy(vrhi_exchange ex) {
   for (uint32_t k = 0; k < kMaxWorld; ++k)
     if (ex->push[k]) vrhi_stream_destroy(ex->push[k]);
   if (ex->arrive) vrhi_stream_destroy(ex->arrive);
-  if (ex->ev_compute) cudaEventDestroy(ex->ev_compute);
   for (uint32_t k = 0; k < kMaxWorld; ++k)
     if (ex->ev_push[k]) cudaEventDestroy(ex->ev_push[k]);
   for (uint32_t k = 0; k < kMaxPending; ++k)

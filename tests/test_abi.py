@@ -134,3 +134,41 @@ def test_struct_layouts_match_the_header():
     assert C.sizeof(L.TapeParams) == 4 * 4 + 16 + 12 + 16 + 12 * 64 + 4 + 4 + 4  # flags, colsum_mask, trailing pad to 8
     assert C.sizeof(L.RowPartition) == 24
 
+
+
+def test_group_and_exchange_entry_points_reject_null_handles_without_a_device():
+    """The multi-GPU entry points validate their handles before they touch CUDA: NULL is an error for
+    everything that uses a group or an exchange, and accepted (ignored) by the destroying functions."""
+    lib = L.lib()
+    out = C.c_void_p()
+    null_cb = C.cast(None, L.ALLGATHER_FN)
+    assert lib.vrhi_group_create(None, 2, 0, null_cb, None, C.byref(out)) == L.ERR_INVALID
+    assert lib.vrhi_group_destroy(None) == L.OK
+    assert lib.vrhi_exchange_destroy(None) == L.OK
+    assert lib.vrhi_group_info(None, None, None) == L.ERR_INVALID
+    assert lib.vrhi_group_set_wait_ms(None, 10) == L.ERR_INVALID
+    assert lib.vrhi_group_all_reduce_sum_f32(None, None, 0, 1, None) == L.ERR_INVALID
+    assert lib.vrhi_exchange_create(None, None, 16, 16, 1, C.byref(out)) == L.ERR_INVALID
+    assert lib.vrhi_exchange_planes(None, None, None) == L.ERR_INVALID
+    assert lib.vrhi_exchange_publish(None, None, 0, 1, 1) == L.ERR_INVALID
+    assert lib.vrhi_exchange_complete(None, None) == L.ERR_INVALID
+    assert lib.vrhi_exchange_check(None) == L.ERR_INVALID
+    assert lib.vrhi_exchange_launch_count(None, None) == L.ERR_INVALID
+    assert b"NULL" in lib.vrhi_last_error()
+
+
+def test_the_header_is_valid_c_and_declares_what_the_library_exports(tmp_path):
+    """include/vrhi.h compiles as C11 with warnings as errors, and every VRHI_API function it declares is a
+    symbol of libvrhi.so (the binding table of the Python package is checked against the library elsewhere;
+    this checks the header against the binding table)."""
+    import re
+    import subprocess
+
+    header = os.path.join(ROOT, "include", "vrhi.h")
+    src = tmp_path / "probe.c"
+    src.write_text('#include "vrhi.h"\nint main(void) { return (int)sizeof(vrhi_escape_params) == 0; }\n')
+    out = subprocess.run(["gcc", "-std=c11", "-Wall", "-Wextra", "-Werror", "-pedantic", "-I", os.path.dirname(header), "-c", str(src), "-o",
+                          str(tmp_path / "probe.o")], capture_output=True, text=True)
+    assert out.returncode == 0, out.stderr
+    declared = set(re.findall(r"VRHI_API\s+[^;(]*?\b(vrhi_\w+)\s*\(", open(header).read()))
+    assert declared and declared == set(L.PROTOTYPES), (declared ^ set(L.PROTOTYPES))

@@ -155,11 +155,13 @@ int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const
   const uint32_t tile_px = pair ? 64u : 32u;  // pixels a warp takes in per intake trip
   p.tiles_per_row = (q.width + tile_px - 1) / tile_px;
   {
-    // batch = unit of work stealing: 512 pixels of one row for large images; small images get smaller
-    // batches so that every resident warp still sees several of them and the tail stays short
+    // batch = unit of work stealing: 1024 pixels of one row for large images (with the rows visited from the
+    // middle outwards the last batches are the cheapest, so large batches cost no tail: 2.164 ms with 512
+    // pixels, 2.145 ms with 1024 on the 16384^2 image); small images get smaller batches so that every
+    // resident warp still sees several of them
     const uint64_t resident_warps = (uint64_t)sms * 48;
     const uint64_t tiles = (uint64_t)p.tiles_per_row * p.rows_owned;
-    const uint64_t most = 512 / tile_px;
+    const uint64_t most = 1024 / tile_px;
     uint64_t bt = tiles / (resident_warps * 8);
     const uint64_t least = pair ? 1 : 2;
     p.batch_tiles = (uint32_t)(bt < least ? least : bt > most ? most : bt);
@@ -192,14 +194,16 @@ int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const
     // computed group by group, frames of a sequence): with 2 blocks per SM and no pinning the blocks of the next
     // launch move in beside the draining ones (measured, four launches of 1/32 of that image each on two streams:
     // 0.39 ms against 0.45 ms with 4 pinned blocks per SM).
-    uint64_t per_sm = px_total < (64ull << 20) ? 2 : 4;
+    // Larger launches: 3 blocks per SM, pinned (measured on the 16384^2 image with 1024-pixel batches: 2.135 ms
+    // against 2.145 ms with 4; with 512-pixel batches 3, 4 and 5 gave 2.170, 2.164 and 2.165 ms).
+    uint64_t per_sm = px_total < (64ull << 20) ? 2 : 3;
     if (env_per_sm >= 1 && env_per_sm <= 6) per_sm = (uint64_t)env_per_sm;
     const uint64_t cap = (uint64_t)sms * per_sm;
     grid = (int)(ctas < cap ? ctas : cap);
     // Small images (2 blocks per SM) are short launches, usually frames of a sequence: there the next
     // frame's blocks should move in while this frame's last ones drain (65 -> 41 us per 1080p frame
     // with two alternating streams), and a few tens of microseconds cannot go far out of balance.
-    const bool pin = per_sm >= 4;
+    const bool pin = per_sm >= 3;
     VRHI_TRY(launch_escape_pair(st, q, p, grid, (int)per_sm, pin, args[0].ptr, counter, wire));
     return post_launch(st, "escape_time (two pixels per lane)");
   }

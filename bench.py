@@ -478,6 +478,34 @@ def frame_workloads(dev, st, torch, fp32_peak, fp32_nominal):
                                  "frac": OPS_PER_ITER * rate / 1e9 / fp32_peak, "frac_of_nominal": OPS_PER_ITER * rate / 1e9 / fp32_nominal}})
 
     frame_line("mandelbrot 1080p max_iter=256, 50 frames back to back on one stream", ms, digest(img) == want)
+    # The same 50 launches on the same one stream into a ring of 4 images, each declared independent of the 3
+    # launches before it (they write other slots): a frame's first blocks start beside the last blocks of the
+    # frame before; every fourth launch is ordered behind everything before it.
+    ring = [img] + [dev.empty((H, W), np.uint32, L.IMAGE) for _ in range(3)]
+    p_ring = ops.escape_params(L.MANDELBROT, W, H, -2.5, -1.0, dx, dy, max_iter=256, independent_of=3)
+    turn = [0]
+
+    def next_frame():
+        ops.escape_time(st, ring[turn[0] % 4], p_ring)
+        turn[0] += 1
+
+    for b in ring:
+        b.fill(0, stream=st)
+    ms_ring = time_launches(dev, st, next_frame, 50)
+    st.check()
+    frame_line("mandelbrot 1080p ring of 4, 50 frames back to back on one stream, each launch declared independent of the 3 before it",
+               ms_ring, all(digest(r) == want for r in ring))
+    with st.record() as seq:
+        for k in range(48):
+            ops.escape_time(st, ring[k % 4], p_ring)
+    for b in ring:
+        b.fill(0, stream=st)
+    ms_ring_seq = time_launches(dev, st, lambda: seq.launch(), 5) / 48
+    st.check()
+    frame_line("mandelbrot 1080p ring of 4, 48 such frames recorded on one stream", ms_ring_seq, all(digest(r) == want for r in ring))
+    seq.close()
+    for b in ring[1:]:
+        b.close()
     # The same frames into a ring of 4 images from two streams in turn, recorded once: the first blocks of a
     # frame start while the last blocks of the frame before drain (a frame is far too short to fill the GPU to its end).
     side = dev.stream()
@@ -507,9 +535,15 @@ def frame_workloads(dev, st, torch, fp32_peak, fp32_nominal):
                                  test=L.TEST_NORM_GE, bound=20.0, output=L.OUT_COLOR_F32, color_scale=0.02)
                for k in range(frames)]
 
-    def run_frames(streams):
-        for k, fp in enumerate(fparams):
+    def run_frames(streams, params=None):
+        for k, fp in enumerate(params or fparams):
             ops.escape_time(streams[k % len(streams)], ring[k % 4], fp)
+
+    fparams_ring = []
+    for fp in fparams:     # the same frames, each declared independent of the 3 before it (the ring has 4 slots)
+        q = L.EscapeParams.from_buffer_copy(fp)
+        q.flags |= 3 << 8
+        fparams_ring.append(q)
 
     ms_plain = time_launches(dev, st, lambda: run_frames([st]), 5) / frames
     with st.record() as seq:
@@ -520,9 +554,14 @@ def frame_workloads(dev, st, torch, fp32_peak, fp32_nominal):
         run_frames([st, side])
     ms_seq2 = time_launches(dev, st, lambda: seq2.launch(), 5) / frames
     st.check()
+    with st.record() as seq3:
+        run_frames([st], fparams_ring)
+    ms_seq3 = time_launches(dev, st, lambda: seq3.launch(), 5) / frames
+    st.check()
+    seq3.close()
     out.append({"workload": f"fractal.py frame 640x320 f32 colour max_iter=50, {frames} frames, a new uniform each", "kernel": "escape_time",
-                "ms": ms_seq2, "ms_plain_launches": ms_plain, "ms_recorded": ms_seq, "ms_recorded_two_streams": ms_seq2,
-                "frames_per_s": 1e3 / ms_seq2})
+                "ms": min(ms_seq2, ms_seq3), "ms_plain_launches": ms_plain, "ms_recorded": ms_seq, "ms_recorded_two_streams": ms_seq2,
+                "ms_recorded_one_stream_independent_launches": ms_seq3, "frames_per_s": 1e3 / min(ms_seq2, ms_seq3)})
     seq.close()
     seq2.close()
     side.close()

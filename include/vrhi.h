@@ -249,6 +249,17 @@ typedef struct vrhi_escape_params {
  * column i) has real part y0 + j*dy and imaginary part x0 + i*dx.  This is the memory order of a
  * field indexed [i, j] whose first index feeds the real part (fractal.py:8,20). */
 #define VRHI_ESCAPE_FLAG_TRANSPOSED 2u
+/* Bits 8-10, k = 1..7: the caller declares that this launch reads and writes nothing that the k
+ * escape_time launches before it on the same stream write (frames that go round a ring of k+1
+ * images, as the loop of fractal.py:30-33 would with a swap chain).  Such a launch may begin while
+ * those launches still run, so that its first blocks fill the SMs the last blocks of the frame
+ * before leave idle; it never completes before them, and whatever else follows on the stream
+ * (copies, events, other operators, launches without the declaration) is ordered behind all of
+ * them as usual.  k = 0 (the default): the launch is ordered behind everything before it.
+ * Results are the same either way. */
+#define VRHI_ESCAPE_FLAG_INDEPENDENT_SHIFT 8
+#define VRHI_ESCAPE_FLAG_INDEPENDENT_MASK 0x700u
+#define VRHI_ESCAPE_INDEPENDENT_OF(k) (((uint32_t)(k) & 7u) << VRHI_ESCAPE_FLAG_INDEPENDENT_SHIFT)
 
 /* op "escape_time", optional second argument: a uint16 image of the same [height][width]
  * geometry that receives every count a second time (uint32 counts only, max_iter <= 65535).

@@ -193,3 +193,127 @@ def test_a_sequence_survives_the_growth_of_its_streams_scratch(dev, stream):
     seq.close()
     for b in (img, M, out):
         b.close()
+
+
+# --------------------------------------------------------------------------------------------------
+# Launches declared independent of their predecessors (VRHI_ESCAPE_INDEPENDENT_OF): frames that go
+# round a ring on ONE stream and may begin before the frames before them end.  Every frame must
+# still be, bit for bit, what an ordered launch with the same parameters writes.
+
+def _view_params(k, W, H, independent_of, max_iter=256):
+    dx, dy = ops.grid_steps(-2.5 + 0.01 * k, 1.0 + 0.01 * k, -1.0, 1.0, W, H)
+    return ops.escape_params(L.MANDELBROT, W, H, -2.5 + 0.01 * k, -1.0, dx, dy, max_iter=max_iter, independent_of=independent_of)
+
+
+@pytest.mark.parametrize("recorded", [False, True])
+@pytest.mark.parametrize("ring_size,independent_of", [(4, 3), (2, 1), (8, 7)])
+def test_independent_launches_on_one_stream_write_the_frames_ordered_launches_write(dev, stream, recorded, ring_size, independent_of):
+    W, H, frames = 960, 544, 2 * ring_size + 3          # work-stealing kernel, two pixels per lane
+    want = []
+    scratch = dev.empty((H, W), np.uint32, L.IMAGE)
+    for k in range(frames):
+        ops.escape_time(stream, scratch, _view_params(k, W, H, 0))
+        stream.check()
+        want.append(scratch.download(dtype=np.uint32, shape=(H, W)))
+    counts, _ = oracle.escape_time(oracle.MANDELBROT, W, H, -2.5 + 0.01 * (frames - 1), -1.0,
+                                   *ops.grid_steps(-2.5 + 0.01 * (frames - 1), 1.0 + 0.01 * (frames - 1), -1.0, 1.0, W, H), 0.0, 0.0, 256)
+    assert np.array_equal(want[-1], counts)
+    ring = [dev.empty((H, W), np.uint32, L.IMAGE) for _ in range(ring_size)]
+
+    def run():
+        for k in range(frames):
+            ops.escape_time(stream, ring[k % ring_size], _view_params(k, W, H, independent_of))
+
+    def check():
+        stream.check()
+        for k in range(frames - ring_size, frames):
+            assert np.array_equal(ring[k % ring_size].download(dtype=np.uint32, shape=(H, W)), want[k]), k
+
+    if not recorded:
+        for _ in range(3):
+            for b in ring:
+                b.fill(0xEE, stream=stream)
+            before = stream.launch_count()
+            run()
+            assert stream.launch_count() - before == frames
+            check()
+    else:
+        with stream.record() as seq:
+            run()
+        assert seq.stats()["kernels"] == frames
+        for _ in range(3):
+            for b in ring:
+                b.fill(0xEE, stream=stream)
+            seq.launch(stream)
+            check()
+        seq.launch(stream)          # replays back to back: the second begins behind the whole of the first
+        seq.launch(stream)
+        check()
+        seq.close()
+    # an ordered launch right behind a run sees the run finished: it overwrites the last frame's slot
+    run()
+    last = (frames - 1) % ring_size
+    ops.escape_time(stream, ring[last], _view_params(0, W, H, 0))
+    stream.check()
+    assert np.array_equal(ring[last].download(dtype=np.uint32, shape=(H, W)), want[0])
+    for b in ring + [scratch]:
+        b.close()
+
+
+def test_independent_small_frames_dealt_without_a_counter(dev, stream):
+    """The reference's own frame (fractal.py:7-25, 640 x 320 colour, at most 50 steps) runs the kernel that deals
+    its batches statically; a run of such frames, each with its own uniform, overlaps on one stream."""
+    half, frames = 320, 16
+    d = float(np.float32(2.0 / half))
+    phases = [0.03 * k for k in range(frames)]
+    ring = [dev.empty((2 * half, half), np.float32, L.IMAGE) for _ in range(4)]
+
+    def params(phase, k):
+        return ops.escape_params(L.JULIA, half, 2 * half, -1.0, -2.0, d, d, cr=-0.8, transposed=True,
+                                 ci=float(np.float32(np.cos(np.float32(phase))) * np.float32(0.2)), max_iter=50,
+                                 test=L.TEST_NORM_GE, bound=20.0, output=L.OUT_COLOR_F32, color_scale=0.02, independent_of=k)
+
+    for k, ph in enumerate(phases):
+        ops.escape_time(stream, ring[k % 4], params(ph, 3))
+    stream.check()
+    for k in range(frames - 4, frames):
+        assert np.array_equal(ring[k % 4].download(dtype=np.float32, shape=(2 * half, half)), _oracle_frame(half, phases[k])), k
+    # a run broken by a launch that declares nothing, and by one that declares less than the run is long
+    for k, ph in enumerate(phases):
+        ops.escape_time(stream, ring[k % 4], params(ph, (3, 3, 0, 1, 3, 2)[k % 6]))
+    stream.check()
+    for k in range(frames - 4, frames):
+        assert np.array_equal(ring[k % 4].download(dtype=np.float32, shape=(2 * half, half)), _oracle_frame(half, phases[k])), k
+    for b in ring:
+        b.close()
+
+
+def test_frame_loop_on_one_stream_overlaps_its_frames():
+    ti.init()
+    half = 160
+    canvas = ti.field(dtype=float, shape=(half * 2, half))
+
+    @ti.kernel
+    def draw(phase: float):
+        for a, b in canvas:
+            k = ti.Vector([-0.8, ti.cos(phase) * 0.2])
+            w = ti.Vector([a / half - 1, b / half - 0.5]) * 2
+            steps = 0
+            while w.norm() < 20 and steps < 50:
+                w = ti.Vector([w[0] ** 2 - w[1] ** 2, w[1] * w[0] * 2]) + k
+                steps += 1
+            canvas[a, b] = 1 - steps * 0.02
+
+    loop = ti.FrameLoop(draw, canvas, ring=4, streams=1)
+    assert loop.independent_of == 3 and len(loop.streams) == 1
+    phases = [k * 0.03 for k in range(9)]
+    loop.record(phases)
+    assert (draw.last_params.flags >> 8) & 7 == 3
+    loop.play()
+    loop.play()
+    for k in (5, 6, 7, 8):
+        assert np.array_equal(loop.frame(k), _oracle_frame(half, phases[k])), k
+    draw(0.5)                                        # outside the loop the kernel declares nothing
+    assert (draw.last_params.flags >> 8) & 7 == 0
+    assert np.array_equal(canvas.to_numpy(), _oracle_frame(half, 0.5))
+    loop.close()

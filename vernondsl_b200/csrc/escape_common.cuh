@@ -78,6 +78,31 @@ __device__ __forceinline__ void store_wire(uint16_t *wire, uint8_t *bytes, size_
   if (bytes) bytes[pix] = (uint8_t)min(count, 255u);
 }
 
+// A launch that its caller declared independent of the launches before it is started with the
+// programmatic-serialization attribute: its blocks may become resident as soon as every block of the
+// launch before it has passed begin_overlap(), i.e. at once, beside that launch's blocks.  Every
+// block calls end_overlap() last: the grid then cannot complete before the grid before it has, so
+// whatever follows on the stream in the ordinary way still finds everything earlier finished.
+// Both are no-ops in a launch without the attribute and nothing after it that carries it.
+__device__ __forceinline__ void begin_overlap() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void end_overlap() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Launch `kern` on the stream; `overlap`: with the attribute described above.
+template <class Kern, class... Args>
+cudaError_t launch_maybe_overlapped(Kern kern, int grid, int block, size_t dyn, cudaStream_t s, bool overlap, Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3((unsigned)block);
+  cfg.dynamicSmemBytes = dyn;
+  cfg.stream = s;
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = overlap ? 1u : 0u;
+  return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
 // Order in which a launch visits its rows: from the middle outwards (k = 0 is the middle row).  The
 // expensive rows of these images lie around the middle and hold the pixels that run for thousands
 // of steps; a pixel started late is a tail nothing else covers (one warp, one dependent chain, tens
@@ -107,7 +132,7 @@ __device__ __forceinline__ uint32_t owned_row_to_image_row(const EscapeDev &p, u
 // launches from several host threads never see a limit below what they ask for.
 template <class Kern>
 int launch_pinned(Kern kern, int grid, int per_sm, vrhi_stream_t *st, const EscapeDev &p, void *image, uint32_t *counter,
-                  uint16_t *wire, bool pin = true) {
+                  uint16_t *wire, bool pin = true, bool overlap = false) {
   struct Entry { size_t fixed; size_t limit; };
   static std::mutex mu;
   static std::unordered_map<uint64_t, Entry> cache;  // key: kernel address mixed with the device ordinal
@@ -134,12 +159,13 @@ int launch_pinned(Kern kern, int grid, int per_sm, vrhi_stream_t *st, const Esca
       it->second.limit = dyn;
     }
   }
-  kern<<<grid, 256, dyn, st->s>>>(p, image, counter, wire);
+  if (overlap) VRHI_CUDA(launch_maybe_overlapped(kern, grid, 256, dyn, st->s, true, p, image, counter, wire));
+  else kern<<<grid, 256, dyn, st->s>>>(p, image, counter, wire);
   return VRHI_OK;
 }
 
 // the two-pixels-per-lane kernel (k_escape_pair.cu)
-int launch_escape_pair(vrhi_stream_t *st, const vrhi_escape_params &q, const EscapeDev &p, int grid, int per_sm, bool pin, void *image,
-                       uint32_t *counter, uint16_t *wire);
+int launch_escape_pair(vrhi_stream_t *st, const vrhi_escape_params &q, const EscapeDev &p, int grid, int per_sm, bool pin, bool overlap,
+                       void *image, uint32_t *counter, uint16_t *wire);
 
 }  // namespace vrhi

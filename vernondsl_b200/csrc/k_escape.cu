@@ -27,6 +27,7 @@ namespace vrhi {
 template <int KIND, int MODE, int TEST, int OUT>
 __global__ void __launch_bounds__(256) escape_checked_kernel(EscapeDev p, void *image, uint32_t *work_counter, uint16_t *wire) {
   const uint32_t lane = threadIdx.x & 31u;
+  begin_overlap();
   // work_counter == nullptr: batches are dealt to warps round-robin (small frames, where the
   // counter's reset would cost as much as the frame); otherwise warps pull batches from the counter
   uint32_t next = blockIdx.x * 8u + (threadIdx.x >> 5);
@@ -67,23 +68,25 @@ __global__ void __launch_bounds__(256) escape_checked_kernel(EscapeDev p, void *
       if (wire) store_wire(wire, p.bytes, row_base + i, count);
     }
   }
+  end_overlap();
 }
 
 template <int KIND, int MODE, int TEST>
-static void launch_checked_out(int out, int grid, cudaStream_t s, const EscapeDev &p, void *image, uint32_t *ctr, uint16_t *wire) {
+static void launch_checked_out(int out, int grid, cudaStream_t s, bool overlap, const EscapeDev &p, void *image, uint32_t *ctr, uint16_t *wire) {
+  uint16_t *const none = nullptr;
   switch (out) {
-    case VRHI_OUT_COUNT_U32: escape_checked_kernel<KIND, MODE, TEST, VRHI_OUT_COUNT_U32><<<grid, 256, 0, s>>>(p, image, ctr, wire); break;
-    case VRHI_OUT_COUNT_U16: escape_checked_kernel<KIND, MODE, TEST, VRHI_OUT_COUNT_U16><<<grid, 256, 0, s>>>(p, image, ctr, nullptr); break;
-    default: escape_checked_kernel<KIND, MODE, TEST, VRHI_OUT_COLOR_F32><<<grid, 256, 0, s>>>(p, image, ctr, nullptr); break;
+    case VRHI_OUT_COUNT_U32: launch_maybe_overlapped(escape_checked_kernel<KIND, MODE, TEST, VRHI_OUT_COUNT_U32>, grid, 256, 0, s, overlap, p, image, ctr, wire); break;
+    case VRHI_OUT_COUNT_U16: launch_maybe_overlapped(escape_checked_kernel<KIND, MODE, TEST, VRHI_OUT_COUNT_U16>, grid, 256, 0, s, overlap, p, image, ctr, none); break;
+    default: launch_maybe_overlapped(escape_checked_kernel<KIND, MODE, TEST, VRHI_OUT_COLOR_F32>, grid, 256, 0, s, overlap, p, image, ctr, none); break;
   }
 }
 
 template <int KIND, int MODE>
-static void launch_checked_test(int test, int out, int grid, cudaStream_t s, const EscapeDev &p, void *image, uint32_t *ctr, uint16_t *wire) {
+static void launch_checked_test(int test, int out, int grid, cudaStream_t s, bool overlap, const EscapeDev &p, void *image, uint32_t *ctr, uint16_t *wire) {
   if (test == VRHI_TEST_NORM2_GT)
-    launch_checked_out<KIND, MODE, VRHI_TEST_NORM2_GT>(out, grid, s, p, image, ctr, wire);
+    launch_checked_out<KIND, MODE, VRHI_TEST_NORM2_GT>(out, grid, s, overlap, p, image, ctr, wire);
   else
-    launch_checked_out<KIND, MODE, VRHI_TEST_NORM_GE>(out, grid, s, p, image, ctr, wire);
+    launch_checked_out<KIND, MODE, VRHI_TEST_NORM_GE>(out, grid, s, overlap, p, image, ctr, wire);
 }
 
 int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const void *params, size_t params_size) {
@@ -177,13 +180,28 @@ int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const
   // A frame of a few batches per warp (the 640 x 320 frame of fractal.py:7-8 is one) is dealt out
   // statically: resetting a work counter would be a second node per frame and cost as much as the frame.
   const bool dealt = !regroup_ok && nb <= (uint64_t)grid * 8 * 4;
+  // A launch declared independent of the k launches before it (flags, bits 8-10) may begin before they end.
+  // Such launches form runs: the first of a run is ordered behind everything earlier on the stream, each
+  // further one is started with the overlap attribute, and a run ends where a launch is no longer independent
+  // of the run's first (run length > k) or anything else happens on the stream.  Launch i of a run therefore
+  // only ever runs beside launches it was declared independent of.  The launches of a run take their work from
+  // counters of their own, all reset by the one memset in front of the run's first launch.
+  const uint32_t independent_of = (q.flags & VRHI_ESCAPE_FLAG_INDEPENDENT_MASK) >> VRHI_ESCAPE_FLAG_INDEPENDENT_SHIFT;
+  const int run = st->escape_chain;  // launches of the current run so far
+  const bool overlap = independent_of != 0 && run >= 1 && (uint32_t)run <= independent_of && run < 8;
   uint32_t *counter = nullptr;
   if (!dealt) {
     uint32_t *ctrl = nullptr;
     VRHI_TRY(stream_arena(st, 0, &ctrl, nullptr));
-    counter = ctrl + CTRL_WORK0;
-    VRHI_CUDA(cudaMemsetAsync(counter, 0, sizeof(uint32_t), st->s));
+    if (independent_of == 0) {
+      counter = ctrl + CTRL_WORK0;
+      VRHI_CUDA(cudaMemsetAsync(counter, 0, sizeof(uint32_t), st->s));
+    } else {
+      counter = ctrl + CTRL_ESCAPE_RING + (overlap ? run : 0);
+      if (!overlap) VRHI_CUDA(cudaMemsetAsync(ctrl + CTRL_ESCAPE_RING, 0, 8 * sizeof(uint32_t), st->s));
+    }
   }
+  const int run_after = independent_of == 0 ? 0 : overlap ? run + 1 : 1;
   if (regroup_ok) {
     // Measured on B200: 3-4 CTAs of 256 threads per SM are as fast as more (the kernels are bound by
     // issue or by the binary32 pipe, not by latency); small images run faster still with 2, because
@@ -204,17 +222,21 @@ int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const
     // frame's blocks should move in while this frame's last ones drain (65 -> 41 us per 1080p frame
     // with two alternating streams), and a few tens of microseconds cannot go far out of balance.
     const bool pin = per_sm >= 3;
-    VRHI_TRY(launch_escape_pair(st, q, p, grid, (int)per_sm, pin, args[0].ptr, counter, wire));
-    return post_launch(st, "escape_time (two pixels per lane)");
+    VRHI_TRY(launch_escape_pair(st, q, p, grid, (int)per_sm, pin, overlap, args[0].ptr, counter, wire));
+    VRHI_TRY(post_launch(st, "escape_time (two pixels per lane)"));
+    st->escape_chain = run_after;
+    return VRHI_OK;
   }
   if (q.kind == VRHI_ESCAPE_MANDELBROT) {
-    if (q.mode == VRHI_ESCAPE_EXACT) launch_checked_test<VRHI_ESCAPE_MANDELBROT, VRHI_ESCAPE_EXACT>(q.test, q.output, grid, st->s, p, args[0].ptr, counter, wire);
-    else launch_checked_test<VRHI_ESCAPE_MANDELBROT, VRHI_ESCAPE_FAST>(q.test, q.output, grid, st->s, p, args[0].ptr, counter, wire);
+    if (q.mode == VRHI_ESCAPE_EXACT) launch_checked_test<VRHI_ESCAPE_MANDELBROT, VRHI_ESCAPE_EXACT>(q.test, q.output, grid, st->s, overlap, p, args[0].ptr, counter, wire);
+    else launch_checked_test<VRHI_ESCAPE_MANDELBROT, VRHI_ESCAPE_FAST>(q.test, q.output, grid, st->s, overlap, p, args[0].ptr, counter, wire);
   } else {
-    if (q.mode == VRHI_ESCAPE_EXACT) launch_checked_test<VRHI_ESCAPE_JULIA, VRHI_ESCAPE_EXACT>(q.test, q.output, grid, st->s, p, args[0].ptr, counter, wire);
-    else launch_checked_test<VRHI_ESCAPE_JULIA, VRHI_ESCAPE_FAST>(q.test, q.output, grid, st->s, p, args[0].ptr, counter, wire);
+    if (q.mode == VRHI_ESCAPE_EXACT) launch_checked_test<VRHI_ESCAPE_JULIA, VRHI_ESCAPE_EXACT>(q.test, q.output, grid, st->s, overlap, p, args[0].ptr, counter, wire);
+    else launch_checked_test<VRHI_ESCAPE_JULIA, VRHI_ESCAPE_FAST>(q.test, q.output, grid, st->s, overlap, p, args[0].ptr, counter, wire);
   }
-  return post_launch(st, "escape_time");
+  VRHI_TRY(post_launch(st, "escape_time"));
+  st->escape_chain = run_after;
+  return VRHI_OK;
 }
 
 // ---------------------------------------------------------------------------------------------

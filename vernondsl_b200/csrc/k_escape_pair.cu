@@ -115,6 +115,7 @@ constexpr int kPairPool = 128;  // pool entries per warp: a refill wants up to 6
 template <int KIND, int OUT, int U, int T, int K, int MODE, bool WIRE, int EX, int NBLK>
 __global__ void __launch_bounds__(256, 4) escape_pair_kernel(EscapeDev p, void *image, uint32_t *work_counter, uint16_t *wire) {
   constexpr bool PER_PIXEL_C = (KIND == VRHI_ESCAPE_MANDELBROT);
+  begin_overlap();
   __shared__ float4 s_pool[8][kPairPool];  // zr, zi, pixel index, count: one 16-byte access per entry
   __shared__ float2 s_c[PER_PIXEL_C ? 8 : 1][PER_PIXEL_C ? kPairPool : 1];
   const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
@@ -329,19 +330,20 @@ __global__ void __launch_bounds__(256, 4) escape_pair_kernel(EscapeDev p, void *
     if (__any_sync(FULL, (occ0 && cnt0 > fast_limit) || (occ1 && cnt1 > fast_limit))) checked_block(std::true_type{});
     else checked_block(std::false_type{});
   }
+  end_overlap();
 }
 
 // The shipped instantiation: U = 12, T = 16 of 64, K = 12 with exits before steps 2, 4, 6 and 8, two blocks
 // between counts.  Sweeps on B200 (U = 6..24, T = 4..32, K = 4..16, one to four blocks between counts)
 // stayed within 3 % of this point on the 16384^2 Julia image.
 
-int launch_escape_pair(vrhi_stream_t *st, const vrhi_escape_params &q, const EscapeDev &p, int grid, int per_sm, bool pin, void *image,
-                       uint32_t *counter, uint16_t *wire) {
+int launch_escape_pair(vrhi_stream_t *st, const vrhi_escape_params &q, const EscapeDev &p, int grid, int per_sm, bool pin, bool overlap,
+                       void *image, uint32_t *counter, uint16_t *wire) {
   constexpr int U = 12, T = 16, K = 12, EX = 0x154, NBLK = 2;
 #define PAIR(KIND, OUT, WIRE)                                                                                                        \
   do {                                                                                                                               \
-    if (q.mode == VRHI_ESCAPE_EXACT) return launch_pinned(escape_pair_kernel<KIND, OUT, U, T, K, VRHI_ESCAPE_EXACT, WIRE, EX, NBLK>, grid, per_sm, st, p, image, counter, wire, pin); \
-    return launch_pinned(escape_pair_kernel<KIND, OUT, U, T, K, VRHI_ESCAPE_FAST, WIRE, EX, NBLK>, grid, per_sm, st, p, image, counter, wire, pin);  \
+    if (q.mode == VRHI_ESCAPE_EXACT) return launch_pinned(escape_pair_kernel<KIND, OUT, U, T, K, VRHI_ESCAPE_EXACT, WIRE, EX, NBLK>, grid, per_sm, st, p, image, counter, wire, pin, overlap); \
+    return launch_pinned(escape_pair_kernel<KIND, OUT, U, T, K, VRHI_ESCAPE_FAST, WIRE, EX, NBLK>, grid, per_sm, st, p, image, counter, wire, pin, overlap);  \
   } while (0)
   if (wire) {
     if (q.kind == VRHI_ESCAPE_MANDELBROT) PAIR(VRHI_ESCAPE_MANDELBROT, VRHI_OUT_COUNT_U32, true);

@@ -47,6 +47,7 @@ int stream_arena(vrhi_stream_t *st, size_t payload, uint32_t **ctrl, char **payl
       VRHI_CUDA(cudaMemcpyAsync(p, st->arena, kCtrlBytes, cudaMemcpyDeviceToDevice, st->s));
       VRHI_CUDA(cudaMemsetAsync(st->arena, 0, sizeof(uint32_t), st->s));  // the status word went along: report it once
       st->retired[st->n_retired++] = st->arena;
+      st->escape_chain = 0;  // the ring of work counters moved: the next escape-time launch starts a new run
     } else {
       VRHI_CUDA(cudaMemsetAsync(p, 0, kCtrlBytes, st->s));
     }
@@ -316,6 +317,7 @@ static int copy(vrhi_buffer buf, uint64_t offset, void *host, uint64_t bytes, vr
   VRHI_TRY(set_device(buf->dev));
   char *d = static_cast<char *>(buf->ptr) + offset;
   if (stream) {
+    stream->escape_chain = 0;
     VRHI_CUDA(cudaMemcpyAsync(up ? (void *)d : host, up ? (const void *)host : (const void *)d, bytes,
                               up ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost, stream->s));
   } else {
@@ -340,6 +342,7 @@ int vrhi_buffer_fill_u8(vrhi_buffer buf, uint64_t offset, int value, uint64_t by
   if (bytes == 0) return VRHI_OK;
   VRHI_TRY(set_device(buf->dev));
   char *d = static_cast<char *>(buf->ptr) + offset;
+  if (stream) stream->escape_chain = 0;
   if (stream)
     VRHI_CUDA(cudaMemsetAsync(d, value, bytes, stream->s));
   else
@@ -377,6 +380,7 @@ int vrhi_buffer_copy_2d(vrhi_buffer dst, uint64_t dst_offset, uint64_t dst_pitch
     return fail(VRHI_ERR_INVALID, "copy destination is read-only (class %s)", vrhi_arg_class_name(dst->cls));
   VRHI_TRY(set_device(src->dev));
   cudaStream_t s = stream ? stream->s : nullptr;
+  if (stream) stream->escape_chain = 0;
   char *d = static_cast<char *>(dst->ptr) + dst_offset;
   const char *sp = static_cast<const char *>(src->ptr) + src_offset;
   if (rows == 1)
@@ -516,6 +520,7 @@ int vrhi_event_destroy(vrhi_event event) {
 int vrhi_event_record(vrhi_event event, vrhi_stream stream) {
   if (!event) return fail(VRHI_ERR_INVALID, "NULL event");
   VRHI_TRY(set_device(event->dev));
+  if (stream) stream->escape_chain = 0;
   VRHI_CUDA(cudaEventRecord(event->e, stream ? stream->s : nullptr));
   return VRHI_OK;
 }
@@ -566,6 +571,7 @@ int vrhi_sequence_begin(vrhi_stream stream) {
   VRHI_CUDA(cudaStreamBeginCapture(stream->s, cudaStreamCaptureModeThreadLocal));
   stream->recording = true;
   stream->record_mark = stream->launches;
+  stream->escape_chain = 0;  // a recording may be replayed behind anything: its first launch is ordered
   return VRHI_OK;
 }
 
@@ -580,6 +586,8 @@ int vrhi_sequence_fork(vrhi_stream stream, vrhi_stream side) {
   VRHI_CUDA(cudaEventRecord(stream->fork_event, stream->s));
   VRHI_CUDA(cudaStreamWaitEvent(side->s, stream->fork_event, 0));  // the side stream joins the capture here
   side->recording = true;
+  side->escape_chain = 0;
+  stream->escape_chain = 0;
   side->record_main = stream;
   side->record_mark = side->launches;
   stream->record_sides[stream->n_record_sides++] = side;
@@ -592,6 +600,7 @@ int vrhi_sequence_end(vrhi_stream stream, vrhi_sequence *inout_seq) {
   if (stream->record_main) return fail(VRHI_ERR_INVALID, "end the recording on the stream it began on");
   VRHI_TRY(set_device(stream->dev));
   stream->recording = false;
+  stream->escape_chain = 0;  // nothing of the recording precedes the next launch on the stream
   uint64_t kernels = stream->launches - stream->record_mark;
   stream->launches = stream->record_mark;  // nothing ran
   for (int k = 0; k < stream->n_record_sides; ++k) {
@@ -605,6 +614,7 @@ int vrhi_sequence_end(vrhi_stream stream, vrhi_sequence *inout_seq) {
     kernels += side->launches - side->record_mark;
     side->launches = side->record_mark;
     side->recording = false;
+    side->escape_chain = 0;
     side->record_main = nullptr;
   }
   stream->n_record_sides = 0;
@@ -652,6 +662,7 @@ int vrhi_sequence_launch(vrhi_sequence seq, vrhi_stream stream) {
   if (seq->dev != stream->dev) return fail(VRHI_ERR_INVALID, "the sequence was recorded on another device");
   VRHI_TRY(set_device(stream->dev));
   VRHI_CUDA(cudaGraphLaunch(seq->exec, stream->s));
+  stream->escape_chain = 0;
   stream->launches += seq->kernels;
   return VRHI_OK;
 }
@@ -675,6 +686,7 @@ int vrhi_sequence_destroy(vrhi_sequence seq) {
 int vrhi_stream_wait_event(vrhi_stream stream, vrhi_event event) {
   if (!stream || !event) return fail(VRHI_ERR_INVALID, "NULL argument");
   VRHI_TRY(set_device(stream->dev));
+  stream->escape_chain = 0;
   VRHI_CUDA(cudaStreamWaitEvent(stream->s, event->e, 0));
   return VRHI_OK;
 }

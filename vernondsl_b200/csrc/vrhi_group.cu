@@ -256,6 +256,7 @@ int vrhi_group_set_wait_ms(vrhi_group g, uint32_t wait_ms) {
 int vrhi_group_all_reduce_sum_f32(vrhi_group g, vrhi_buffer buf, uint64_t offset, uint64_t n, vrhi_stream stream) {
   if (!g || !buf || !stream) return fail(VRHI_ERR_INVALID, "NULL argument");
   if (buf->dev != g->dev || stream->dev != g->dev) return fail(VRHI_ERR_INVALID, "buffer and stream must live on the group's device");
+  stream->escape_chain = 0;
   if (offset % 4) return fail(VRHI_ERR_SIZE, "offset %llu is not a multiple of 4", (unsigned long long)offset);
   if (n > kBoxCapacity) return fail(VRHI_ERR_SIZE, "all-reduce of %llu floats: at most %u per call", (unsigned long long)n, kBoxCapacity);
   if (offset > buf->bytes || n * 4 > buf->bytes - offset) return fail(VRHI_ERR_SIZE, "range exceeds the buffer");
@@ -456,6 +457,7 @@ int vrhi_exchange_publish(vrhi_exchange ex, vrhi_stream compute, uint32_t slab_f
   if (!ex || !compute) return fail(VRHI_ERR_INVALID, "NULL argument");
   vrhi_group_t *g = ex->grp;
   if (compute->dev != g->dev) return fail(VRHI_ERR_INVALID, "the stream belongs to another device than the group");
+  compute->escape_chain = 0;
   const uint32_t stride = slab_stride ? slab_stride : 1u;
   if (slab_count == 0) return fail(VRHI_ERR_SIZE, "an empty group of slabs cannot be published (every rank must publish the same groups)");
   if ((uint64_t)slab_first + (uint64_t)(slab_count - 1) * stride >= ex->n_slabs) return fail(VRHI_ERR_SIZE, "slabs %u + k*%u, k < %u, reach beyond the image's %u", slab_first, stride, slab_count, ex->n_slabs);
@@ -477,6 +479,7 @@ int vrhi_exchange_publish(vrhi_exchange ex, vrhi_stream compute, uint32_t slab_f
 int vrhi_exchange_complete(vrhi_exchange ex, vrhi_stream stream) {
   if (!ex || !stream) return fail(VRHI_ERR_INVALID, "NULL argument");
   if (stream->dev != ex->grp->dev) return fail(VRHI_ERR_INVALID, "the stream belongs to another device than the group");
+  stream->escape_chain = 0;
   ex->steps++;
   if (ex->grp->world == 1) return VRHI_OK;
   VRHI_TRY(set_dev(ex->grp->dev));

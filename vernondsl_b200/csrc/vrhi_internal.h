@@ -50,6 +50,11 @@ struct vrhi_stream_t {
   // verdict), and must find them intact however much the stream's scratch has grown since.
   char *retired[24];
   int n_retired;
+  // Escape-time launches that their caller declared independent of their predecessors may begin before those
+  // end (k_escape.cu).  Length of the current run of such launches, counted from the last launch that was
+  // ordered behind everything before it; 0: the next launch is ordered.  Every other operation on the stream
+  // that the library sees sets it back to 0.
+  int escape_chain;
 };
 
 struct vrhi_sequence_t {
@@ -67,7 +72,8 @@ namespace vrhi {
 
 constexpr size_t kCtrlBytes = 256;
 // control-word indices (uint32) inside the arena's control block
-enum { CTRL_STATUS = 0, CTRL_WORK0 = 1, CTRL_WORK1 = 2, CTRL_DONE = 3, CTRL_WAIT_OK = 4 };
+enum { CTRL_STATUS = 0, CTRL_WORK0 = 1, CTRL_WORK1 = 2, CTRL_DONE = 3, CTRL_WAIT_OK = 4,
+       CTRL_ESCAPE_RING = 8 /* 8 work counters, one per launch of a run of overlapping escape-time launches */ };
 
 int fail(int code, const char *fmt, ...) __attribute__((format(printf, 2, 3)));
 void clear_error();
@@ -192,6 +198,7 @@ inline int post_launch(vrhi_stream_t *st, const char *what, int kernels = 1) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(VRHI_ERR_CUDA, "launch of %s failed: %s", what, cudaGetErrorString(e));
   st->launches += (uint64_t)kernels;
+  st->escape_chain = 0;  // the escape-time launcher sets its own value after this
   return VRHI_OK;
 }
 

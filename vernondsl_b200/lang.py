@@ -53,7 +53,8 @@ class LangError(NotImplementedError):
     pass
 
 
-_state: Dict[str, Any] = {"dev": None, "stream": None}
+# "independent_of": FrameLoop sets it while it records frames that go round its ring on one stream
+_state: Dict[str, Any] = {"dev": None, "stream": None, "independent_of": 0}
 
 
 def init(arch=cuda, device: int = 0, **_ignored) -> None:
@@ -555,7 +556,7 @@ class Kernel:
             raise LangError("stores supported: the count into an integer field, or 1 - count*s into a float field")
         p = ops.escape_params(kind, cols, rows, float(f32(float(x0))), float(f32(float(y0))), float(f32(float(dx))),
                               float(f32(float(dy))), cr=cr, ci=ci, max_iter=max_iter, test=test, bound=bound, output=output,
-                              color_scale=scale, transposed=transposed)
+                              color_scale=scale, transposed=transposed, independent_of=_state["independent_of"])
         self.last_plan = f"escape_time kind={'julia' if kind == L.JULIA else 'mandelbrot'} {cols}x{rows} transposed={transposed}"
         self.last_params = p
         ops.escape_time(st, fld.buffer, p)
@@ -644,7 +645,7 @@ class FrameLoop:
     again with other uniforms re-targets the existing recording in place.
     """
 
-    def __init__(self, kern: "Kernel", target: Field, ring: int = 4, streams: int = 2):
+    def __init__(self, kern: "Kernel", target: Field, ring: int = 4, streams: int = 2, overlap: bool = True):
         if ring < 1:
             raise ValueError("the ring needs at least one frame")
         if not 1 <= streams <= 4:
@@ -657,6 +658,9 @@ class FrameLoop:
         # frame's first blocks may start while the last blocks of this one drain
         self.streams: List[Stream] = [st] + [dev.stream() for _ in range(streams - 1)]
         self.ring: List[Buffer] = [target.buffer] + [dev.empty(target.shape, target.dtype, L.IMAGE) for _ in range(ring - 1)]
+        # with one stream the frames still overlap where the ring allows it: each launch is declared independent
+        # of the ring - 1 frames before it (they write other slots), which lets it begin before they end
+        self.independent_of = min(7, ring - 1) if overlap and len(self.streams) == 1 else 0
         self.seq = None
         self.frames = 0
 
@@ -675,6 +679,7 @@ class FrameLoop:
             with self.stream.record(self.seq) as seq:
                 for s in self.streams[1:n_streams]:
                     self.stream.fork_recording(s)
+                _state["independent_of"] = self.independent_of
                 for k, u in enumerate(uniforms):
                     self.target.buffer = self.ring[k % len(self.ring)]
                     _state["stream"] = self.streams[k % n_streams]
@@ -684,6 +689,7 @@ class FrameLoop:
         finally:
             self.target.buffer = home
             _state["stream"] = self.stream
+            _state["independent_of"] = 0
 
     def play(self) -> None:
         if self.seq is None:

@@ -54,14 +54,18 @@ def escape_params(kind: int, width: int, height: int, x0: float, y0: float, dx: 
                   ci: float = 0.0, max_iter: int = 256, mode: int = L.EXACT, test: int = L.TEST_NORM2_GT,
                   bound: float = 4.0, output: int = L.OUT_COUNT_U32, color_scale: float = 0.0,
                   partition: Optional[L.RowPartition] = None, checked_only: bool = False,
-                  transposed: bool = False) -> L.EscapeParams:
+                  transposed: bool = False, independent_of: int = 0) -> L.EscapeParams:
+    """``independent_of`` = k (0..7): the launch touches nothing that the k escape_time launches before it on its
+    stream write (a ring of k+1 frames), and may begin before they end."""
+    if not 0 <= independent_of <= 7:
+        raise ValueError("independent_of: 0..7")
     p = L.EscapeParams()
     p.size = C.sizeof(L.EscapeParams)
     p.kind, p.mode, p.test, p.output = kind, mode, test, output
     p.width, p.height, p.max_iter = width, height, max_iter
     p.x0, p.y0, p.dx, p.dy = x0, y0, dx, dy
     p.cr, p.ci, p.bound, p.color_scale = cr, ci, bound, color_scale
-    p.flags = (1 if checked_only else 0) | (2 if transposed else 0)
+    p.flags = (1 if checked_only else 0) | (2 if transposed else 0) | (independent_of << 8)
     if partition is not None:
         p.chunk_rows, p.chunk_first = partition.chunk_rows, partition.chunk_first
         p.chunk_step, p.chunk_count = partition.chunk_step, partition.chunk_count

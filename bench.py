@@ -471,13 +471,13 @@ def frame_workloads(dev, st, torch, fp32_peak, fp32_nominal):
         idx = torch.arange(1, H * W + 1, device=t.device, dtype=torch.int64)
         return [int(t.sum().item()), int((t * idx).sum().item()) & 0xFFFFFFFFFFFFFFFF]
 
-    def frame_line(name, ms_frame, ok):
+    def frame_line(name, ms_frame, ok, short):
         rate = total / (ms_frame * 1e-3)
-        out.append({"workload": name, "kernel": "escape_time", "ms": ms_frame, "gpixel_iters_per_s": rate / 1e9, "verified": ok,
+        out.append({"workload": name, "short": short, "kernel": "escape_time", "ms": ms_frame, "gpixel_iters_per_s": rate / 1e9, "verified": ok,
                     "roofline": {"bound": "fp32", "achieved": OPS_PER_ITER * rate / 1e9, "peak": fp32_peak, "unit": "Gop/s",
                                  "frac": OPS_PER_ITER * rate / 1e9 / fp32_peak, "frac_of_nominal": OPS_PER_ITER * rate / 1e9 / fp32_nominal}})
 
-    frame_line("mandelbrot 1080p max_iter=256, 50 frames back to back on one stream", ms, digest(img) == want)
+    frame_line("mandelbrot 1080p max_iter=256, 50 frames back to back on one stream", ms, digest(img) == want, "1080p, 1 stream, 1 image")
     # The same 50 launches on the same one stream into a ring of 4 images, each declared independent of the 3
     # launches before it (they write other slots): a frame's first blocks start beside the last blocks of the
     # frame before; every fourth launch is ordered behind everything before it.
@@ -494,15 +494,19 @@ def frame_workloads(dev, st, torch, fp32_peak, fp32_nominal):
     ms_ring = time_launches(dev, st, next_frame, 50)
     st.check()
     frame_line("mandelbrot 1080p ring of 4, 50 frames back to back on one stream, each launch declared independent of the 3 before it",
-               ms_ring, all(digest(r) == want for r in ring))
+               ms_ring, all(digest(r) == want for r in ring), "1080p, 1 stream, ring of 4")
+    # a ring of 8, each launch independent of the 7 before it: one ordered launch in eight; recorded once
+    ring += [dev.empty((H, W), np.uint32, L.IMAGE) for _ in range(4)]
+    p_ring8 = ops.escape_params(L.MANDELBROT, W, H, -2.5, -1.0, dx, dy, max_iter=256, independent_of=7)
     with st.record() as seq:
         for k in range(48):
-            ops.escape_time(st, ring[k % 4], p_ring)
+            ops.escape_time(st, ring[k % 8], p_ring8)
     for b in ring:
         b.fill(0, stream=st)
     ms_ring_seq = time_launches(dev, st, lambda: seq.launch(), 5) / 48
     st.check()
-    frame_line("mandelbrot 1080p ring of 4, 48 such frames recorded on one stream", ms_ring_seq, all(digest(r) == want for r in ring))
+    frame_line("mandelbrot 1080p ring of 8, 48 frames recorded on one stream, each launch declared independent of the 7 before it",
+               ms_ring_seq, all(digest(r) == want for r in ring), "1080p, 1 stream, ring of 8, recorded")
     seq.close()
     for b in ring[1:]:
         b.close()
@@ -519,7 +523,7 @@ def frame_workloads(dev, st, torch, fp32_peak, fp32_nominal):
             ops.escape_time(st if k % 2 == 0 else side, ring[k % 4], p)
     ms2 = time_launches(dev, st, lambda: seq.launch(), 5) / 48
     st.check()
-    frame_line("mandelbrot 1080p, 48 frames recorded on two alternating streams, ring of 4", ms2, all(digest(r) == want for r in ring))
+    frame_line("mandelbrot 1080p, 48 frames recorded on two alternating streams, ring of 4", ms2, all(digest(r) == want for r in ring), "1080p, 2 streams, recorded")
     seq.close()
     for b in ring:
         b.close()
@@ -576,7 +580,7 @@ def compact(entries):
     rows = []
     for e in entries:
         r = e.get("roofline", {})
-        rows.append([e["kernel"] if e["kernel"] != "escape_time" else e["workload"][:28], float(f"{e['ms']:.4g}"),
+        rows.append([e.get("short") or (e["kernel"] if e["kernel"] != "escape_time" else e["workload"][:28]), float(f"{e['ms']:.4g}"),
                      float(f"{r.get('frac', 0):.3g}"), float(f"{r.get('frac_of_nominal_8tbs', r.get('frac_of_nominal', 0)):.3g}"),
                      e.get("verified"), float(f"{e.get('max_err', 0):.2g}")])
     return rows

@@ -158,13 +158,13 @@ int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const
   const uint32_t tile_px = pair ? 64u : 32u;  // pixels a warp takes in per intake trip
   p.tiles_per_row = (q.width + tile_px - 1) / tile_px;
   {
-    // batch = unit of work stealing: 1024 pixels of one row for large images (with the rows visited from the
-    // middle outwards the last batches are the cheapest, so large batches cost no tail: 2.164 ms with 512
-    // pixels, 2.145 ms with 1024 on the 16384^2 image); small images get smaller batches so that every
-    // resident warp still sees several of them
+    // batch = unit of work stealing: 1536 pixels of one row for large images (with the rows visited from the
+    // middle outwards the last batches are the cheapest, so large batches cost no tail; on the 16384^2 image
+    // with 3 blocks per SM: 2.170 ms with 512 pixels, 2.144 with 768, 2.133 with 1024, 2.121 with 1536, 2.127
+    // with 2048); small images get smaller batches so that every resident warp still sees several of them
     const uint64_t resident_warps = (uint64_t)sms * 48;
     const uint64_t tiles = (uint64_t)p.tiles_per_row * p.rows_owned;
-    const uint64_t most = 1024 / tile_px;
+    const uint64_t most = 1536 / tile_px;
     uint64_t bt = tiles / (resident_warps * 8);
     const uint64_t least = pair ? 1 : 2;
     p.batch_tiles = (uint32_t)(bt < least ? least : bt > most ? most : bt);
@@ -212,7 +212,7 @@ int launch_escape_time(vrhi_stream_t *st, const ArgView *args, int n_args, const
     // computed group by group, frames of a sequence): with 2 blocks per SM and no pinning the blocks of the next
     // launch move in beside the draining ones (measured, four launches of 1/32 of that image each on two streams:
     // 0.39 ms against 0.45 ms with 4 pinned blocks per SM).
-    // Larger launches: 3 blocks per SM, pinned (measured on the 16384^2 image with 1024-pixel batches: 2.135 ms
+    // Larger launches: 3 blocks per SM, pinned (measured on the 16384^2 image with 1024-pixel batches: 2.133 ms
     // against 2.145 ms with 4; with 512-pixel batches 3, 4 and 5 gave 2.170, 2.164 and 2.165 ms).
     uint64_t per_sm = px_total < (64ull << 20) ? 2 : 3;
     if (env_per_sm >= 1 && env_per_sm <= 6) per_sm = (uint64_t)env_per_sm;

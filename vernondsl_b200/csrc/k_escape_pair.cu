@@ -21,7 +21,7 @@
 //    INTAKE: 64 fresh pixels of a stolen tile run K checked steps in lock step (most pixels of the
 //    far exterior end there and are stored coalesced); survivors are pushed to the ring with their
 //    state.  Long-lived pixels therefore share warps with other long-lived pixels.
-//  * WORK STEALING.  Warps pull batches of up to 16 tiles (1024 pixels of one row) from a global
+//  * WORK STEALING.  Warps pull batches of up to 24 tiles (1536 pixels of one row) from a global
 //    counter.  Nothing here waits on another warp or block: no spin loops, no barriers.
 //
 // TWO PIXELS PER LANE.  Every lane carries two slots, and all arithmetic on them is issued as packed

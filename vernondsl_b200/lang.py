@@ -54,7 +54,24 @@ class LangError(NotImplementedError):
 
 
 # "independent_of": FrameLoop sets it while it records frames that go round its ring on one stream
-_state: Dict[str, Any] = {"dev": None, "stream": None, "independent_of": 0}
+# "plan_only": kernels are lowered but nothing is allocated or launched (see plan_only())
+_state: Dict[str, Any] = {"dev": None, "stream": None, "independent_of": 0, "plan_only": False}
+
+
+class plan_only:
+    """``with ti.plan_only():`` fields created inside hold no device memory and kernels called inside are only
+    lowered: ``kernel.last_plan``, ``kernel.last_params`` (escape-time shape) and ``kernel.last_tape``
+    (elementwise shape) show what a real call would launch.  Nothing is computed: this is how the lowering
+    is inspected, and tested, where there is no GPU."""
+
+    def __enter__(self):
+        self.before = _state["plan_only"]
+        _state["plan_only"] = True
+        return self
+
+    def __exit__(self, *exc):
+        _state["plan_only"] = self.before
+        return False
 
 
 def init(arch=cuda, device: int = 0, **_ignored) -> None:
@@ -80,7 +97,6 @@ class Field:
     """Dense device array (fractal.py:8).  ``dtype`` float -> binary32, int -> int32."""
 
     def __init__(self, dtype, shape):
-        dev, _ = _runtime()
         self.shape = tuple(int(s) for s in (shape if isinstance(shape, (tuple, list)) else (shape,)))
         if dtype in (float, f32, np.dtype(np.float32)):
             self.dtype = np.dtype(np.float32)
@@ -90,10 +106,14 @@ class Field:
             self.dtype = np.dtype(np.uint32)
         else:
             raise LangError(f"field dtype {dtype!r} is not supported")
-        self.buffer: Buffer = dev.empty(self.shape, self.dtype, L.IMAGE)
-        self.buffer.fill(0)
+        self.buffer: Optional[Buffer] = None     # stays None for a field made under plan_only()
+        if not _state["plan_only"]:
+            self.buffer = _runtime()[0].empty(self.shape, self.dtype, L.IMAGE)
+            self.buffer.fill(0)
 
     def to_numpy(self) -> np.ndarray:
+        if self.buffer is None:
+            raise LangError("a field made under plan_only() holds no data")
         _runtime()[1].check()
         return self.buffer.download(dtype=self.dtype, shape=self.shape)
 
@@ -101,6 +121,8 @@ class Field:
         a = np.ascontiguousarray(a, dtype=self.dtype)
         if a.shape != self.shape:
             raise ValueError(f"shape {a.shape} does not match the field's {self.shape}")
+        if self.buffer is None:
+            raise LangError("a field made under plan_only() holds no data")
         self.buffer.upload(a)
 
     def fill(self, value) -> None:
@@ -414,9 +436,11 @@ class Kernel:
         self.fn = fn
         self.__name__ = fn.__name__
         self.last_plan: Optional[str] = None
+        self.last_params = None
+        self.last_tape = None
 
     def __call__(self, *args):
-        dev, st = _runtime()
+        st = None if _state["plan_only"] else _runtime()[1]     # None: lower only
         w = _Walker(self.fn, args)
         body = [s for s in w.fdef.body if not (isinstance(s, ast.Expr) and isinstance(s.value, ast.Constant))]
         if len(body) != 1 or not isinstance(body[0], ast.For):
@@ -559,6 +583,10 @@ class Kernel:
                               color_scale=scale, transposed=transposed, independent_of=_state["independent_of"])
         self.last_plan = f"escape_time kind={'julia' if kind == L.JULIA else 'mandelbrot'} {cols}x{rows} transposed={transposed}"
         self.last_params = p
+        if st is None:
+            return
+        if fld.buffer is None:
+            raise LangError("the field was made under plan_only() and holds no device memory")
         ops.escape_time(st, fld.buffer, p)
 
     # -- elementwise shape -----------------------------------------------------------------------
@@ -627,6 +655,11 @@ class Kernel:
             tape.output(emit(e if isinstance(e, Sym) else Sym("const", value=e)))
         rows, cols = (fld.shape if len(fld.shape) == 2 else (1, fld.shape[0]))
         self.last_plan = f"map_tape inputs={len(inputs)} outputs={len(outputs)} instr={len(tape.instr)}"
+        self.last_tape = tape
+        if st is None:
+            return
+        if any(f.buffer is None for f, _ in list(inputs) + list(outputs)):
+            raise LangError("a field was made under plan_only() and holds no device memory")
         ops.map_tape(st, tape, [f.buffer for f, _ in inputs], [f.buffer for f, _ in outputs], rows, cols)
 
 

@@ -71,3 +71,20 @@ def test_compact_summary_carries_every_line():
     assert rows[0] == ["k", 0.1235, 1.05, 0.856, True, 0.012]
     assert rows[1][0].startswith("mandelbrot") and rows[1][3] == 0.47
     assert bench.round_floats({"a": 1.23456789, "b": [2.000001, "s"], "c": 3}) == {"a": 1.2346, "b": [2.0, "s"], "c": 3}
+
+
+def test_the_summary_of_a_default_run_fits_a_1500_character_tail():
+    """Whoever keeps only the end of the benchmark's line must still find every workload in it: the summary is the
+    last key, and with the names a default single-GPU run produces and the widest numbers it can print it stays
+    well under 1500 characters."""
+    import json
+
+    names = ["1080p, 1 stream, 1 image", "1080p, 1 stream, ring of 4", "1080p, 1 stream, ring of 8, recorded", "1080p, 2 streams, recorded",
+             "fractal.py frame 640x320 f32", "fused_map", "map_tape (compiled at first use)", "map_tape (interpreted)", "row_sum", "row_max",
+             "row_softmax", "row_stats_softmax", "mse_tanh_fwd", "mse_tanh_bwd", "graph: 1 kernels", "graph: 3 kernels"]
+    lines = [{"workload": n, "short": n if n[0] in "1f" and n != "fused_map" else None, "kernel": "escape_time" if n[0] == "1" or n.startswith("fractal") else n,
+              "ms": 0.0123456, "roofline": {"frac": 0.98765, "frac_of_nominal_8tbs": 0.87654}, "verified": False, "max_err": 0.00098765} for n in names]
+    rows = bench.compact(lines)
+    assert [r[0] for r in rows] == names
+    tail = json.dumps({"summary": {"headline": [2.123, 0.752, 0.714, False], "others": rows}})
+    assert len(tail) < 1400, len(tail)

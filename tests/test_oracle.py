@@ -152,3 +152,52 @@ def test_coordinate_folding_of_the_front_end_differs_from_fractal_py_on_a_known_
     ci = f(np.cos(f(0.3))) * f(0.2)
     differing = int((counts(xa, ya, ci) != counts(xb, yb, ci)).sum())
     assert differing <= 2 * n * n // 10000   # at most 0.01 % of the frame's pixels
+
+
+@pytest.mark.parametrize("bound", [4.0, 6.25, 400.0, 1.0e30])
+def test_escape_is_final_in_binary32_where_blocks_of_updates_run_untested(bound):
+    """The premise of the kernel that runs blocks of updates without a test (vernondsl_b200/csrc/k_escape_pair.cu):
+    for bound >= 4 and |c| <= 1.5, once a + b > bound the test `!(a + b <= bound)` stays true on every later step,
+    in the exact binary32 operation order of the loop (fractal.py:11-13,22-24), through overflow to Inf and NaN.
+    One test after a block therefore says whether any step inside the block would have ended the pixel."""
+    f = np.float32
+    rng = np.random.default_rng(17)
+    n = 400_000
+    # starting points just outside the bound, a little further out, and far out (overflow within a few steps)
+    radius = np.sqrt(np.float64(bound)) * np.concatenate([1.0 + rng.uniform(0, 1e-6, n // 4), 1.0 + rng.uniform(0, 1e-2, n // 4),
+                                                         rng.uniform(1.0, 4.0, n // 4), 10.0 ** rng.uniform(0, 12, n // 4)])
+    angle = rng.uniform(0, 2 * np.pi, n)
+    zr, zi = (radius * np.cos(angle)).astype(f), (radius * np.sin(angle)).astype(f)
+    cabs = np.where(rng.uniform(size=n) < 0.25, 1.5, rng.uniform(0, 1.5, n))      # a quarter on the limit |c| = 1.5 itself
+    cang = rng.uniform(0, 2 * np.pi, n)
+    cr, ci = (cabs * np.cos(cang)).astype(f), (cabs * np.sin(cang)).astype(f)
+    inside_limit = cr.astype(np.float64) ** 2 + ci.astype(np.float64) ** 2 <= 2.25   # the launcher's own condition on c
+    b32 = f(min(bound, 3.0e38))
+    with np.errstate(over="ignore", invalid="ignore"):
+        a, b = zr * zr, zi * zi
+        started = ~((a + b) <= b32) & inside_limit
+        assert started.sum() > n // 2
+        for step in range(30):
+            t = zr * zi
+            zi = (t + t) + ci
+            zr = (a - b) + cr
+            a, b = zr * zr, zi * zi
+            still = ~((a + b) <= b32)
+            assert still[started].all(), (bound, step, int((~still[started]).sum()))
+
+
+def test_below_the_limits_of_the_untested_blocks_escape_is_not_final():
+    """Why the launcher sends bound < 4 to the kernel that tests every step: with |c| = 1.5 and bound 3, points just
+    outside the bound come back inside it (the condition bound >= 4 is not slack)."""
+    f = np.float32
+    rng = np.random.default_rng(17)
+    n = 100_000
+    radius = np.sqrt(3.0) * (1.0 + rng.uniform(0, 1e-2, n))
+    angle, cang = rng.uniform(0, 2 * np.pi, n), rng.uniform(0, 2 * np.pi, n)
+    zr, zi = (radius * np.cos(angle)).astype(f), (radius * np.sin(angle)).astype(f)
+    cr, ci = (1.5 * np.cos(cang)).astype(f), (1.5 * np.sin(cang)).astype(f)
+    a, b = zr * zr, zi * zi
+    t = zr * zi
+    zi2, zr2 = (t + t) + ci, (a - b) + cr
+    came_back = ((zr2 * zr2 + zi2 * zi2) <= f(3.0)) & ~((a + b) <= f(3.0))
+    assert came_back.sum() > 100

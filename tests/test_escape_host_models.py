@@ -1,6 +1,7 @@
-"""CPU: the rule by which escape_time launches that were declared independent of their predecessors
-are grouped into runs (vernondsl_b200/csrc/k_escape.cu, launch_escape_time), restated and checked
-exhaustively.
+"""CPU: host-side rules of the escape-time launcher, restated and checked exhaustively.
+
+The first is the rule by which escape_time launches that were declared independent of their predecessors
+are grouped into runs (vernondsl_b200/csrc/k_escape.cu, launch_escape_time).
 
 A launch declares k: it touches nothing the k escape_time launches before it on its stream write.
 The launcher starts a launch "overlapped" (it may begin before the launch before it ends) only inside
@@ -71,3 +72,22 @@ def test_a_ring_of_four_orders_every_fourth_launch():
     # anything else on the stream ends the run
     got = plan([3, 3, "x", 3, 3])
     assert [got[i][0] for i in (0, 1, 3, 4)] == [False, True, False, True]
+
+
+def test_rows_visited_from_the_middle_outwards_are_each_visited_once():
+    """The order in which a launch of the work-stealing kernel visits its rows (middle_out in
+    vernondsl_b200/csrc/escape_common.cuh), restated: a permutation for every row count, middle first."""
+    def middle_out(k, rows):
+        mid, h = rows >> 1, (k + 1) >> 1
+        if k & 1:
+            return mid - h if h <= mid else k
+        return mid + h if mid + h < rows else rows - 1 - k
+
+    for rows in list(range(1, 600)) + [1080, 2048, 16384]:
+        order = [middle_out(k, rows) for k in range(rows)]
+        assert sorted(order) == list(range(rows)), rows
+        assert order[0] == rows // 2
+        # distance from the middle never shrinks by more than one row from one visit to the next
+        dist = [abs(r - rows // 2) for r in order]
+        assert all(b >= a - 1 for a, b in zip(dist, dist[1:])), rows
+    assert [middle_out(k, 7) for k in range(7)] == [3, 2, 4, 1, 5, 0, 6]
